@@ -1,0 +1,349 @@
+"""Benchmark of the NVFP4 MoE layer hot path on B200 (one JSON line on stdout, printed by rank 0).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload dsv3|qwen3|c1] [--impl reference]
+
+A step = one pass of the whole layer over one batch of synthetic tokens: bf16 activations -> NVFP4 quantiser ->
+router logits + top-k/softmax -> route map -> permute -> FC1 + SwiGLU + requantise -> FC2 -> weighted combine
+-> bf16 output. `value` times it with the bf16 inputs already resident in HBM; `e2e` times the same call chain
+with pinned HOST buffers (host->device copy of the tokens and device->host copy of the output inside the timed
+region). With --gpus N > 1 (launched under torchrun) experts are sharded over the ranks and tokens travel by
+NCCL all-to-all (weak scaling: every rank brings its own T tokens).
+
+`--impl reference` times the CPU restatement of the reference operator's fp32 dequantise-then-matmul path
+(oracle/) on the host cores, on a bounded sample of the same geometry.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: hidden, intermediate, routed experts, top-k, shared experts, tokens per rank, zipf alpha (0 = uniform)
+    "dsv3": dict(h=7168, i=2048, e=256, k=8, s=1, t=8192, zipf=1.2,
+                 label="deepseek_v3_moe_layer_T8192_E256_top8_shared1_zipf1.2"),
+    "qwen3": dict(h=2048, i=768, e=128, k=8, s=0, t=16384, zipf=0.0, label="qwen3_30b_a3b_moe_layer_T16384_E128_top8"),
+    "c1": dict(h=1024, i=512, e=8, k=2, s=0, t=256, zipf=0.0, label="small_moe_layer_T256_E8_top2"),
+}
+ACT_GLOBAL_SCALE = 1.0 / 448.0     # static (calibrated) activation global scale: amax 6 -> 6/(6*448)
+FP4_NOMINAL_TFLOPS = 9000.0
+L2_BYTES = 126e6
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return dict(hbm_gbs=d["hbm_gbs"], bf16=d["bf16_tflops"], bf16_sustained=d.get("bf16_tflops_sustained", d["bf16_tflops"]),
+                    source="measured")
+    return dict(hbm_gbs=6650.0, bf16=1590.0, bf16_sustained=1400.0, source="fallback")
+
+
+# --------------------------------------------------------------------------------------------- clocks
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.index), "-lms", "100"], stdout=subprocess.PIPE, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons, power = [], [], set(), []
+        for r in self.rows:
+            if len(r) < 7:
+                continue
+            try:
+                sm.append(float(r[0])); mx.append(float(r[1])); power.append(float(r[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["no samples"])
+        return dict(sm_mhz=float(np.median(sm)), sm_max_mhz=float(max(mx)), power_w_max=float(max(power)), samples=len(sm),
+                    reasons=sorted(reasons))
+
+
+# --------------------------------------------------------------------------------------------- synthetic layer
+def build_layer(wl, rank, world, device):
+    """Random-init weights of the named geometry, quantised on the device with per-expert global scales
+    amax/(6*448); the routed experts are sharded contiguously over the ranks, the shared expert is replicated."""
+    import torch
+    import kernelschema_b200 as ks
+    h, i, e, s = wl["h"], wl["i"], wl["e"], wl["s"]
+    e_local = e // world
+    etot = e_local + s
+    gen = torch.Generator(device=device).manual_seed(1000 + rank)
+    w1q = torch.empty((etot, 2 * i, h // 2), dtype=torch.uint8, device=device)
+    w1s = torch.empty((etot, 2 * i, h // 16), dtype=torch.uint8, device=device)
+    w2q = torch.empty((etot, h, i // 2), dtype=torch.uint8, device=device)
+    w2s = torch.empty((etot, h, i // 16), dtype=torch.uint8, device=device)
+    g1 = torch.empty(etot, dtype=torch.float32, device=device)
+    g2 = torch.empty(etot, dtype=torch.float32, device=device)
+    for j in range(etot):
+        if j >= e_local:   # shared expert: same values on every rank
+            gen_j = torch.Generator(device=device).manual_seed(7)
+        else:
+            gen_j = gen
+        w = (torch.randn((2 * i, h), device=device, generator=gen_j) * 0.02).to(torch.bfloat16)
+        g1[j] = w.float().abs().max() / (6.0 * 448.0)
+        q, sf = ks.nvfp4_quantize(w, float(g1[j]), tiled_scales=True)
+        w1q[j] = q
+        w1s[j] = sf.reshape(2 * i, h // 16)
+        w = (torch.randn((h, i), device=device, generator=gen_j) * 0.02).to(torch.bfloat16)
+        g2[j] = w.float().abs().max() / (6.0 * 448.0)
+        q, sf = ks.nvfp4_quantize(w, float(g2[j]), tiled_scales=True)
+        w2q[j] = q
+        w2s[j] = sf.reshape(h, i // 16)
+    gen0 = torch.Generator(device=device).manual_seed(5)
+    gate_w = (torch.randn((e, h), device=device, generator=gen0) * 0.02).to(torch.bfloat16)
+    bias = None
+    if wl["zipf"] > 0:
+        perm = torch.randperm(e, device=device, generator=gen0)
+        bias = torch.log(1.0 / (perm.float() + 1.0) ** wl["zipf"])
+    return dict(w1q=w1q, w1s=w1s, w2q=w2q, w2s=w2s, scale_fc1=(g1 * ACT_GLOBAL_SCALE).contiguous(), scale_fc2=g2.contiguous(),
+                gate_w=gate_w, bias=bias, e_local=e_local)
+
+
+def make_step(wl, L, world, device):
+    """Returns step(x_bf16_device) -> out_bf16_device, the launch count per step, and the route statistics."""
+    import torch
+    import kernelschema_b200 as ks
+    h, i, k, s, t = wl["h"], wl["i"], wl["k"], wl["s"], wl["t"]
+    if world == 1:
+        layer = ks.MoELayer(h, i, L["e_local"], k, t, num_shared_experts=s, tile_n=int(os.environ.get("B200MOE_TILE_N", "0")))
+        out = torch.empty((t, h), dtype=torch.bfloat16, device=device)
+
+        def step(x):
+            hq, hs = ks.nvfp4_quantize(x, ACT_GLOBAL_SCALE)
+            ids, w = ks.route_topk(ks.router_logits(x, L["gate_w"]), k, L["bias"])
+            layer.run(ids, w, hq, hs.view(torch.uint8), L["w1q"], L["w1s"], L["w2q"], L["w2s"], out, scale_up=L["scale_fc1"],
+                      scale_gate=L["scale_fc1"], scale_out=L["scale_fc2"])
+            return out, ids
+
+        return step, layer, 10
+    from kernelschema_b200.ep import ExpertParallelMoE
+    ep = ExpertParallelMoE(h, i, wl["e"], k, t, num_shared_experts=s)
+
+    def step(x):
+        hq, hs = ks.nvfp4_quantize(x, ACT_GLOBAL_SCALE)
+        ids, w = ks.route_topk(ks.router_logits(x, L["gate_w"]), k, L["bias"])
+        out = ep.forward(ids, w, hq, hs.view(torch.uint8), L["w1q"], L["w1s"], L["w2q"], L["w2s"], scale_up=L["scale_fc1"],
+                         scale_gate=L["scale_fc1"], scale_out=L["scale_fc2"])
+        return out, ids
+
+    return step, ep, ep.launches_per_step + 3
+
+
+def layer_flops(wl, valid_routes, tokens):
+    return 6.0 * valid_routes * wl["i"] * wl["h"] + 6.0 * tokens * wl["s"] * wl["i"] * wl["h"]
+
+
+# --------------------------------------------------------------------------------------------- CPU arm
+def cpu_sample_case(wl):
+    """Bounded sample of the workload for the host cores: same hidden / intermediate sizes, 8 routed experts
+    (+ the shared one), 256 tokens, top-2."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from helpers import make_moe_case
+    e, k, t = (8, 2, 256) if wl["e"] >= 8 else (wl["e"], wl["k"], wl["t"])
+    p = make_moe_case(0, t, wl["h"], wl["i"], e, k, shared=wl["s"], global_scales=True)
+    valid = int((p["topk_ids"][0] >= 0).sum())
+    flops = 6.0 * valid * wl["i"] * wl["h"] + 6.0 * t * wl["s"] * wl["i"] * wl["h"]
+    desc = f"H={wl['h']} I={wl['i']} experts={e}+{wl['s']} shared, T={t}, top-{k}: {flops / 1e9:.1f} GFLOP per pass"
+    return p, flops, t, desc
+
+
+def time_cpu(wl, steps, warmup):
+    from oracle import nvfp4_oracle as o
+    p, flops, t, desc = cpu_sample_case(wl)
+    for _ in range(warmup):
+        o.moe_expected(p)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        o.moe_expected(p)
+    dt = (time.perf_counter() - t0) / steps
+    return dict(tflops=flops / dt / 1e12, tokens_per_s=t / dt, seconds=dt, sample=desc, cores=os.cpu_count())
+
+
+def run_reference(args, wl):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    r = time_cpu(wl, max(1, args.steps), max(0, min(args.warmup, 1)))
+    line = dict(impl="reference", metric="nvfp4_moe_layer_tflops", value=r["tflops"], unit="TFLOP/s", n_gpus=args.gpus,
+                steps=args.steps, warmup=args.warmup, ms_per_step=r["seconds"] * 1e3, higher_is_better=True, scaling="weak",
+                vs_baseline=None, dtype="f32", data="synthetic", tokens_per_s=r["tokens_per_s"],
+                config=dict(workload=wl["label"], sample=r["sample"]),
+                cpu_baseline=dict(value=r["tflops"], unit="TFLOP/s", cores=r["cores"], kind="port", sample=r["sample"]),
+                e2e=dict(value=r["tflops"], unit="TFLOP/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0))
+    print(json.dumps(line))
+
+
+# --------------------------------------------------------------------------------------------- GPU arm
+def run_gpu(args, wl):
+    import torch
+    import torch.distributed as dist
+    import kernelschema_b200 as ks   # noqa: F401  (fails loudly if the library is missing)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run --nproc-per-node {args.gpus}")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    if wl["e"] % world:
+        raise SystemExit("experts must divide evenly over the ranks")
+    L = build_layer(wl, rank, world, device)
+    step, owner, launches = make_step(wl, L, world, device)
+    t, h = wl["t"], wl["h"]
+    gen = torch.Generator(device=device).manual_seed(42 + rank)
+    x_dev = torch.randn((t, h), device=device, generator=gen).to(torch.bfloat16)
+    x_host = x_dev.cpu().pin_memory()
+    out_host = torch.empty((t, h), dtype=torch.bfloat16).pin_memory()
+    x_stage = torch.empty_like(x_dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps, warmup):
+        for _ in range(warmup):
+            fn()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=device)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    state = {}
+
+    def resident():
+        state["out"], state["ids"] = step(x_dev)
+
+    def end_to_end():
+        x_stage.copy_(x_host, non_blocking=True)
+        out, _ = step(x_stage)
+        out_host.copy_(out, non_blocking=True)
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ms = timed(resident, args.steps, args.warmup)
+    clocks = sampler.stop() if rank == 0 else None
+    ms_e2e = timed(end_to_end, args.steps, max(1, args.warmup))
+    status = owner.status()
+
+    valid = (state["ids"] >= 0).sum().to(torch.float64)
+    if world > 1:
+        dist.all_reduce(valid)
+    flops = layer_flops(wl, float(valid.item()), t * world)
+    per_step = ms / args.steps
+    tflops = flops / (per_step * 1e-3) / 1e12
+    tflops_e2e = flops / (ms_e2e / args.steps * 1e-3) / 1e12
+
+    roof = stage = None
+    if world == 1:
+        # stage durations with CUDA events on the launching stream (same inputs, same launches)
+        hq, hs = ks.nvfp4_quantize(x_dev, ACT_GLOBAL_SCALE)
+        ids, w = ks.route_topk(ks.router_logits(x_dev, L["gate_w"]), wl["k"], L["bias"])
+        acc = None
+        reps = max(3, min(args.steps, 10))
+        for _ in range(reps):
+            d = owner.run_profiled(ids, w, hq, hs.view(torch.uint8), L["w1q"], L["w1s"], L["w2q"], L["w2s"], state["out"],
+                                   scale_up=L["scale_fc1"], scale_gate=L["scale_fc1"], scale_out=L["scale_fc2"])
+            acc = d if acc is None else {k2: acc[k2] + v for k2, v in d.items()}
+        stage = {k2: v / reps for k2, v in acc.items()}
+        pk = peaks()
+        fc1_flops = flops * 2.0 / 3.0
+        achieved = fc1_flops / (stage["fc1"] * 1e-3) / 1e12
+        peak = 4.0 * pk["bf16_sustained"]
+        roof = dict(bound="tensor", kernel="k_gemm_nvfp4<FC1>", achieved=achieved, peak=peak, unit="TFLOP/s", frac=achieved / peak,
+                    peak_source=f"4 x bf16_tflops_sustained of {pk['source']} MEASURED_PEAKS (FP4:bf16 nominal ratio)",
+                    frac_of_nominal_fp4=achieved / FP4_NOMINAL_TFLOPS, traffic=None,
+                    layer_frac_of_nominal_fp4=tflops / FP4_NOMINAL_TFLOPS)
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    cpu = time_cpu(wl, 1, 0) if world == 1 else None
+    line = dict(metric="nvfp4_moe_layer_tflops", value=tflops, unit="TFLOP/s", n_gpus=world, steps=args.steps, warmup=args.warmup,
+                ms_per_step=per_step, higher_is_better=True, scaling="weak", vs_baseline=None, dtype="nvfp4 (e2m1 x ue4m3, fp32 accumulate)",
+                data="synthetic", tokens_per_s=t * world / (per_step * 1e-3),
+                config=dict(workload=wl["label"], tokens_per_gpu=t, hidden=h, intermediate=wl["i"], experts=wl["e"], top_k=wl["k"],
+                            shared_experts=wl["s"], parallelism=f"ep{world}",
+                            l2="weights (%.2f GB per GPU) exceed the 126 MB L2; no flush needed" %
+                               ((L["w1q"].numel() + L["w1s"].numel() + L["w2q"].numel() + L["w2s"].numel()) / 1e9)),
+                e2e=dict(value=tflops_e2e, unit="TFLOP/s", h2d_bytes_per_step=x_host.numel() * 2, d2h_bytes_per_step=out_host.numel() * 2,
+                         ms_per_step=ms_e2e / args.steps),
+                gpu_launches=launches * args.steps, device_status=status, clocks=clocks)
+    if stage:
+        line["stage_ms"] = stage
+    if roof:
+        line["roofline"] = roof
+    if cpu:
+        line["cpu_baseline"] = dict(value=cpu["tflops"], unit="TFLOP/s", cores=cpu["cores"], kind="port", sample=cpu["sample"],
+                                    tokens_per_s=cpu["tokens_per_s"])
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="dsv3", choices=sorted(WORKLOADS))
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+    wl = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        run_reference(args, wl)
+    else:
+        run_gpu(args, wl)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,151 @@
+/* b200moe — C ABI of the B200 (sm_100a) NVFP4 mixture-of-experts library.
+ *
+ * Drop-in boundary for the `nvfp4_fused_moe` operator of bcacdwk/KernelSchema
+ * (kernel_wiki/aka-cuda-operators-20261030/operators/moe/nvfp4_fused_moe, "NV/" below) and for the dense
+ * NVFP4 GEMM next to it (operators/gemm/dense/bf16_nvfp4_gemm, "DG/" below). Plain pointers and sizes only:
+ * all pointers are CUDA device pointers unless stated otherwise, `stream` is a cudaStream_t passed as void*.
+ * Every function returns 0 on success or a non-zero code (CUDA error numbers < 700; 7xx = argument, shape or
+ * tensor-map refusals raised before any launch); b200moe_last_error() gives the text. Nothing throws, nothing
+ * traps on the device; bounded device waits report through b200moe_status().
+ *
+ * Number formats (NV/problem/input.py:53-71, NV/problem/reference.py:28-50): payload = two E2M1 codes per
+ * byte, even element in the low nibble; one E4M3 scale byte per 16 elements along K; weights in the published
+ * prepared layout (NV/problem/input.py:82-99: rows 32-shuffled, FC1 rows up/gate interleaved, scales in
+ * 128-row x 4-column tiles).
+ */
+#ifndef B200MOE_H
+#define B200MOE_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200MOE_ABI_VERSION 1
+
+/* Scale-factor layouts. */
+#define B200MOE_SF_ROW_MAJOR 0 /* [rows, cols/16]                                   */
+#define B200MOE_SF_TILED 1     /* [ceil(rows/128), cols/64, 32, 16] (128x4 tiles)   */
+
+typedef struct b200moe_layer* b200moe_handle;
+
+/* Geometry of one MoE layer instance; fixes the workspace the library owns for it. */
+typedef struct {
+  int32_t struct_size;        /* sizeof(b200moe_config) */
+  int32_t hidden;             /* H, multiple of 256 */
+  int32_t intermediate;       /* I, multiple of 256 */
+  int32_t num_experts;        /* routed experts held by this instance (local experts) */
+  int32_t top_k;              /* routed slots per token */
+  int32_t num_shared_experts; /* S experts every token also visits with weight 1; stored after the routed ones */
+  int32_t max_tokens;         /* largest T a run may pass */
+  int32_t tile_n;             /* GEMM n-tile: 0 = default, else 128 or 256 */
+  int32_t reserved[8];
+} b200moe_config;
+
+/* One forward call. Field names follow the reference operator's forward() arguments
+ * (NV/problem/reference.py:96; layouts NV/problem/input.py:101-112). */
+typedef struct {
+  int32_t struct_size;               /* sizeof(b200moe_args) */
+  int32_t num_tokens;                /* T */
+  const int32_t* topk_ids;           /* [T, top_k]; ids outside [offset, offset+num_experts) are skipped (-1 = none) */
+  const float* topk_weights;         /* [T, top_k] */
+  const void* hidden_states;         /* uint8 [T, H/2] */
+  const void* hidden_states_scale;   /* E4M3 bytes, layout below */
+  int32_t hidden_states_scale_layout;/* 2 = row-major [T, H/16] (the reference's value); 1 = 128x4 tiled */
+  int32_t activation_type;           /* 3 = gate*sigmoid(alpha*gate)*(up+beta); 10 = SiTU (NV/problem/reference.py:86-89) */
+  const void* gemm1_weights;         /* uint8 [E+S, 2I, H/2] prepared */
+  const void* gemm1_weights_scale;   /* E4M3 [E+S, 2I, H/16] bytes holding 128x4 tiles */
+  const void* gemm2_weights;         /* uint8 [E+S, H, I/2] prepared */
+  const void* gemm2_weights_scale;   /* E4M3 [E+S, H, I/16] bytes holding 128x4 tiles */
+  const float* gemm1_alpha;          /* [E+S] or NULL (=1) */
+  const float* gemm1_beta;           /* [E+S] or NULL (=0) */
+  const float* gemm1_clamp_limit;    /* [E+S] or NULL (no clamp) */
+  const float* output1_scale_scalar;      /* [E+S] multiplier of the FC1 "up" accumulator, or NULL (=1) */
+  const float* output1_scale_gate_scalar; /* [E+S] multiplier of the FC1 "gate" accumulator, or NULL (=1) */
+  const float* output2_scale_scalar;      /* [E+S] multiplier of the FC2 accumulator, or NULL (=1) */
+  int32_t local_expert_offset;       /* id of this instance's first routed expert */
+  int32_t reserved0;
+  void* output;                      /* bf16 [T, H]; the only caller memory that is written */
+  int64_t output_stride;             /* elements between output rows (H when contiguous) */
+} b200moe_args;
+
+/* Device pointers into the library-owned workspace of a layer, for tests and for the expert-parallel
+ * wrapper. Valid until b200moe_destroy. */
+typedef struct {
+  int32_t* counts;        /* [E+S] routes per expert */
+  int32_t* seg_start;     /* [E+S+1] first permuted row of each expert (multiples of 128) */
+  int32_t* tile_expert;   /* [tile_capacity] */
+  int32_t* tile_row0;     /* [tile_capacity] */
+  int32_t* tile_rows;     /* [tile_capacity] */
+  int32_t* totals;        /* {m-tiles, permuted rows in use, valid routes} */
+  int32_t* row_of;        /* [T, top_k+S] permuted row of a route or -1 */
+  int32_t* tok_of_row;    /* [row_capacity] token of a permuted row or -1 */
+  float* weight_of_row;   /* [row_capacity] */
+  uint8_t* a_q;           /* [row_capacity, H/2] permuted activations */
+  uint8_t* a_sf;          /* tiled scales of a_q */
+  uint8_t* act_q;         /* [row_capacity, I/2] requantised intermediate */
+  uint8_t* act_sf;        /* tiled scales of act_q */
+  uint16_t* rout;         /* bf16 [row_capacity, H] per-route FC2 results */
+  int64_t row_capacity;
+  int64_t tile_capacity;
+} b200moe_workspace_view;
+
+int b200moe_abi_version(void);
+/* Text of the calling thread's last failure ("" if none). Host memory owned by the library. */
+const char* b200moe_last_error(void);
+
+/* (2) bf16 -> NVFP4 quantiser. Replaces quantize() of NV/problem/input.py:53-71 (global_scale == 1) and of
+ * DG/problem/input.py:40-64 (global_scale != 1); codes and scale bytes are bit-identical to them.
+ * x: bf16 [rows, cols] with row_stride elements between rows; cols % 64 == 0; payload: uint8 [rows, cols/2];
+ * scales: layout B200MOE_SF_ROW_MAJOR or B200MOE_SF_TILED (caller sizes it for rows rounded up to 128). */
+int b200moe_quantize_nvfp4(const void* x, int64_t rows, int64_t cols, int64_t row_stride, float global_scale, void* payload,
+                           void* scales, int32_t scale_layout, void* stream);
+
+/* Row-major scale bytes [rows, cols/16] -> 128x4 tiles (the block_scales() step of NV/problem/input.py:82-87
+ * for one matrix). dst holds ceil(rows/128)*128 * cols/16 bytes; padding rows become 0. */
+int b200moe_scales_to_tiles(const void* scales_row_major, int64_t rows, int64_t cols, void* dst, void* stream);
+
+/* (1) Router. logits fp32 [T, E]; optional bias fp32 [E] added before selection. Replaces the selection part
+ * of routes() in NV/problem/input.py:35-36: ids = top-k by logit (descending, ties to the lower index),
+ * weights = softmax over the selected logits. ids int32 [T, K], weights fp32 [T, K]. E <= 1024, K <= 32. */
+int b200moe_route_topk(const float* logits, const float* bias, int64_t num_tokens, int32_t num_experts, int32_t top_k,
+                       int32_t* ids, float* weights, void* stream);
+/* Router logits x[T,H] (bf16) times gate[E,H]^T (bf16) in fp32. The reference synthesises its logits
+ * (NV/problem/input.py:23-27), so this has no counterpart there. */
+int b200moe_router_logits(const void* x, const void* gate_weight, int64_t num_tokens, int32_t hidden, int32_t num_experts,
+                          float* logits, void* stream);
+
+/* Dense NVFP4 GEMM: out[M,N] = bf16(alpha * A @ B^T), both operands NVFP4 with tiled scales. Contract of
+ * DG/problem/reference.py:10-15 with the A operand quantised by b200moe_quantize_nvfp4; B rows are logical
+ * (no shuffle). K % 256 == 0, N % tile_n == 0. status: optional device int32 that receives a non-zero code
+ * if a bounded device wait expired. */
+int b200moe_gemm_nvfp4(const void* a_q, const void* a_sf_tiled, const void* b_q, const void* b_sf_tiled, float alpha, void* out,
+                       int64_t m, int64_t n, int64_t k, int64_t out_stride, int32_t tile_n, int32_t* status, void* stream);
+
+/* Layer life cycle. Replaces moe_init / moe_run of NV/candidate/nvfp4_moe.cu:6618, :9496 (bound there through
+ * ctypes, NV/candidate/solution.py:96-102). create allocates the workspace on the current device. */
+int b200moe_create(const b200moe_config* cfg, b200moe_handle* out);
+int b200moe_destroy(b200moe_handle h);
+int64_t b200moe_workspace_bytes(const b200moe_config* cfg);
+int b200moe_workspace(b200moe_handle h, b200moe_workspace_view* out);
+
+/* (1b) Expert-permutation index build only (route map into the workspace). Replaces k_count / k_scan_tiles /
+ * k_scatter_agg of NV/candidate/nvfp4_moe.cu:582, :750, :700. */
+int b200moe_route_map(b200moe_handle h, const int32_t* topk_ids, const float* topk_weights, int32_t num_tokens,
+                      int32_t local_expert_offset, void* stream);
+
+/* (3)+(4) Whole layer on `stream`, asynchronous: route map, permute, FC1 + activation + NVFP4 requantise,
+ * FC2, routing-weighted combine into args->output. Replaces run_pipeline of NV/candidate/nvfp4_moe.cu:9078-9363
+ * and matches expected() of NV/problem/reference.py:69-92 within the operator's tolerance. */
+int b200moe_run(b200moe_handle h, const b200moe_args* args, void* stream);
+/* Same, recording CUDA events between stages and returning their durations in milliseconds (synchronises).
+ * stage_ms[0..4] = route map, permute, FC1, FC2, combine. Counterpart of moe_profile, NV/candidate/nvfp4_moe.cu:9678. */
+int b200moe_run_profiled(b200moe_handle h, const b200moe_args* args, void* stream, float* stage_ms);
+/* Synchronises `stream` and returns the device status word of the layer (0 = no bounded wait expired). */
+int b200moe_status(b200moe_handle h, void* stream, int32_t* code);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200MOE_H */

@@ -1,0 +1,411 @@
+// C-ABI layer of libb200moe: argument checks, workspace ownership, tensor-map cache and the launch chain.
+// Declarations and the reference interfaces they replace are in include/b200moe.h.
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "../../include/b200moe.h"
+#include "kernels.cuh"
+
+using namespace b200;
+
+static thread_local char g_err[512] = "";
+
+static int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+static int cuda_fail(int code, const char* what) {
+  if (code == 0) return 0;
+  if (code < 700)
+    return fail(code, "%s: CUDA error %d (%s)", what, code, cudaGetErrorString((cudaError_t)code));
+  return fail(code, "%s: refused with code %d", what, code);
+}
+
+struct b200moe_layer {
+  b200moe_config cfg;
+  int etot;              // E + S
+  int kk;                // top_k + S
+  int64_t row_capacity;  // permuted rows
+  int64_t tile_capacity;
+  int sm_count;
+  int bn;
+  void* base;            // one cudaMalloc
+  int64_t bytes;
+  RouteMapBuffers rm;
+  uint8_t *a_q, *a_sf, *act_q, *act_sf;
+  __nv_bfloat16* rout;
+  int32_t* status;
+  CUtensorMap tm_a1, tm_a2, tm_b1, tm_b2;
+  const void* b1_ptr;
+  const void* b2_ptr;
+};
+
+namespace {
+
+int64_t align_up(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
+
+struct Plan {
+  int64_t row_capacity, tile_capacity, nblk;
+  int64_t off_block_hist, off_counts, off_seg, off_texp, off_trow0, off_trows, off_totals, off_row_of, off_tok, off_w, off_aq,
+      off_asf, off_actq, off_actsf, off_rout, off_status, total;
+};
+
+int check_cfg(const b200moe_config* c) {
+  if (!c || c->struct_size != (int32_t)sizeof(b200moe_config)) return fail(710, "config: bad struct_size");
+  if (c->hidden <= 0 || c->hidden % 256) return fail(711, "config: hidden=%d must be a positive multiple of 256", c->hidden);
+  if (c->intermediate <= 0 || c->intermediate % 256)
+    return fail(712, "config: intermediate=%d must be a positive multiple of 256", c->intermediate);
+  if (c->num_experts < 0 || c->num_shared_experts < 0 || c->num_experts + c->num_shared_experts <= 0 ||
+      c->num_experts + c->num_shared_experts > 1024)
+    return fail(713, "config: num_experts + num_shared_experts must be in 1..1024");
+  if (c->top_k < 0 || c->top_k > 32 || c->top_k + c->num_shared_experts <= 0) return fail(714, "config: top_k out of range");
+  if (c->max_tokens <= 0) return fail(715, "config: max_tokens must be positive");
+  if (c->tile_n != 0 && c->tile_n != 128 && c->tile_n != 256) return fail(716, "config: tile_n must be 0, 128 or 256");
+  return 0;
+}
+
+Plan make_plan(const b200moe_config& c) {
+  Plan p;
+  const int64_t etot = c.num_experts + c.num_shared_experts, kk = c.top_k + c.num_shared_experts;
+  const int64_t routes = (int64_t)c.max_tokens * kk;
+  // an expert with c routes owns ceil(c/128) <= c/128 + 1 tiles, so this bounds every routing
+  p.tile_capacity = routes / 128 + etot + 1;
+  p.row_capacity = p.tile_capacity * 128;
+  p.nblk = (routes + 2047) / 2048;
+  int64_t o = 0;
+  auto take = [&](int64_t bytes) { int64_t at = o; o = align_up(o + bytes, 1024); return at; };
+  p.off_block_hist = take(4 * (p.nblk + 1) * etot);
+  p.off_counts = take(4 * etot);
+  p.off_seg = take(4 * (etot + 1));
+  p.off_texp = take(4 * p.tile_capacity);
+  p.off_trow0 = take(4 * p.tile_capacity);
+  p.off_trows = take(4 * p.tile_capacity);
+  p.off_totals = take(16);
+  p.off_row_of = take(4 * routes);
+  p.off_tok = take(4 * p.row_capacity);
+  p.off_w = take(4 * p.row_capacity);
+  p.off_aq = take(p.row_capacity * (c.hidden / 2));
+  p.off_asf = take(p.row_capacity * (c.hidden / 16));
+  p.off_actq = take(p.row_capacity * (c.intermediate / 2));
+  p.off_actsf = take(p.row_capacity * (c.intermediate / 16));
+  p.off_rout = take(p.row_capacity * c.hidden * 2);
+  p.off_status = take(16);
+  p.total = o;
+  return p;
+}
+
+int check_args(const b200moe_layer* h, const b200moe_args* a) {
+  if (!h) return fail(720, "run: null handle");
+  if (!a || a->struct_size != (int32_t)sizeof(b200moe_args)) return fail(721, "run: bad args struct_size");
+  if (a->num_tokens < 0 || a->num_tokens > h->cfg.max_tokens)
+    return fail(722, "run: num_tokens=%d outside 0..max_tokens=%d", a->num_tokens, h->cfg.max_tokens);
+  if (a->num_tokens == 0) return 0;
+  if (h->cfg.top_k > 0 && (!a->topk_ids || !a->topk_weights)) return fail(723, "run: topk_ids / topk_weights are null");
+  if (!a->hidden_states || !a->hidden_states_scale) return fail(724, "run: hidden_states / hidden_states_scale are null");
+  if (a->hidden_states_scale_layout != 2 && a->hidden_states_scale_layout != 1)
+    return fail(725, "run: hidden_states_scale_layout=%d, expected 2 (row-major) or 1 (tiled)", a->hidden_states_scale_layout);
+  if (!a->gemm1_weights || !a->gemm1_weights_scale || !a->gemm2_weights || !a->gemm2_weights_scale)
+    return fail(726, "run: weight pointers are null");
+  if (a->activation_type != 3 && a->activation_type != 10)
+    return fail(727, "run: activation_type=%d, expected 3 or 10", a->activation_type);
+  if (!a->output) return fail(728, "run: output is null");
+  if (a->output_stride < h->cfg.hidden || a->output_stride % 8)
+    return fail(729, "run: output_stride=%lld must be >= hidden and a multiple of 8", (long long)a->output_stride);
+  if (((uintptr_t)a->output | (uintptr_t)a->hidden_states | (uintptr_t)a->gemm1_weights | (uintptr_t)a->gemm2_weights |
+       (uintptr_t)a->gemm1_weights_scale | (uintptr_t)a->gemm2_weights_scale) & 15)
+    return fail(730, "run: tensors must be 16-byte aligned");
+  if (((uintptr_t)a->hidden_states_scale) & 3) return fail(731, "run: hidden_states_scale must be 4-byte aligned");
+  return 0;
+}
+
+int run_impl(b200moe_layer* h, const b200moe_args* a, cudaStream_t st, cudaEvent_t* ev) {
+  const b200moe_config& c = h->cfg;
+  const int T = a->num_tokens;
+  if (T == 0) return 0;
+  int rc;
+  auto mark = [&](int i) { if (ev) cudaEventRecord(ev[i], st); };
+  mark(0);
+  rc = launch_route_map(a->topk_ids, a->topk_weights, T, c.top_k, c.num_shared_experts, c.num_experts, a->local_expert_offset,
+                        h->rm, st);
+  if (rc) return cuda_fail(rc, "route map");
+  mark(1);
+  rc = launch_gather_rows(a->hidden_states, a->hidden_states_scale, a->hidden_states_scale_layout == 1, h->rm.tok_of_row,
+                          h->rm.totals, c.hidden, h->row_capacity, h->a_q, h->a_sf, st);
+  if (rc) return cuda_fail(rc, "permute");
+  mark(2);
+  if (h->b1_ptr != a->gemm1_weights) {
+    rc = make_operand_map(&h->tm_b1, a->gemm1_weights, (uint64_t)h->etot * 2 * c.intermediate, c.hidden / 2, h->bn);
+    if (rc) return cuda_fail(rc, "FC1 weight tensor map");
+    h->b1_ptr = a->gemm1_weights;
+  }
+  if (h->b2_ptr != a->gemm2_weights) {
+    rc = make_operand_map(&h->tm_b2, a->gemm2_weights, (uint64_t)h->etot * c.hidden, c.intermediate / 2, h->bn);
+    if (rc) return cuda_fail(rc, "FC2 weight tensor map");
+    h->b2_ptr = a->gemm2_weights;
+  }
+  GemmParams g;
+  memset(&g, 0, sizeof(g));
+  g.tile_expert = h->rm.tile_expert;
+  g.tile_row0 = h->rm.tile_row0;
+  g.tile_rows = h->rm.tile_rows;
+  g.n_tiles_ptr = h->rm.totals;
+  g.status = h->status;
+  // FC1: [rows, H] x [2I, H]^T -> activation -> NVFP4 [rows, I]
+  g.N = 2 * c.intermediate;
+  g.K = c.hidden;
+  g.sfa = h->a_sf;
+  g.sfb = (const uint8_t*)a->gemm1_weights_scale;
+  g.act_q = h->act_q;
+  g.act_sf = h->act_sf;
+  g.scale_up = a->output1_scale_scalar;
+  g.scale_gate = a->output1_scale_gate_scalar;
+  g.alpha = a->gemm1_alpha;
+  g.beta = a->gemm1_beta;
+  g.limit = a->gemm1_clamp_limit;
+  g.act_type = a->activation_type;
+  {
+    const int64_t worst_tiles = (int64_t)T * h->kk / 128 + h->etot;
+    const int64_t items = worst_tiles * (g.N / h->bn);
+    const int grid = (int)(items < h->sm_count ? items : h->sm_count);
+    rc = launch_gemm_nvfp4(kGemmFc1, h->bn, h->tm_a1, h->tm_b1, g, grid, st);
+    if (rc) return cuda_fail(rc, "FC1");
+  }
+  mark(3);
+  // FC2: [rows, I] x [H, I]^T -> bf16 [rows, H]
+  g.N = c.hidden;
+  g.K = c.intermediate;
+  g.sfa = h->act_sf;
+  g.sfb = (const uint8_t*)a->gemm2_weights_scale;
+  g.out = h->rout;
+  g.out_stride = c.hidden;
+  g.out_scale = a->output2_scale_scalar;
+  {
+    const int64_t worst_tiles = (int64_t)T * h->kk / 128 + h->etot;
+    const int64_t items = worst_tiles * (g.N / h->bn);
+    const int grid = (int)(items < h->sm_count ? items : h->sm_count);
+    rc = launch_gemm_nvfp4(kGemmFc2, h->bn, h->tm_a2, h->tm_b2, g, grid, st);
+    if (rc) return cuda_fail(rc, "FC2");
+  }
+  mark(4);
+  rc = launch_finalize(h->rout, h->rm.row_of, h->rm.weight_of_row, T, h->kk, c.hidden, a->output, a->output_stride, st);
+  if (rc) return cuda_fail(rc, "combine");
+  mark(5);
+  return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+int b200moe_abi_version(void) { return B200MOE_ABI_VERSION; }
+const char* b200moe_last_error(void) { return g_err; }
+
+int b200moe_quantize_nvfp4(const void* x, int64_t rows, int64_t cols, int64_t row_stride, float global_scale, void* payload,
+                           void* scales, int32_t scale_layout, void* stream) {
+  if (rows < 0 || cols <= 0 || cols % 64) return fail(740, "quantize: cols=%lld must be a positive multiple of 64", (long long)cols);
+  if (row_stride < cols || row_stride % 8) return fail(741, "quantize: row_stride must be >= cols and a multiple of 8");
+  if (rows && (!x || !payload || !scales)) return fail(742, "quantize: null pointer");
+  if (((uintptr_t)x & 15) || ((uintptr_t)payload & 7)) return fail(743, "quantize: x must be 16-byte and payload 8-byte aligned");
+  if (!(global_scale > 0.f)) return fail(744, "quantize: global_scale must be positive");
+  if (scale_layout != B200MOE_SF_ROW_MAJOR && scale_layout != B200MOE_SF_TILED) return fail(745, "quantize: unknown scale_layout");
+  return cuda_fail(launch_quantize_nvfp4(x, rows, cols, row_stride, global_scale, payload, scales, scale_layout, (cudaStream_t)stream),
+                   "quantize");
+}
+
+int b200moe_scales_to_tiles(const void* src, int64_t rows, int64_t cols, void* dst, void* stream) {
+  if (rows < 0 || cols <= 0 || cols % 64) return fail(746, "scales_to_tiles: cols must be a positive multiple of 64");
+  if (rows && (!src || !dst)) return fail(747, "scales_to_tiles: null pointer");
+  if (((uintptr_t)src & 3) || ((uintptr_t)dst & 15)) return fail(748, "scales_to_tiles: misaligned pointer");
+  return cuda_fail(launch_sf_to_tiles(src, rows, cols / 16, dst, (cudaStream_t)stream), "scales_to_tiles");
+}
+
+int b200moe_route_topk(const float* logits, const float* bias, int64_t T, int32_t E, int32_t K, int32_t* ids, float* weights,
+                       void* stream) {
+  if (T < 0 || E <= 0 || E > 1024 || K <= 0 || K > 32 || K > E) return fail(750, "route_topk: need 0 < K <= min(E, 32), E <= 1024");
+  if (T && (!logits || !ids || !weights)) return fail(751, "route_topk: null pointer");
+  return cuda_fail(launch_route_topk(logits, bias, T, E, K, ids, weights, (cudaStream_t)stream), "route_topk");
+}
+
+int b200moe_router_logits(const void* x, const void* w, int64_t T, int32_t H, int32_t E, float* logits, void* stream) {
+  if (T < 0 || H <= 0 || H % 8 || E <= 0) return fail(752, "router_logits: hidden must be a positive multiple of 8");
+  if (T && (!x || !w || !logits)) return fail(753, "router_logits: null pointer");
+  if (((uintptr_t)x | (uintptr_t)w) & 15) return fail(754, "router_logits: operands must be 16-byte aligned");
+  return cuda_fail(launch_router_logits(x, w, T, H, E, logits, (cudaStream_t)stream), "router_logits");
+}
+
+int b200moe_gemm_nvfp4(const void* a_q, const void* a_sf, const void* b_q, const void* b_sf, float alpha, void* out, int64_t m,
+                       int64_t n, int64_t k, int64_t out_stride, int32_t tile_n, int32_t* status, void* stream) {
+  const int bn = tile_n ? tile_n : 128;
+  if (bn != 128 && bn != 256) return fail(760, "gemm: tile_n must be 0, 128 or 256");
+  if (m < 0 || n <= 0 || k <= 0 || k % 256 || n % bn) return fail(761, "gemm: need K %% 256 == 0 and N %% tile_n == 0");
+  if (m == 0) return 0;
+  if (!a_q || !a_sf || !b_q || !b_sf || !out) return fail(762, "gemm: null pointer");
+  if (((uintptr_t)a_q | (uintptr_t)a_sf | (uintptr_t)b_q | (uintptr_t)b_sf | (uintptr_t)out) & 15)
+    return fail(763, "gemm: operands must be 16-byte aligned");
+  if (out_stride < n || out_stride % 8) return fail(764, "gemm: out_stride must be >= N and a multiple of 8");
+  CUtensorMap ta, tb;
+  int rc = make_operand_map(&ta, a_q, (uint64_t)m, (uint64_t)k / 2, 128);
+  if (rc) return cuda_fail(rc, "gemm A tensor map");
+  rc = make_operand_map(&tb, b_q, (uint64_t)n, (uint64_t)k / 2, bn);
+  if (rc) return cuda_fail(rc, "gemm B tensor map");
+  GemmParams g;
+  memset(&g, 0, sizeof(g));
+  g.n_tiles_static = (int)((m + 127) / 128);
+  g.M = (int)m;
+  g.N = (int)n;
+  g.K = (int)k;
+  g.sfa = (const uint8_t*)a_sf;
+  g.sfb = (const uint8_t*)b_sf;
+  g.out = (__nv_bfloat16*)out;
+  g.out_stride = out_stride;
+  g.dense_alpha = alpha;
+  g.status = status;
+  int dev = 0, sms = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int64_t items = (int64_t)g.n_tiles_static * (n / bn);
+  const int grid = (int)(items < sms ? items : sms);
+  return cuda_fail(launch_gemm_nvfp4(kGemmDense, bn, ta, tb, g, grid, (cudaStream_t)stream), "gemm");
+}
+
+int64_t b200moe_workspace_bytes(const b200moe_config* cfg) {
+  if (check_cfg(cfg)) return -1;
+  return make_plan(*cfg).total;
+}
+
+int b200moe_create(const b200moe_config* cfg, b200moe_handle* out) {
+  if (!out) return fail(717, "create: null output handle");
+  *out = nullptr;
+  int rc = check_cfg(cfg);
+  if (rc) return rc;
+  const Plan p = make_plan(*cfg);
+  b200moe_layer* h = new b200moe_layer();
+  memset(h, 0, sizeof(*h));
+  h->cfg = *cfg;
+  h->etot = cfg->num_experts + cfg->num_shared_experts;
+  h->kk = cfg->top_k + cfg->num_shared_experts;
+  h->row_capacity = p.row_capacity;
+  h->tile_capacity = p.tile_capacity;
+  h->bn = cfg->tile_n ? cfg->tile_n : 128;
+  if ((2 * cfg->intermediate) % h->bn || cfg->hidden % h->bn) {
+    delete h;
+    return fail(718, "create: tile_n=%d does not divide 2*intermediate and hidden", h->bn);
+  }
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e == cudaSuccess) e = cudaDeviceGetAttribute(&h->sm_count, cudaDevAttrMultiProcessorCount, dev);
+  if (e == cudaSuccess) e = cudaMalloc(&h->base, (size_t)p.total);
+  if (e != cudaSuccess) {
+    delete h;
+    return cuda_fail((int)e, "create: workspace allocation");
+  }
+  h->bytes = p.total;
+  uint8_t* b = (uint8_t*)h->base;
+  h->rm.block_hist = (int32_t*)(b + p.off_block_hist);
+  h->rm.counts = (int32_t*)(b + p.off_counts);
+  h->rm.seg_start = (int32_t*)(b + p.off_seg);
+  h->rm.tile_expert = (int32_t*)(b + p.off_texp);
+  h->rm.tile_row0 = (int32_t*)(b + p.off_trow0);
+  h->rm.tile_rows = (int32_t*)(b + p.off_trows);
+  h->rm.totals = (int32_t*)(b + p.off_totals);
+  h->rm.row_of = (int32_t*)(b + p.off_row_of);
+  h->rm.tok_of_row = (int32_t*)(b + p.off_tok);
+  h->rm.weight_of_row = (float*)(b + p.off_w);
+  h->rm.row_capacity = p.row_capacity;
+  h->a_q = b + p.off_aq;
+  h->a_sf = b + p.off_asf;
+  h->act_q = b + p.off_actq;
+  h->act_sf = b + p.off_actsf;
+  h->rout = (__nv_bfloat16*)(b + p.off_rout);
+  h->status = (int32_t*)(b + p.off_status);
+  e = cudaMemset(h->base, 0, (size_t)p.off_aq);   // index tables and status start at zero
+  if (e == cudaSuccess) e = cudaMemset(h->status, 0, 16);
+  if (e != cudaSuccess) {
+    cudaFree(h->base);
+    delete h;
+    return cuda_fail((int)e, "create: workspace clear");
+  }
+  rc = make_operand_map(&h->tm_a1, h->a_q, (uint64_t)p.row_capacity, cfg->hidden / 2, 128);
+  if (!rc) rc = make_operand_map(&h->tm_a2, h->act_q, (uint64_t)p.row_capacity, cfg->intermediate / 2, 128);
+  if (rc) {
+    cudaFree(h->base);
+    delete h;
+    return cuda_fail(rc, "create: activation tensor maps");
+  }
+  *out = h;
+  return 0;
+}
+
+int b200moe_destroy(b200moe_handle h) {
+  if (!h) return 0;
+  cudaError_t e = cudaFree(h->base);
+  delete h;
+  return cuda_fail((int)e, "destroy");
+}
+
+int b200moe_workspace(b200moe_handle h, b200moe_workspace_view* v) {
+  if (!h || !v) return fail(719, "workspace: null argument");
+  v->counts = h->rm.counts;
+  v->seg_start = h->rm.seg_start;
+  v->tile_expert = h->rm.tile_expert;
+  v->tile_row0 = h->rm.tile_row0;
+  v->tile_rows = h->rm.tile_rows;
+  v->totals = h->rm.totals;
+  v->row_of = h->rm.row_of;
+  v->tok_of_row = h->rm.tok_of_row;
+  v->weight_of_row = h->rm.weight_of_row;
+  v->a_q = h->a_q;
+  v->a_sf = h->a_sf;
+  v->act_q = h->act_q;
+  v->act_sf = h->act_sf;
+  v->rout = (uint16_t*)h->rout;
+  v->row_capacity = h->row_capacity;
+  v->tile_capacity = h->tile_capacity;
+  return 0;
+}
+
+int b200moe_route_map(b200moe_handle h, const int32_t* ids, const float* weights, int32_t T, int32_t offset, void* stream) {
+  if (!h) return fail(720, "route_map: null handle");
+  if (T < 0 || T > h->cfg.max_tokens) return fail(722, "route_map: num_tokens=%d outside 0..max_tokens=%d", T, h->cfg.max_tokens);
+  if (T && h->cfg.top_k > 0 && !ids) return fail(723, "route_map: topk_ids is null");
+  return cuda_fail(launch_route_map(ids, weights, T, h->cfg.top_k, h->cfg.num_shared_experts, h->cfg.num_experts, offset, h->rm,
+                                    (cudaStream_t)stream),
+                   "route map");
+}
+
+int b200moe_run(b200moe_handle h, const b200moe_args* args, void* stream) {
+  int rc = check_args(h, args);
+  if (rc) return rc;
+  return run_impl(h, args, (cudaStream_t)stream, nullptr);
+}
+
+int b200moe_run_profiled(b200moe_handle h, const b200moe_args* args, void* stream, float* stage_ms) {
+  int rc = check_args(h, args);
+  if (rc) return rc;
+  if (!stage_ms) return fail(732, "run_profiled: stage_ms is null");
+  cudaEvent_t ev[6];
+  for (int i = 0; i < 6; ++i) cudaEventCreate(&ev[i]);
+  for (int i = 0; i < 5; ++i) stage_ms[i] = 0.f;
+  rc = run_impl(h, args, (cudaStream_t)stream, ev);
+  if (!rc && args->num_tokens > 0) {
+    cudaError_t e = cudaEventSynchronize(ev[5]);
+    if (e != cudaSuccess) rc = cuda_fail((int)e, "run_profiled: synchronize");
+    else
+      for (int i = 0; i < 5; ++i) cudaEventElapsedTime(&stage_ms[i], ev[i], ev[i + 1]);
+  }
+  for (int i = 0; i < 6; ++i) cudaEventDestroy(ev[i]);
+  return rc;
+}
+
+int b200moe_status(b200moe_handle h, void* stream, int32_t* code) {
+  if (!h || !code) return fail(719, "status: null argument");
+  cudaError_t e = cudaMemcpyAsync(code, h->status, sizeof(int32_t), cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
+  return cuda_fail((int)e, "status");
+}
+
+}  // extern "C"

@@ -1,0 +1,53 @@
+// Routing-weighted combine: out[t, h] = bf16( sum_k fp32(rout[row_of[t, k], h]) * weight[t, k] ), slots in
+// ascending k, tokens without any valid route produce zeros, every output element is written.
+// Follows reference.py:91-92 of moe/nvfp4_fused_moe/problem (per-route bf16 rounding happens before the
+// weight, the sum is fp32, one final bf16 rounding); same role as the candidate's k_finalize
+// (candidate/nvfp4_moe.cu:1464). HBM-bound: reads K rows of H bf16 per token, writes one.
+#include "kernels.cuh"
+#include "ptx.cuh"
+
+namespace b200 {
+
+__global__ void __launch_bounds__(128) k_finalize(const __nv_bfloat16* __restrict__ rout, const int32_t* __restrict__ row_of,
+                                                  const float* __restrict__ weight_of_row, int64_t T, int KK, int H,
+                                                  __nv_bfloat16* __restrict__ out, int64_t out_stride) {
+  const int vecs = H >> 3;
+  for (int64_t t = blockIdx.x; t < T; t += gridDim.x) {
+    for (int v = threadIdx.x; v < vecs; v += blockDim.x) {
+      float acc[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+      for (int k = 0; k < KK; ++k) {
+        const int row = row_of[t * KK + k];
+        if (row < 0) continue;
+        const float w = weight_of_row[row];
+        const uint4 raw = __ldg(reinterpret_cast<const uint4*>(rout + (size_t)row * H) + v);
+        const uint32_t* u = reinterpret_cast<const uint32_t*>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          acc[2 * i] = fmaf(__uint_as_float(u[i] << 16), w, acc[2 * i]);
+          acc[2 * i + 1] = fmaf(__uint_as_float(u[i] & 0xFFFF0000u), w, acc[2 * i + 1]);
+        }
+      }
+      uint4 o;
+      uint32_t* ou = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const __nv_bfloat162 p = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+        ou[i] = *reinterpret_cast<const uint32_t*>(&p);
+      }
+      *(reinterpret_cast<uint4*>(out + t * out_stride) + v) = o;
+    }
+  }
+}
+
+int launch_finalize(const void* rout, const int32_t* row_of, const float* weight_of_row, int64_t T, int KK, int H, void* out,
+                    int64_t out_stride, cudaStream_t st) {
+  if (T == 0) return 0;
+  int64_t blocks = T < 148 * 16 ? T : 148 * 16;
+  k_finalize<<<(unsigned)blocks, 128, 0, st>>>((const __nv_bfloat16*)rout, row_of, weight_of_row, T, KK, H, (__nv_bfloat16*)out,
+                                              out_stride);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace b200

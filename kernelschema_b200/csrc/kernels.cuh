@@ -1,0 +1,69 @@
+// Internal launch interface shared by the kernel files and the C-ABI layer (api.cu).
+#pragma once
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace b200 {
+
+enum { kGemmDense = 0, kGemmFc1 = 1, kGemmFc2 = 2 };
+
+// Device buffers produced by the route-map build.
+struct RouteMapBuffers {
+  int32_t* block_hist;     // [nblk, E'] scratch
+  int32_t* counts;         // [E']
+  int32_t* seg_start;      // [E' + 1], multiples of 128
+  int32_t* tile_expert;    // [tile_capacity]
+  int32_t* tile_row0;      // [tile_capacity]
+  int32_t* tile_rows;      // [tile_capacity] valid rows of the tile (1..128)
+  int32_t* totals;         // {n_tiles, rows in use (multiple of 128), valid routes}
+  int32_t* row_of;         // [T, K'] permuted row of a route, -1 when invalid
+  int32_t* tok_of_row;     // [row_capacity] token of a permuted row, -1 for padding
+  float* weight_of_row;    // [row_capacity] routing weight of a permuted row
+  int64_t row_capacity;
+};
+
+struct GemmParams {
+  const int32_t* tile_expert;   // null: dense (expert 0, m-tiles are consecutive 128-row blocks)
+  const int32_t* tile_row0;
+  const int32_t* tile_rows;
+  const int32_t* n_tiles_ptr;   // device count of m-tiles, or null -> n_tiles_static
+  int n_tiles_static;
+  int M;                        // rows of A (dense mode only)
+  int N;                        // weight rows per expert (2I for FC1, H for FC2)
+  int K;                        // reduction length in FP4 elements
+  const uint8_t* sfa;           // A scales, 128x4 tiles [rows/128][K/64][512]
+  const uint8_t* sfb;           // B scales, 128x4 tiles [E*N/128][K/64][512]
+  uint8_t* act_q;               // FC1 out: packed activations [rows, I/2]
+  uint8_t* act_sf;              // FC1 out: activation scales, 128x4 tiles [rows/128][I/64][512]
+  __nv_bfloat16* out;           // FC2 / dense out
+  int64_t out_stride;           // elements between output rows
+  const float* scale_up;        // per expert multipliers of the FC1 accumulators (null = 1)
+  const float* scale_gate;
+  const float* alpha;           // per expert activation parameters (null = 1 / 0 / no clamp)
+  const float* beta;
+  const float* limit;
+  int act_type;                 // 3 = SwiGLU form gate*sigmoid(alpha*gate)*(up+beta); 10 = SiTU
+  const float* out_scale;       // per expert multiplier of the FC2 accumulator (null = 1)
+  float dense_alpha;
+  int32_t* status;              // device word; first non-zero code sticks (bounded waits report here)
+};
+
+int launch_quantize_nvfp4(const void* x, int64_t rows, int64_t cols, int64_t row_stride, float gs, void* payload, void* scales,
+                          int sf_layout, cudaStream_t st);
+int launch_sf_to_tiles(const void* src, int64_t rows, int64_t blocks_per_row, void* dst, cudaStream_t st);
+int launch_route_topk(const float* logits, const float* bias, int64_t T, int E, int K, int32_t* ids, float* weights,
+                      cudaStream_t st);
+int launch_router_logits(const void* x, const void* w, int64_t T, int H, int E, float* logits, cudaStream_t st);
+int launch_route_map(const int32_t* ids, const float* scores, int64_t T, int K, int S, int E, int expert_offset, RouteMapBuffers b,
+                     cudaStream_t st);
+int launch_gather_rows(const void* hid_q, const void* hid_sf, int hid_sf_tiled, const int32_t* tok_of_row, const int32_t* totals,
+                       int H, int64_t row_capacity, void* a_q, void* a_sf, cudaStream_t st);
+int launch_finalize(const void* rout, const int32_t* row_of, const float* weight_of_row, int64_t T, int KK, int H, void* out,
+                    int64_t out_stride, cudaStream_t st);
+int make_operand_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_rows);
+int launch_gemm_nvfp4(int mode, int bn, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid,
+                      cudaStream_t st);
+
+}  // namespace b200

@@ -1,0 +1,187 @@
+// Expert-permutation index build: per-expert counts, 128-row-aligned segment starts, the m-tile list,
+// and the route <-> permuted-row maps.
+//
+// Same outputs as the reference candidate's k_count / k_scan_tiles / k_scatter_agg chain
+// (moe/nvfp4_fused_moe/candidate/nvfp4_moe.cu:582, :750, :700; specified in
+// schema_wiki/.../nvfp4_fused_moe/root.yaml:172-197), with one tightening: the position of a route
+// inside its expert segment is its rank in ascending flat index t*K+k (the reference leaves that
+// order arbitrary), so every integer output is reproducible and can be compared bit for bit.
+// No atomics: three passes (block histograms, scan, stable scatter).
+#include "kernels.cuh"
+#include "ptx.cuh"
+
+namespace b200 {
+
+constexpr int kRouteChunk = 2048;        // routes per block: 8 warps x 8 steps x 32 lanes
+constexpr int kRouteWarps = 8;
+
+struct RouteView {
+  const int32_t* ids;
+  int64_t T;
+  int K;            // routed slots per token
+  int S;            // shared experts: extra always-selected slots
+  int E;            // local routed experts
+  int expert_offset;
+};
+
+DEV int route_expert(const RouteView& r, int64_t f, int64_t total) {
+  if (f >= total) return -1;
+  const int kk = r.K + r.S;
+  const int64_t t = f / kk;
+  const int k = (int)(f - t * kk);
+  if (k >= r.K) return r.E + (k - r.K);
+  const int e = r.ids[t * r.K + k] - r.expert_offset;
+  return (e >= 0 && e < r.E) ? e : -1;
+}
+
+// Per-warp histograms of this block's chunk into hist[warp][e]; each warp owns its row, so no atomics.
+DEV void chunk_histogram(const RouteView& r, int64_t total, int etot, int* hist) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int i = threadIdx.x; i < kRouteWarps * etot; i += blockDim.x) hist[i] = 0;
+  __syncthreads();
+  const int64_t base = (int64_t)blockIdx.x * kRouteChunk + warp * (kRouteChunk / kRouteWarps);
+  for (int step = 0; step < kRouteChunk / kRouteWarps / 32; ++step) {
+    const int e = route_expert(r, base + step * 32 + lane, total);
+    const unsigned m = __match_any_sync(0xFFFFFFFFu, e);
+    if (e >= 0 && lane == (__ffs(m) - 1)) hist[warp * etot + e] += __popc(m);
+    __syncwarp();
+  }
+  __syncthreads();
+}
+
+__global__ void __launch_bounds__(256) k_route_hist(RouteView r, int etot, int32_t* __restrict__ block_hist) {
+  extern __shared__ int hist[];
+  const int64_t total = r.T * (r.K + r.S);
+  chunk_histogram(r, total, etot, hist);
+  for (int e = threadIdx.x; e < etot; e += blockDim.x) {
+    int s = 0;
+#pragma unroll
+    for (int w = 0; w < kRouteWarps; ++w) s += hist[w * etot + e];
+    block_hist[(int64_t)blockIdx.x * etot + e] = s;
+  }
+}
+
+// One block. Turns block_hist into exclusive per-expert prefixes over blocks, then scans experts:
+// seg_start (segments padded to 128 rows), the m-tile list, and the totals {n_tiles, r_pad, r_valid}.
+__global__ void __launch_bounds__(1024) k_route_scan(int etot, int nblk, int32_t* __restrict__ block_hist,
+                                                     int32_t* __restrict__ counts, int32_t* __restrict__ seg_start,
+                                                     int32_t* __restrict__ tile_expert, int32_t* __restrict__ tile_row0,
+                                                     int32_t* __restrict__ tile_rows, int32_t* __restrict__ totals) {
+  __shared__ int warp_pad[32], warp_tiles[32], warp_cnt[32];
+  __shared__ int carry[3];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (threadIdx.x < 3) carry[threadIdx.x] = 0;
+  __syncthreads();
+  for (int e0 = 0; e0 < etot; e0 += blockDim.x) {
+    const int e = e0 + threadIdx.x;
+    int cnt = 0;
+    if (e < etot) {
+      for (int b = 0; b < nblk; ++b) {
+        const int v = block_hist[(int64_t)b * etot + e];
+        block_hist[(int64_t)b * etot + e] = cnt;
+        cnt += v;
+      }
+      counts[e] = cnt;
+    }
+    const int ntile = (cnt + 127) >> 7;
+    const int pad = ntile << 7;
+    int ip = pad, it = ntile, ic = cnt;        // inclusive warp scans
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const int a = __shfl_up_sync(0xFFFFFFFFu, ip, off);
+      const int b = __shfl_up_sync(0xFFFFFFFFu, it, off);
+      const int c = __shfl_up_sync(0xFFFFFFFFu, ic, off);
+      if (lane >= off) { ip += a; it += b; ic += c; }
+    }
+    if (lane == 31) { warp_pad[warp] = ip; warp_tiles[warp] = it; warp_cnt[warp] = ic; }
+    __syncthreads();
+    int bp = carry[0], bt = carry[1];
+    for (int w = 0; w < warp; ++w) { bp += warp_pad[w]; bt += warp_tiles[w]; }
+    const int start = bp + ip - pad;
+    const int tile0 = bt + it - ntile;
+    if (e < etot) {
+      seg_start[e] = start;
+      for (int j = 0; j < ntile; ++j) {
+        tile_expert[tile0 + j] = e;
+        tile_row0[tile0 + j] = start + (j << 7);
+        tile_rows[tile0 + j] = min(128, cnt - (j << 7));
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x == blockDim.x - 1) {
+      int tc = 0;
+      for (int w = 0; w < 32; ++w) tc += warp_cnt[w];
+      carry[0] = bp + ip;
+      carry[1] = bt + it;
+      carry[2] += tc;
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    seg_start[etot] = carry[0];
+    totals[0] = carry[1];   // number of 128-row tiles
+    totals[1] = carry[0];   // rows of the permuted buffer in use (multiple of 128)
+    totals[2] = carry[2];   // valid routes
+  }
+}
+
+__global__ void __launch_bounds__(256) k_route_scatter(RouteView r, const float* __restrict__ scores, int etot,
+                                                       const int32_t* __restrict__ block_base, const int32_t* __restrict__ seg_start,
+                                                       int32_t* __restrict__ row_of, int32_t* __restrict__ tok_of_row,
+                                                       float* __restrict__ weight_of_row) {
+  extern __shared__ int hist[];
+  const int kk = r.K + r.S;
+  const int64_t total = r.T * kk;
+  chunk_histogram(r, total, etot, hist);
+  for (int e = threadIdx.x; e < etot; e += blockDim.x) {
+    int run = seg_start[e] + block_base[(int64_t)blockIdx.x * etot + e];
+#pragma unroll
+    for (int w = 0; w < kRouteWarps; ++w) {
+      const int c = hist[w * etot + e];
+      hist[w * etot + e] = run;
+      run += c;
+    }
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t base = (int64_t)blockIdx.x * kRouteChunk + warp * (kRouteChunk / kRouteWarps);
+  for (int step = 0; step < kRouteChunk / kRouteWarps / 32; ++step) {
+    const int64_t f = base + step * 32 + lane;
+    const int e = route_expert(r, f, total);
+    const unsigned m = __match_any_sync(0xFFFFFFFFu, e);
+    int pos = -1;
+    if (e >= 0) pos = hist[warp * etot + e] + __popc(m & ((1u << lane) - 1u));
+    __syncwarp();
+    if (e >= 0 && lane == (__ffs(m) - 1)) hist[warp * etot + e] += __popc(m);
+    __syncwarp();
+    if (f < total) {
+      row_of[f] = pos;
+      if (pos >= 0) {
+        const int64_t t = f / kk;
+        const int k = (int)(f - t * kk);
+        tok_of_row[pos] = (int32_t)t;
+        weight_of_row[pos] = (k < r.K) ? (scores ? scores[t * r.K + k] : 1.0f) : 1.0f;
+      }
+    }
+  }
+}
+
+int launch_route_map(const int32_t* ids, const float* scores, int64_t T, int K, int S, int E, int expert_offset, RouteMapBuffers b,
+                     cudaStream_t st) {
+  const int etot = E + S;
+  const int64_t total = T * (K + S);
+  const int nblk = (int)((total + kRouteChunk - 1) / kRouteChunk);
+  RouteView r{ids, T, K, S, E, expert_offset};
+  cudaError_t err = cudaMemsetAsync(b.tok_of_row, 0xFF, sizeof(int32_t) * (size_t)b.row_capacity, st);
+  if (err != cudaSuccess) return (int)err;
+  const size_t smem = sizeof(int) * kRouteWarps * (size_t)etot;
+  if (nblk > 0) k_route_hist<<<nblk, 256, smem, st>>>(r, etot, b.block_hist);
+  k_route_scan<<<1, 1024, 0, st>>>(etot, nblk, b.block_hist, b.counts, b.seg_start, b.tile_expert, b.tile_row0, b.tile_rows,
+                                   b.totals);
+  if (nblk > 0)
+    k_route_scatter<<<nblk, 256, smem, st>>>(r, scores, etot, b.block_hist, b.seg_start, b.row_of, b.tok_of_row,
+                                            b.weight_of_row);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace b200

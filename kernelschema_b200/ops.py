@@ -1,0 +1,203 @@
+"""Torch-facing wrappers of the C ABI. Torch supplies device memory and the current stream only; every
+computation runs in libb200moe.so and a missing library or a non-CUDA tensor is an error, never a fallback."""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _lib
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _need_cuda(*tensors) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise ValueError("libb200moe operates on CUDA tensors only")
+
+
+def _ptr(t) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def nvfp4_quantize(x: torch.Tensor, global_scale: float = 1.0, tiled_scales: bool = False):
+    """bf16 [rows, cols] -> (payload uint8 [rows, cols/2], scales float8_e4m3fn).
+
+    Same bytes as the reference generator's ``quantize(value, 16)`` (problem/input.py:53-71) and, with a
+    global scale, as the dense GEMM problem's ``quantize`` (bf16_nvfp4_gemm/problem/input.py:40-64).
+    ``tiled_scales`` returns the 128x4-tiled layout (uint8, [ceil(rows/128), cols/64, 32, 16]) instead of
+    row-major [rows, cols/16].
+    """
+    _need_cuda(x)
+    if x.dtype != torch.bfloat16 or x.dim() != 2:
+        raise ValueError("nvfp4_quantize expects a 2-D bfloat16 tensor")
+    if x.stride(1) != 1:
+        x = x.contiguous()
+    rows, cols = x.shape
+    payload = torch.empty((rows, cols // 2), dtype=torch.uint8, device=x.device)
+    if tiled_scales:
+        scales = torch.zeros(((rows + 127) // 128, cols // 64, 32, 16), dtype=torch.uint8, device=x.device)
+    else:
+        scales = torch.empty((rows, cols // 16), dtype=torch.uint8, device=x.device)
+    lib = _lib.load()
+    _lib.check(lib.b200moe_quantize_nvfp4(x.data_ptr(), rows, cols, x.stride(0), float(global_scale), payload.data_ptr(),
+                                          scales.data_ptr(), _lib.SF_TILED if tiled_scales else _lib.SF_ROW_MAJOR, _stream()),
+               "b200moe_quantize_nvfp4")
+    return payload, (scales if tiled_scales else scales.view(torch.float8_e4m3fn))
+
+
+def scales_to_tiles(scales: torch.Tensor) -> torch.Tensor:
+    """Row-major scale bytes [rows, cols/16] -> 128x4 tiles [ceil(rows/128), cols/64, 32, 16] (uint8)."""
+    _need_cuda(scales)
+    s = scales.contiguous().view(torch.uint8)
+    rows, blocks = s.shape
+    out = torch.empty(((rows + 127) // 128, blocks // 4, 32, 16), dtype=torch.uint8, device=s.device)
+    _lib.check(_lib.load().b200moe_scales_to_tiles(s.data_ptr(), rows, blocks * 16, out.data_ptr(), _stream()),
+               "b200moe_scales_to_tiles")
+    return out
+
+
+def route_topk(logits: torch.Tensor, top_k: int, bias: torch.Tensor | None = None):
+    """fp32 logits [T, E] -> (ids int32 [T, K], weights fp32 [T, K]); problem/input.py:35-36."""
+    _need_cuda(logits, bias)
+    lg = logits.contiguous().float()
+    t, e = lg.shape
+    ids = torch.empty((t, top_k), dtype=torch.int32, device=lg.device)
+    w = torch.empty((t, top_k), dtype=torch.float32, device=lg.device)
+    b = None if bias is None else bias.contiguous().float()
+    _lib.check(_lib.load().b200moe_route_topk(lg.data_ptr(), _ptr(b), t, e, top_k, ids.data_ptr(), w.data_ptr(), _stream()),
+               "b200moe_route_topk")
+    return ids, w
+
+
+def router_logits(x: torch.Tensor, gate_weight: torch.Tensor) -> torch.Tensor:
+    """bf16 x [T, H] times bf16 gate [E, H]^T -> fp32 logits [T, E]."""
+    _need_cuda(x, gate_weight)
+    x = x.contiguous()
+    g = gate_weight.contiguous()
+    out = torch.empty((x.shape[0], g.shape[0]), dtype=torch.float32, device=x.device)
+    _lib.check(_lib.load().b200moe_router_logits(x.data_ptr(), g.data_ptr(), x.shape[0], x.shape[1], g.shape[0], out.data_ptr(),
+                                                 _stream()), "b200moe_router_logits")
+    return out
+
+
+def mm_nvfp4(a_q, a_sf_tiled, b_q, b_sf_tiled, alpha: float = 1.0, out: torch.Tensor | None = None, tile_n: int = 0,
+             status: torch.Tensor | None = None):
+    """out[M, N] = bf16(alpha * A @ B^T) with both operands NVFP4 (payload uint8 [rows, K/2], tiled scales)."""
+    _need_cuda(a_q, a_sf_tiled, b_q, b_sf_tiled, out)
+    m, k2 = a_q.shape
+    n = b_q.shape[0]
+    if out is None:
+        out = torch.empty((m, n), dtype=torch.bfloat16, device=a_q.device)
+    _lib.check(_lib.load().b200moe_gemm_nvfp4(a_q.data_ptr(), a_sf_tiled.data_ptr(), b_q.data_ptr(), b_sf_tiled.data_ptr(),
+                                              float(alpha), out.data_ptr(), m, n, k2 * 2, out.stride(0), tile_n, _ptr(status),
+                                              _stream()), "b200moe_gemm_nvfp4")
+    return out
+
+
+class MoELayer:
+    """One layer instance: owns the library workspace for a geometry (b200moe_create / b200moe_destroy)."""
+
+    def __init__(self, hidden: int, intermediate: int, num_experts: int, top_k: int, max_tokens: int,
+                 num_shared_experts: int = 0, tile_n: int = 0):
+        lib = _lib.load()
+        if not torch.cuda.is_available():
+            raise RuntimeError("libb200moe needs a CUDA device (sm_100a); there is no CPU path")
+        self.cfg = _lib.Config(struct_size=C.sizeof(_lib.Config), hidden=hidden, intermediate=intermediate,
+                               num_experts=num_experts, top_k=top_k, num_shared_experts=num_shared_experts,
+                               max_tokens=max_tokens, tile_n=tile_n)
+        self._h = C.c_void_p()
+        _lib.check(lib.b200moe_create(C.byref(self.cfg), C.byref(self._h)), "b200moe_create")
+        self.device = torch.cuda.current_device()
+        self._keep = None
+
+    def close(self):
+        if getattr(self, "_h", None) is not None and self._h:
+            _lib.load().b200moe_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # ------------------------------------------------------------------ building blocks
+    def _args(self, ids, weights, hidden_states, hidden_states_scale, w1, s1, w2, s2, out, *, alpha=None, beta=None, limit=None,
+              scale_up=None, scale_gate=None, scale_out=None, activation_type=3, expert_offset=0, scale_layout=2):
+        t = hidden_states.shape[0]
+        a = _lib.Args(struct_size=C.sizeof(_lib.Args), num_tokens=t, topk_ids=_ptr(ids), topk_weights=_ptr(weights),
+                      hidden_states=_ptr(hidden_states), hidden_states_scale=_ptr(hidden_states_scale),
+                      hidden_states_scale_layout=scale_layout, activation_type=activation_type, gemm1_weights=_ptr(w1),
+                      gemm1_weights_scale=_ptr(s1), gemm2_weights=_ptr(w2), gemm2_weights_scale=_ptr(s2),
+                      gemm1_alpha=_ptr(alpha), gemm1_beta=_ptr(beta), gemm1_clamp_limit=_ptr(limit),
+                      output1_scale_scalar=_ptr(scale_up), output1_scale_gate_scalar=_ptr(scale_gate),
+                      output2_scale_scalar=_ptr(scale_out), local_expert_offset=expert_offset, output=_ptr(out),
+                      output_stride=out.stride(0))
+        return a
+
+    def run(self, ids, weights, hidden_states, hidden_states_scale, w1, s1, w2, s2, out, **kw):
+        """Asynchronous forward on the current stream; writes ``out`` (bf16 [T, H]) in place."""
+        _need_cuda(hidden_states, hidden_states_scale, w1, s1, w2, s2, out)
+        a = self._args(ids, weights, hidden_states, hidden_states_scale, w1, s1, w2, s2, out, **kw)
+        _lib.check(_lib.load().b200moe_run(self._h, C.byref(a), _stream()), "b200moe_run")
+        return out
+
+    def run_profiled(self, ids, weights, hidden_states, hidden_states_scale, w1, s1, w2, s2, out, **kw):
+        a = self._args(ids, weights, hidden_states, hidden_states_scale, w1, s1, w2, s2, out, **kw)
+        ms = (C.c_float * 5)()
+        _lib.check(_lib.load().b200moe_run_profiled(self._h, C.byref(a), _stream(), ms), "b200moe_run_profiled")
+        return dict(zip(("route_map", "permute", "fc1", "fc2", "combine"), (float(v) for v in ms)))
+
+    def route_map(self, ids, weights, expert_offset: int = 0):
+        t = ids.shape[0]
+        _lib.check(_lib.load().b200moe_route_map(self._h, _ptr(ids), _ptr(weights), t, expert_offset, _stream()),
+                   "b200moe_route_map")
+
+    def status(self) -> int:
+        code = C.c_int32(0)
+        _lib.check(_lib.load().b200moe_status(self._h, _stream(), C.byref(code)), "b200moe_status")
+        return int(code.value)
+
+    def workspace(self) -> dict:
+        """Torch views (no copies) of the library-owned intermediates, for tests and the expert-parallel wrapper."""
+        v = _lib.WorkspaceView()
+        _lib.check(_lib.load().b200moe_workspace(self._h, C.byref(v)), "b200moe_workspace")
+        c = self.cfg
+        etot, kk = c.num_experts + c.num_shared_experts, c.top_k + c.num_shared_experts
+        rows, tiles = int(v.row_capacity), int(v.tile_capacity)
+
+        def view(ptr, nbytes, dtype, shape):
+            return _from_device_ptr(ptr, nbytes, dtype, shape, self.device)
+
+        return dict(
+            counts=view(v.counts, 4 * etot, torch.int32, (etot,)),
+            seg_start=view(v.seg_start, 4 * (etot + 1), torch.int32, (etot + 1,)),
+            tile_expert=view(v.tile_expert, 4 * tiles, torch.int32, (tiles,)),
+            tile_row0=view(v.tile_row0, 4 * tiles, torch.int32, (tiles,)),
+            tile_rows=view(v.tile_rows, 4 * tiles, torch.int32, (tiles,)),
+            totals=view(v.totals, 12, torch.int32, (3,)),
+            row_of=view(v.row_of, 4 * c.max_tokens * kk, torch.int32, (c.max_tokens, kk)),
+            tok_of_row=view(v.tok_of_row, 4 * rows, torch.int32, (rows,)),
+            weight_of_row=view(v.weight_of_row, 4 * rows, torch.float32, (rows,)),
+            a_q=view(v.a_q, rows * c.hidden // 2, torch.uint8, (rows, c.hidden // 2)),
+            a_sf=view(v.a_sf, rows * c.hidden // 16, torch.uint8, (rows // 128, c.hidden // 64, 32, 16)),
+            act_q=view(v.act_q, rows * c.intermediate // 2, torch.uint8, (rows, c.intermediate // 2)),
+            act_sf=view(v.act_sf, rows * c.intermediate // 16, torch.uint8, (rows // 128, c.intermediate // 64, 32, 16)),
+            rout=view(v.rout, rows * c.hidden * 2, torch.bfloat16, (rows, c.hidden)),
+            row_capacity=rows, tile_capacity=tiles)
+
+
+class _DevMem:
+    """Minimal __cuda_array_interface__ carrier so torch can alias library-owned device memory."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+
+
+def _from_device_ptr(ptr: int, nbytes: int, dtype, shape, device):
+    raw = torch.as_tensor(_DevMem(ptr, nbytes), device=f"cuda:{device}")
+    return raw.view(dtype).view(shape)

@@ -1,0 +1,97 @@
+"""Drop-in ``Model`` for the reference operator ``nvfp4_fused_moe``.
+
+Same constructor and the same keyword-only 36-argument ``forward`` as the reference's
+``problem/reference.py:94-101`` and ``candidate/solution.py:1023`` (interface recorded in the catalogue
+MANIFEST, operators/41): it writes the caller's ``output`` tensor in place and returns ``[output]``.
+Shape violations raise ``ValueError`` before any launch and a failing library call raises ``RuntimeError``,
+as the reference host does (candidate/solution.py:1112-1138, :1560-1562). The work is done by libb200moe.so
+through its C ABI; the forward is asynchronous on the current CUDA stream.
+
+Beyond the reference (which passes ones / None and never reads them): ``output1_scale_scalar``,
+``output1_scale_gate_scalar`` and ``output2_scale_scalar`` are applied as per-expert multipliers of the FC1
+up / FC1 gate / FC2 accumulators, and ``num_fused_shared_experts = S`` expects S extra experts appended to
+the weight tensors which every token visits with weight 1.
+"""
+from __future__ import annotations
+
+import torch
+
+from .ops import MoELayer
+
+
+class Model(torch.nn.Module):
+    def __init__(self):
+        super().__init__()
+        self._layers = {}
+
+    def _layer(self, hidden, intermediate, experts, top_k, shared, tokens, tune_max):
+        cap = max(int(tokens), int(tune_max or 0), 1)
+        key = (hidden, intermediate, experts, top_k, shared, torch.cuda.current_device())
+        layer = self._layers.get(key)
+        if layer is None or layer.cfg.max_tokens < tokens:
+            if layer is not None:
+                layer.close()
+            layer = MoELayer(hidden, intermediate, experts, top_k, cap, num_shared_experts=shared)
+            self._layers[key] = layer
+        return layer
+
+    def forward(self, topk_ids, routing_bias, hidden_states, hidden_states_scale, gemm1_weights, gemm1_weights_scale,
+                gemm1_bias, gemm1_alpha, gemm1_beta, gemm1_clamp_limit, gemm2_weights, gemm2_weights_scale, gemm2_bias,
+                output1_scale_scalar, output1_scale_gate_scalar, output2_scale_scalar, num_experts, top_k, n_group,
+                topk_group, intermediate_size, local_expert_offset, local_num_experts, routed_scaling_factor,
+                routing_method_type=0, do_finalize=True, enable_pdl=None, activation_type=3, per_token_scale=None,
+                output=None, tune_max_num_tokens=8192, gemm1_lora_delta=None, valid_hidden_size=None,
+                valid_intermediate_size=None, num_fused_shared_experts=None, hidden_states_scale_layout=None):
+        ids, scores = topk_ids
+        if output is None:
+            raise ValueError("output tensor is required (the operator writes in place)")
+        if not hidden_states.is_cuda:
+            raise ValueError("this operator runs on CUDA tensors only")
+        for name, val in (("routing_bias", routing_bias), ("gemm1_bias", gemm1_bias), ("gemm2_bias", gemm2_bias),
+                          ("per_token_scale", per_token_scale), ("gemm1_lora_delta", gemm1_lora_delta)):
+            if val is not None:
+                raise ValueError(f"{name} is outside the operator's generated boundary and must be None")
+        if routed_scaling_factor not in (None, 1.0):
+            raise ValueError("routed_scaling_factor must be 1.0")
+        if not do_finalize:
+            raise ValueError("do_finalize=False is not supported")
+        if hidden_states_scale_layout not in (None, 2):
+            raise ValueError("hidden_states_scale_layout must be 2 (row-major [T, H/16])")
+        t, half_h = hidden_states.shape
+        hidden = half_h * 2
+        inter = int(intermediate_size)
+        shared = int(num_fused_shared_experts or 0)
+        local = int(local_num_experts if local_num_experts is not None else num_experts)
+        if ids.shape != (t, top_k) or scores.shape != (t, top_k):
+            raise ValueError("topk_ids must be (ids[T, top_k], scores[T, top_k])")
+        if ids.dtype != torch.int32 or scores.dtype != torch.float32:
+            raise ValueError("ids must be int32 and scores float32")
+        if output.shape != (t, hidden) or output.dtype != torch.bfloat16 or output.stride(1) != 1:
+            raise ValueError("output must be bfloat16 [T, H] with unit inner stride")
+        if tuple(hidden_states_scale.shape) != (t, hidden // 16):
+            raise ValueError("hidden_states_scale must be [T, H/16]")
+        if tuple(gemm1_weights.shape) != (local + shared, 2 * inter, hidden // 2):
+            raise ValueError("gemm1_weights must be [E, 2I, H/2]")
+        if tuple(gemm2_weights.shape) != (local + shared, hidden, inter // 2):
+            raise ValueError("gemm2_weights must be [E, H, I/2]")
+        if hidden % 256 or inter % 256:
+            raise ValueError("hidden and intermediate_size must be multiples of 256")
+        if valid_hidden_size not in (None, hidden) or valid_intermediate_size not in (None, inter):
+            raise ValueError("valid_hidden_size / valid_intermediate_size must match the tensor sizes")
+        if t == 0:
+            return [output]
+
+        def f32(x):
+            return None if x is None else x.contiguous().float()
+
+        layer = self._layer(hidden, inter, local, int(top_k), shared, t, tune_max_num_tokens)
+        keep = [ids.contiguous(), scores.contiguous(), hidden_states.contiguous(),
+                hidden_states_scale.contiguous().view(torch.uint8), gemm1_weights.contiguous(),
+                gemm1_weights_scale.contiguous().view(torch.uint8), gemm2_weights.contiguous(),
+                gemm2_weights_scale.contiguous().view(torch.uint8), f32(gemm1_alpha), f32(gemm1_beta), f32(gemm1_clamp_limit),
+                f32(output1_scale_scalar), f32(output1_scale_gate_scalar), f32(output2_scale_scalar)]
+        layer.run(keep[0], keep[1], keep[2], keep[3], keep[4], keep[5], keep[6], keep[7], output, alpha=keep[8], beta=keep[9],
+                  limit=keep[10], scale_up=keep[11], scale_gate=keep[12], scale_out=keep[13],
+                  activation_type=int(activation_type), expert_offset=int(local_expert_offset or 0))
+        self._last_inputs = keep   # keep converted temporaries alive until the stream has consumed them
+        return [output]

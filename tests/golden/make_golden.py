@@ -175,13 +175,13 @@ def pack_inputs(p):
 
 def gen_moe_small():
     cases = {
-        "balanced": dict(hidden=256, intermediate=128, local_experts=4, tokens=48, topk=2),
-        "skew_clamp": dict(hidden=256, intermediate=128, local_experts=8, tokens=70, topk=4, routing="skewed",
+        "balanced": dict(hidden=256, intermediate=256, local_experts=4, tokens=48, topk=2),
+        "skew_clamp": dict(hidden=256, intermediate=256, local_experts=8, tokens=70, topk=4, routing="skewed",
                            activation_alpha=1.702, activation_beta=1.0, activation_limit=7.0),
-        "situ": dict(hidden=128, intermediate=64, local_experts=4, tokens=33, topk=2, activation="situ"),
-        "masked": dict(hidden=256, intermediate=64, local_experts=8, tokens=30, topk=8, masked_routes=True),
-        "empty": dict(hidden=128, intermediate=64, local_experts=4, tokens=16, topk=2, routing="empty"),
-        "zero": dict(hidden=128, intermediate=64, local_experts=4, tokens=16, topk=2, distribution="zero", routing="skewed"),
+        "situ": dict(hidden=256, intermediate=256, local_experts=4, tokens=33, topk=2, activation="situ"),
+        "masked": dict(hidden=256, intermediate=256, local_experts=8, tokens=30, topk=8, masked_routes=True),
+        "empty": dict(hidden=256, intermediate=256, local_experts=4, tokens=16, topk=2, routing="empty"),
+        "zero": dict(hidden=256, intermediate=256, local_experts=4, tokens=16, topk=2, distribution="zero", routing="skewed"),
         "hotspot": dict(hidden=256, intermediate=256, local_experts=8, tokens=200, topk=2, routing="hotspot"),
     }
     model = moe_ref.Model()

@@ -1,0 +1,74 @@
+"""CPU-only checks of the C-ABI boundary: the library loads, exports exactly what include/b200moe.h declares,
+and refuses bad arguments before touching a device."""
+import ctypes as C
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    from kernelschema_b200 import _lib, build
+    build.build()
+    return _lib.load()
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "b200moe.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(b200moe_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_and_binding_agree(lib):
+    from kernelschema_b200 import _lib
+    names = declared_symbols()
+    assert names == sorted(_lib.SIGNATURES), (names, sorted(_lib.SIGNATURES))
+    for n in names:
+        assert hasattr(lib, n), n
+    assert lib.b200moe_abi_version() == _lib.ABI_VERSION
+
+
+def test_struct_sizes_match_header(lib):
+    from kernelschema_b200 import _lib
+    assert C.sizeof(_lib.Config) == 16 * 4
+    assert C.sizeof(_lib.Args) == 8 + 8 * 4 + 8 + 8 * 10 + 8 + 16
+    assert C.sizeof(_lib.WorkspaceView) == 14 * 8 + 16
+
+
+def test_bad_config_is_refused_without_a_device(lib):
+    from kernelschema_b200 import _lib
+    cfg = _lib.Config(struct_size=C.sizeof(_lib.Config), hidden=100, intermediate=256, num_experts=4, top_k=2, max_tokens=8)
+    assert lib.b200moe_workspace_bytes(C.byref(cfg)) == -1
+    assert b"hidden" in lib.b200moe_last_error()
+    h = C.c_void_p()
+    assert lib.b200moe_create(C.byref(cfg), C.byref(h)) == 711 and not h
+    cfg.hidden = 256
+    cfg.struct_size = 3
+    assert lib.b200moe_create(C.byref(cfg), C.byref(h)) == 710
+    cfg.struct_size = C.sizeof(_lib.Config)
+    assert lib.b200moe_workspace_bytes(C.byref(cfg)) > 0
+
+
+def test_argument_checks_precede_launches(lib):
+    assert lib.b200moe_quantize_nvfp4(None, 4, 100, 100, 1.0, None, None, 0, None) == 740
+    assert lib.b200moe_quantize_nvfp4(None, 4, 128, 128, 1.0, None, None, 0, None) == 742
+    assert lib.b200moe_route_topk(None, None, 4, 8, 9, None, None, None) == 750
+    assert lib.b200moe_gemm_nvfp4(None, None, None, None, 1.0, None, 4, 128, 100, 128, 0, None, None) == 761
+    assert lib.b200moe_run(None, None, None) == 720
+
+
+def test_model_refuses_cpu_tensors():
+    import torch
+    import kernelschema_b200 as ks
+    m = ks.Model()
+    z = torch.zeros(2, 128, dtype=torch.uint8)
+    with pytest.raises(ValueError):
+        m(topk_ids=(torch.zeros(2, 2, dtype=torch.int32), torch.zeros(2, 2)), routing_bias=None, hidden_states=z,
+          hidden_states_scale=torch.zeros(2, 16, dtype=torch.uint8), gemm1_weights=z, gemm1_weights_scale=z, gemm1_bias=None,
+          gemm1_alpha=None, gemm1_beta=None, gemm1_clamp_limit=None, gemm2_weights=z, gemm2_weights_scale=z, gemm2_bias=None,
+          output1_scale_scalar=None, output1_scale_gate_scalar=None, output2_scale_scalar=None, num_experts=4, top_k=2,
+          n_group=None, topk_group=None, intermediate_size=256, local_expert_offset=0, local_num_experts=4,
+          routed_scaling_factor=1.0, output=torch.zeros(2, 256, dtype=torch.bfloat16))

@@ -1,0 +1,139 @@
+"""GPU parity of the front-end kernels (quantiser, router, route map) through the C ABI: bit-exact."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import load_golden
+from oracle import nvfp4_oracle as o
+
+pytestmark = pytest.mark.gpu
+
+
+def _bf16_dev(bits):
+    return torch.from_numpy(bits.view(np.int16)).cuda().view(torch.bfloat16)
+
+
+def test_quantize_golden_bytes():
+    import kernelschema_b200 as ks
+    g = load_golden("quantize")
+    for xk, pk, sk in (("x", "payload", "scale"), ("special", "special_payload", "special_scale"),
+                       ("ties", "ties_payload", "ties_scale")):
+        q, s = ks.nvfp4_quantize(_bf16_dev(g[xk]))
+        assert np.array_equal(q.cpu().numpy(), g[pk]), xk
+        assert np.array_equal(s.view(torch.uint8).cpu().numpy(), g[sk]), xk
+    q, s = ks.nvfp4_quantize(_bf16_dev(g["x"]), float(g["global_scale"]))
+    assert np.array_equal(q.cpu().numpy(), g["payload_gs"])
+    assert np.array_equal(s.view(torch.uint8).cpu().numpy(), g["scale_gs"])
+
+
+@pytest.mark.parametrize("rows,cols,scale", [(1000, 7168, 1.0), (257, 2048, 37.0), (64, 64, 1e-3), (0, 256, 1.0)])
+def test_quantize_matches_oracle(rows, cols, scale):
+    import kernelschema_b200 as ks
+    gen = torch.Generator(device="cpu").manual_seed(rows + cols)
+    x = (torch.randn(rows, cols, generator=gen) * scale).to(torch.bfloat16)
+    q, s = ks.nvfp4_quantize(x.cuda())
+    oq, os_ = o.quantize(x.float().numpy())
+    assert np.array_equal(q.cpu().numpy(), oq)
+    assert np.array_equal(s.view(torch.uint8).cpu().numpy(), os_)
+    if rows:
+        gs = float(x.float().abs().max() / (6 * 448))
+        q, s = ks.nvfp4_quantize(x.cuda(), gs)
+        oq, os_ = o.quantize(x.float().numpy(), 16, gs)
+        assert np.array_equal(q.cpu().numpy(), oq)
+        assert np.array_equal(s.view(torch.uint8).cpu().numpy(), os_)
+        # tiled scale layout = block_scales() of the row-major bytes
+        q2, st = ks.nvfp4_quantize(x.cuda(), 1.0, tiled_scales=True)
+        ref_t = o.block_scales(o.quantize(x.float().numpy())[1][None])[0]
+        assert np.array_equal(st.cpu().numpy(), ref_t)
+        assert np.array_equal(ks.scales_to_tiles(ks.nvfp4_quantize(x.cuda())[1]).cpu().numpy(), ref_t)
+
+
+def test_quantize_strided_rows():
+    import kernelschema_b200 as ks
+    x = torch.randn(50, 512, device="cuda").to(torch.bfloat16)
+    view = x[:, :256]
+    q, s = ks.nvfp4_quantize(view)
+    oq, os_ = o.quantize(view.float().cpu().numpy())
+    assert np.array_equal(q.cpu().numpy(), oq) and np.array_equal(s.view(torch.uint8).cpu().numpy(), os_)
+
+
+def test_router_golden():
+    import kernelschema_b200 as ks
+    g = load_golden("routes")
+    for i in range(int(g["n"])):
+        t, e, k, empty, masked = g[f"meta{i}"]
+        lg = g[f"logits{i}"]
+        ids, w = ks.route_topk(torch.from_numpy(lg).cuda(), int(k))
+        ids, w = ids.cpu().numpy(), w.cpu().numpy()
+        oi, ow = o.route_topk(lg, int(k))
+        assert np.array_equal(ids, oi), i
+        ulp = np.abs(w.view(np.int32).astype(np.int64) - ow.view(np.int32).astype(np.int64))
+        assert ulp.max() <= 1, (i, ulp.max())          # against the correctly rounded oracle
+        ids, w = o.apply_route_masks(ids, w, empty=bool(empty), masked_routes=bool(masked))
+        assert np.array_equal(ids, g[f"ids{i}"]), i     # against the reference
+        ulp = np.abs(w.view(np.int32).astype(np.int64) - g[f"w{i}"].view(np.int32).astype(np.int64))
+        assert ulp.max() <= 4, (i, ulp.max())           # torch's fp32 softmax
+
+
+@pytest.mark.parametrize("t,e,k", [(1, 8, 2), (333, 256, 8), (4096, 128, 8), (100, 1024, 32), (7, 5, 5)])
+def test_router_random_with_bias_and_ties(t, e, k):
+    import kernelschema_b200 as ks
+    rng = np.random.default_rng(t + e)
+    lg = rng.standard_normal((t, e), dtype=np.float32)
+    lg[::5] = np.round(lg[::5] * 2) / 2            # many exact ties: lowest index must win
+    bias = rng.standard_normal(e).astype(np.float32)
+    ids, w = ks.route_topk(torch.from_numpy(lg).cuda(), k, torch.from_numpy(bias).cuda())
+    oi, ow = o.route_topk(lg, k, bias)
+    assert np.array_equal(ids.cpu().numpy(), oi)
+    ulp = np.abs(w.cpu().numpy().view(np.int32).astype(np.int64) - ow.view(np.int32).astype(np.int64))
+    assert ulp.max() <= 1
+
+
+def test_router_logits():
+    import kernelschema_b200 as ks
+    x = torch.randn(300, 2048).to(torch.bfloat16)
+    w = (torch.randn(130, 2048) * 0.02).to(torch.bfloat16)
+    got = ks.router_logits(x.cuda(), w.cuda()).cpu().numpy()
+    ref = o.router_logits(x.float().numpy(), w.float().numpy())
+    assert np.abs(got - ref).max() <= 1e-4 * np.abs(ref).max() + 1e-6    # fp32 accumulation vs fp64
+
+
+@pytest.mark.parametrize("t,k,e,shared,offset", [(1, 8, 128, 0, 0), (300, 4, 8, 0, 0), (4096, 8, 256, 1, 0),
+                                                 (1000, 8, 32, 0, 64), (50, 2, 4, 2, 0), (2049, 1, 3, 0, 0)])
+def test_route_map_matches_oracle(t, k, e, shared, offset):
+    import kernelschema_b200 as ks
+    rng = np.random.default_rng(t * 7 + e)
+    span = e * 4 if offset else e
+    ids = np.stack([rng.permutation(span)[:k] for _ in range(t)]).astype(np.int32)
+    ids[rng.random(ids.shape) < 0.1] = -1
+    w = rng.random(ids.shape, dtype=np.float32)
+    layer = ks.MoELayer(256, 256, e, k, t, num_shared_experts=shared)
+    layer.route_map(torch.from_numpy(ids).cuda(), torch.from_numpy(w).cuda(), offset)
+    torch.cuda.synchronize()
+    ws = layer.workspace()
+    m = o.route_map(ids, e, 128, expert_offset=offset, shared_experts=shared)
+    n_tiles, rows, valid = (int(v) for v in ws["totals"].cpu())
+    assert n_tiles == len(m["tile_expert"]) and rows == m["seg_start"][-1] and valid == (m["row_of"] >= 0).sum()
+    assert np.array_equal(ws["counts"].cpu().numpy(), m["counts"])
+    assert np.array_equal(ws["seg_start"].cpu().numpy(), m["seg_start"])
+    for name in ("tile_expert", "tile_row0", "tile_rows"):
+        assert np.array_equal(ws[name][:n_tiles].cpu().numpy(), m[name]), name
+    assert np.array_equal(ws["row_of"][:t].cpu().numpy(), m["row_of"])
+    assert np.array_equal(ws["tok_of_row"][:rows].cpu().numpy(), m["tok_of_row"])
+    wr = ws["weight_of_row"][:rows].cpu().numpy()
+    full_w = np.concatenate([w, np.ones((t, shared), np.float32)], 1)
+    live = m["tok_of_row"] >= 0
+    assert np.array_equal(wr[live], full_w[m["tok_of_row"][live], m["slot_of_row"][live]])
+    layer.close()
+
+
+def test_route_map_all_invalid():
+    import kernelschema_b200 as ks
+    ids = torch.full((64, 8), -1, dtype=torch.int32, device="cuda")
+    layer = ks.MoELayer(256, 256, 16, 8, 64)
+    layer.route_map(ids, torch.zeros(64, 8, device="cuda"))
+    torch.cuda.synchronize()
+    ws = layer.workspace()
+    assert ws["totals"].cpu().tolist() == [0, 0, 0]
+    assert bool((ws["row_of"][:64] == -1).all())
+    layer.close()
