@@ -135,6 +135,22 @@ int b200moe_workspace(b200moe_handle h, b200moe_workspace_view* out);
 int b200moe_route_map(b200moe_handle h, const int32_t* topk_ids, const float* topk_weights, int32_t num_tokens,
                       int32_t local_expert_offset, void* stream);
 
+/* Route-map build for callers that must not allocate device memory, e.g. code running inside a memory pool
+ * it does not own, under a framework allocator that forbids raw cudaMalloc, or in a latency-critical section
+ * where an allocation would synchronise the device. This entry point has no counterpart in the reference.
+ * It computes exactly what b200moe_route_map computes, but into caller-provided output arrays (sizes as in
+ * b200moe_workspace_view; row_capacity >= (T*(top_k+num_shared)/128 + experts + 1) * 128) and keeps its only
+ * scratch, the per-block histograms, in a fixed array inside the library: at most 264 experts (routed + shared)
+ * and 524288 routes, larger problems are refused with code 770. It never calls cudaMalloc, cudaFree or any
+ * allocating routine. The first call on each device looks up the device address of that array (a host-side
+ * query, no allocation); make that first call outside any CUDA stream capture. All calls on one device share the
+ * array, so two calls whose kernels may overlap on the GPU (different streams) race; calls on one stream are safe.
+ * Nothing in the scratch has to start at zero: every call overwrites the part it reads. */
+int b200moe_route_map_noalloc(const int32_t* topk_ids, const float* topk_weights, int32_t num_tokens, int32_t top_k,
+                              int32_t num_shared_experts, int32_t num_experts, int32_t local_expert_offset, int32_t* counts,
+                              int32_t* seg_start, int32_t* tile_expert, int32_t* tile_row0, int32_t* tile_rows, int32_t* totals,
+                              int32_t* row_of, int32_t* tok_of_row, float* weight_of_row, int64_t row_capacity, void* stream);
+
 /* (3)+(4) Whole layer on `stream`, asynchronous: route map, permute, FC1 + activation + NVFP4 requantise,
  * FC2, routing-weighted combine into args->output. Replaces run_pipeline of NV/candidate/nvfp4_moe.cu:9078-9363
  * and matches expected() of NV/problem/reference.py:69-92 within the operator's tolerance. */

@@ -377,6 +377,38 @@ int b200moe_route_map(b200moe_handle h, const int32_t* ids, const float* weights
                    "route map");
 }
 
+int b200moe_route_map_noalloc(const int32_t* ids, const float* weights, int32_t T, int32_t top_k, int32_t num_shared,
+                              int32_t num_experts, int32_t offset, int32_t* counts, int32_t* seg_start, int32_t* tile_expert,
+                              int32_t* tile_row0, int32_t* tile_rows, int32_t* totals, int32_t* row_of, int32_t* tok_of_row,
+                              float* weight_of_row, int64_t row_capacity, void* stream) {
+  if (T < 0 || top_k < 0 || num_shared < 0 || top_k + num_shared <= 0 || num_experts < 0 || num_experts + num_shared <= 0)
+    return fail(772, "route_map_noalloc: bad sizes");
+  const int64_t routes = (int64_t)T * (top_k + num_shared);
+  const int etot = num_experts + num_shared;
+  if (etot > 264 || routes > 256LL * 2048)
+    return fail(770, "route_map_noalloc: %d experts / %lld routes exceed the built-in scratch (264 experts, 524288 routes)", etot,
+                (long long)routes);
+  if (row_capacity < (routes / 128 + etot + 1) * 128)
+    return fail(773, "route_map_noalloc: row_capacity=%lld is below (routes/128 + experts + 1) * 128", (long long)row_capacity);
+  if (!counts || !seg_start || !tile_expert || !tile_row0 || !tile_rows || !totals || !row_of || !tok_of_row || !weight_of_row ||
+      (T && top_k && !ids))
+    return fail(774, "route_map_noalloc: null pointer");
+  RouteMapBuffers b;
+  memset(&b, 0, sizeof(b));
+  b.counts = counts;
+  b.seg_start = seg_start;
+  b.tile_expert = tile_expert;
+  b.tile_row0 = tile_row0;
+  b.tile_rows = tile_rows;
+  b.totals = totals;
+  b.row_of = row_of;
+  b.tok_of_row = tok_of_row;
+  b.weight_of_row = weight_of_row;
+  b.row_capacity = row_capacity;
+  return cuda_fail(launch_route_map_static(ids, weights, T, top_k, num_shared, num_experts, offset, b, (cudaStream_t)stream),
+                   "route_map_noalloc");
+}
+
 int b200moe_run(b200moe_handle h, const b200moe_args* args, void* stream) {
   int rc = check_args(h, args);
   if (rc) return rc;

@@ -184,4 +184,37 @@ int launch_route_map(const int32_t* ids, const float* scores, int64_t T, int K, 
   return (int)cudaGetLastError();
 }
 
+// ----------------------------------------------------------------------------- allocation-free variant
+// Scratch of the route-map build (the per-block histograms) held in a file-scope device array instead of a
+// caller- or library-allocated buffer. Sized for kStaticMaxBlocks blocks of 2048 routes and kStaticMaxExperts
+// experts: 256 x 264 x 4 B = 264 KiB, resident on every GPU that loads the library until the process exits.
+constexpr int kStaticMaxBlocks = 256;      // routes <= 256 * 2048 = 524288
+constexpr int kStaticMaxExperts = 264;     // routed + shared experts
+static __device__ __align__(256) int32_t g_route_scratch[kStaticMaxBlocks * kStaticMaxExperts];
+
+constexpr int kMaxDevices = 64;
+static int32_t* g_route_scratch_ptr[kMaxDevices];   // device address of g_route_scratch, per device, filled on first use
+
+int launch_route_map_static(const int32_t* ids, const float* scores, int64_t T, int K, int S, int E, int expert_offset,
+                            RouteMapBuffers b, cudaStream_t st) {
+  const int etot = E + S;
+  const int64_t total = T * (K + S);
+  const int64_t nblk = (total + kRouteChunk - 1) / kRouteChunk;
+  if (etot > kStaticMaxExperts || nblk > kStaticMaxBlocks) return 770;
+  int dev = -1;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess) return (int)err;
+  if (dev < 0 || dev >= kMaxDevices) return 771;
+  if (!g_route_scratch_ptr[dev]) {
+    // The array's name is only a host-side handle: kernels need its device address, looked up once per device
+    // with that device current.
+    void* p = nullptr;
+    err = cudaGetSymbolAddress(&p, g_route_scratch);
+    if (err != cudaSuccess) return (int)err;
+    g_route_scratch_ptr[dev] = (int32_t*)p;
+  }
+  b.block_hist = g_route_scratch_ptr[dev];
+  return launch_route_map(ids, scores, T, K, S, E, expert_offset, b, st);
+}
+
 }  // namespace b200
