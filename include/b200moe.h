@@ -135,6 +135,13 @@ int b200moe_workspace(b200moe_handle h, b200moe_workspace_view* out);
 int b200moe_route_map(b200moe_handle h, const int32_t* topk_ids, const float* topk_weights, int32_t num_tokens,
                       int32_t local_expert_offset, void* stream);
 
+/* (4) Routing-weighted combine alone: out[t, :] = bf16( sum_s fp32(rows[row_of[t, s], :]) * weight_of_row[row_of[t, s]] ),
+ * slots in ascending s, row_of < 0 skipped, every output element written. rows: bf16 [n_rows, hidden] contiguous.
+ * Replaces k_finalize of NV/candidate/nvfp4_moe.cu:1464 (NV/problem/reference.py:91-92); the expert-parallel
+ * wrapper calls it on the rows returned by the combine all-to-all. */
+int b200moe_combine(const void* rows, const int32_t* row_of, const float* weight_of_row, int64_t num_tokens, int32_t slots,
+                    int32_t hidden, void* out, int64_t out_stride, void* stream);
+
 /* Route-map build for callers that must not allocate device memory, e.g. code running inside a memory pool
  * it does not own, under a framework allocator that forbids raw cudaMalloc, or in a latency-critical section
  * where an allocation would synchronise the device. This entry point has no counterpart in the reference.

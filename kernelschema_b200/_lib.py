@@ -56,6 +56,8 @@ SIGNATURES = {
     "b200moe_workspace_bytes": (C.c_int64, [C.POINTER(Config)]),
     "b200moe_workspace": (C.c_int, [C.c_void_p, C.POINTER(WorkspaceView)]),
     "b200moe_route_map": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p]),
+    "b200moe_combine": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_void_p, C.c_int64,
+                                  C.c_void_p]),
     "b200moe_route_map_noalloc": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32]
                                   + [C.c_void_p] * 9 + [C.c_int64, C.c_void_p]),
     "b200moe_run": (C.c_int, [C.c_void_p, C.POINTER(Args), C.c_void_p]),

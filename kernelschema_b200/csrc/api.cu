@@ -377,6 +377,16 @@ int b200moe_route_map(b200moe_handle h, const int32_t* ids, const float* weights
                    "route map");
 }
 
+int b200moe_combine(const void* rows, const int32_t* row_of, const float* weight_of_row, int64_t T, int32_t slots, int32_t hidden,
+                    void* out, int64_t out_stride, void* stream) {
+  if (T < 0 || slots <= 0 || hidden <= 0 || hidden % 8) return fail(780, "combine: hidden must be a positive multiple of 8");
+  if (T == 0) return 0;
+  if (!rows || !row_of || !weight_of_row || !out) return fail(781, "combine: null pointer");
+  if (((uintptr_t)rows | (uintptr_t)out) & 15 || out_stride < hidden || out_stride % 8)
+    return fail(782, "combine: rows/out must be 16-byte aligned, out_stride >= hidden and a multiple of 8");
+  return cuda_fail(launch_finalize(rows, row_of, weight_of_row, T, slots, hidden, out, out_stride, (cudaStream_t)stream), "combine");
+}
+
 int b200moe_route_map_noalloc(const int32_t* ids, const float* weights, int32_t T, int32_t top_k, int32_t num_shared,
                               int32_t num_experts, int32_t offset, int32_t* counts, int32_t* seg_start, int32_t* tile_expert,
                               int32_t* tile_row0, int32_t* tile_rows, int32_t* totals, int32_t* row_of, int32_t* tok_of_row,

@@ -98,6 +98,15 @@ def mm_nvfp4(a_q, a_sf_tiled, b_q, b_sf_tiled, alpha: float = 1.0, out: torch.Te
     return out
 
 
+def combine(rows: torch.Tensor, row_of: torch.Tensor, weight_of_row: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[t] = bf16(sum_s rows[row_of[t, s]] * weight_of_row[row_of[t, s]]) (reference.py:91-92), slots ascending."""
+    _need_cuda(rows, row_of, weight_of_row, out)
+    t, slots = row_of.shape
+    _lib.check(_lib.load().b200moe_combine(rows.data_ptr(), row_of.data_ptr(), weight_of_row.data_ptr(), t, slots,
+                                           rows.shape[1], out.data_ptr(), out.stride(0), _stream()), "b200moe_combine")
+    return out
+
+
 class MoELayer:
     """One layer instance: owns the library workspace for a geometry (b200moe_create / b200moe_destroy)."""
 

@@ -1,0 +1,57 @@
+"""Expert-parallel layer on 2 GPUs of one box (NCCL all-to-all + libb200moe on every rank) against the single-process
+oracle. Skipped when fewer than two GPUs are visible."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+T, H, I, E, K, S = 96, 512, 256, 8, 4, 1
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, results):
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        import sys
+        sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+        from helpers import assert_layer_parity, make_moe_case
+        from oracle import nvfp4_oracle as o
+        from kernelschema_b200.ep import ExpertParallelMoE
+        p = make_moe_case(33, T * world, H, I, E, K, shared=S, global_scales=True, routing="zipf")
+        e_local = E // world
+        mine = slice(rank * T, (rank + 1) * T)
+        own = list(range(rank * e_local, (rank + 1) * e_local)) + list(range(E, E + S))
+        dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+        ep = ExpertParallelMoE(H, I, E, K, T, num_shared_experts=S)
+        ids, scores = p["topk_ids"]
+        out = ep.forward(dev(ids[mine]), dev(scores[mine]), dev(p["hidden_states"][mine]), dev(p["hidden_states_scale"][mine]),
+                         dev(p["gemm1_weights"][own]), dev(p["gemm1_weights_scale"][own]), dev(p["gemm2_weights"][own]),
+                         dev(p["gemm2_weights_scale"][own]), scale_up=dev(p["output1_scale_scalar"][own]),
+                         scale_gate=dev(p["output1_scale_gate_scalar"][own]), scale_out=dev(p["output2_scale_scalar"][own]))
+        torch.cuda.synchronize()
+        assert ep.status() == 0
+        r = assert_layer_parity(out.float().cpu().numpy(), o.moe_expected(p)[mine], f"rank {rank}")
+        results[rank] = r["rel_l2"]
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_expert_parallel_two_gpus():
+    import torch.multiprocessing as mp
+    with mp.Manager() as mgr:
+        results = mgr.dict()
+        mp.spawn(_worker, args=(2, _free_port(), results), nprocs=2, join=True)
+        assert sorted(results.keys()) == [0, 1]
