@@ -309,6 +309,9 @@ def run_gpu(args, wl):
                                    scale_up=L["scale_fc1"], scale_gate=L["scale_fc1"], scale_out=L["scale_fc2"])
             acc = d if acc is None else {k2: acc[k2] + v for k2, v in d.items()}
         stage = {k2: v / reps for k2, v in acc.items()}
+        totals = owner.workspace()["totals"].cpu().tolist()
+        stage["m_tiles"] = totals[0]
+        stage["tile_fill"] = totals[2] / max(1, totals[0] * 128)
         pk = peaks()
         fc1_flops = flops * 2.0 / 3.0
         achieved = fc1_flops / (stage["fc1"] * 1e-3) / 1e12
@@ -351,9 +354,13 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="dsv3", choices=sorted(WORKLOADS))
+    ap.add_argument("--zipf", type=float, default=None, help="override the workload's Zipf exponent of the router bias (0 = uniform)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
-    wl = WORKLOADS[args.workload]
+    wl = dict(WORKLOADS[args.workload])
+    if args.zipf is not None:
+        wl["zipf"] = args.zipf
+        wl["label"] += f"_zipf{args.zipf:g}_override"
     if args.impl == "reference":
         run_reference(args, wl)
     else:

@@ -107,6 +107,132 @@ __global__ void __launch_bounds__(256) k_router_logits(const __nv_bfloat16* __re
   }
 }
 
+// ----------------------------------------------------------------------------- tensor-core router logits
+// Same product on the 5th-gen tensor cores: 128-token tiles, the whole gate matrix (E <= 256 rows) as the B tile,
+// K staged 64 bf16 (128 B rows, 128-byte swizzle) at a time by TMA, tcgen05.mma kind::f16 into double-buffered TMEM
+// accumulators, fp32 results stored straight from TMEM. Warp roles as in the NVFP4 GEMM.
+constexpr int kLgStages = 4;
+constexpr int kLgABytes = 128 * 128;
+constexpr int kLgBBytes = 256 * 128;
+constexpr int kLgSmem = kLgStages * (kLgABytes + kLgBBytes) + 1024 + 128;
+
+__global__ void __launch_bounds__(192, 1)
+k_router_logits_tc(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w, int T, int H, int E,
+                   int e_pad, float* __restrict__ logits, int32_t* status) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t s_a = base, s_b = s_a + kLgStages * kLgABytes, s_bar = s_b + kLgStages * kLgBBytes;
+  const uint32_t bar_full = s_bar, bar_empty = s_bar + 8 * kLgStages, bar_acc_full = bar_empty + 8 * kLgStages,
+                 bar_acc_empty = bar_acc_full + 16, s_slot = bar_acc_empty + 16;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kLgStages; ++s) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(bar_acc_full + 8 * b, 1); mbar_init(bar_acc_empty + 8 * b, 4); }
+    mbar_init_fence();
+  }
+  if (warp == 1) tmem_alloc<512>(s_slot);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  uint32_t tmem;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem) : "r"(s_slot));
+  const int n_tiles = (T + 127) >> 7;
+  const int nk = H >> 6;
+  const uint32_t stage_bytes = kLgABytes + (uint32_t)e_pad * 128;
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t g = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x)
+        for (int ks = 0; ks < nk; ++ks, ++g) {
+          const uint32_t s = g % kLgStages;
+          if (!mbar_wait(bar_empty + 8 * s, ((g / kLgStages) & 1) ^ 1)) { if (status) atomicCAS(status, 0, 111); ok = false; break; }
+          mbar_expect_tx(bar_full + 8 * s, stage_bytes);
+          tma_load_2d(s_a + s * kLgABytes, &tm_x, bar_full + 8 * s, ks * 128, tile * 128);
+          tma_load_2d(s_b + s * kLgBBytes, &tm_w, bar_full + 8 * s, ks * 128, 0);
+        }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_bf16(128, e_pad);
+      uint32_t g = 0, it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x, ++it) {
+        const uint32_t buf = it & 1;
+        if (!mbar_wait(bar_acc_empty + 8 * buf, ((it >> 1) & 1) ^ 1)) { if (status) atomicCAS(status, 0, 112); break; }
+        tc_fence_after();
+        for (int ks = 0; ks < nk; ++ks, ++g) {
+          const uint32_t s = g % kLgStages;
+          if (!mbar_wait(bar_full + 8 * s, (g / kLgStages) & 1)) { if (status) atomicCAS(status, 0, 113); ok = false; break; }
+          tc_fence_after();
+          const uint64_t a_d = make_desc_sw128(s_a + s * kLgABytes), b_d = make_desc_sw128(s_b + s * kLgBBytes);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) mma_bf16(tmem + buf * 256, a_d + 2 * q, b_d + 2 * q, idesc, (ks | q) ? 1u : 0u);
+          mma_commit(bar_empty + 8 * s);
+        }
+        if (ok) mma_commit(bar_acc_full + 8 * buf);
+      }
+    }
+  } else {
+    const int quad = warp & 3;
+    uint32_t it = 0;
+    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++it) {
+      const uint32_t buf = it & 1;
+      int okw = 1;
+      if (lane == 0) okw = mbar_wait(bar_acc_full + 8 * buf, (it >> 1) & 1) ? 1 : 0;
+      okw = __shfl_sync(0xFFFFFFFFu, okw, 0);
+      if (!okw) { if (lane == 0 && status) atomicCAS(status, 0, 114); break; }
+      tc_fence_after();
+      const int row = tile * 128 + quad * 32 + lane;
+      const uint32_t taddr = tmem + ((uint32_t)(quad * 32) << 16) + buf * 256;
+      for (int cb = 0; cb < e_pad / 32; ++cb) {
+        float v[32];
+        tmem_ld32(taddr + cb * 32, v);
+        tmem_ld_wait();
+        if (row < T) {
+          float* dst = logits + (size_t)row * E + cb * 32;
+          if (cb * 32 + 32 <= E && (E & 3) == 0) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) reinterpret_cast<float4*>(dst)[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (cb * 32 + j < E) dst[j] = v[j];
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_acc_empty + 8 * buf);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { __syncwarp(); tmem_dealloc<512>(tmem); }
+}
+
+int launch_router_logits_tc(const void* x, const void* w, int64_t T, int H, int E, float* logits, int32_t* status, cudaStream_t st) {
+  if (T == 0) return 0;
+  const int e_pad = (E + 31) / 32 * 32;
+  CUtensorMap tx, tw;
+  int rc = make_operand_map(&tx, x, (uint64_t)T, (uint64_t)H * 2, 128);
+  if (rc) return rc;
+  rc = make_operand_map(&tw, w, (uint64_t)E, (uint64_t)H * 2, (uint32_t)e_pad);
+  if (rc) return rc;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(k_router_logits_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, kLgSmem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  int dev = 0, sms = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int n_tiles = (int)((T + 127) / 128);
+  k_router_logits_tc<<<n_tiles < sms ? n_tiles : sms, 192, kLgSmem, st>>>(tx, tw, (int)T, H, E, e_pad, logits, status);
+  return (int)cudaGetLastError();
+}
+
 int launch_route_topk(const float* logits, const float* bias, int64_t T, int E, int K, int32_t* ids, float* weights,
                       cudaStream_t st) {
   if (T == 0) return 0;

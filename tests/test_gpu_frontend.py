@@ -89,10 +89,12 @@ def test_router_random_with_bias_and_ties(t, e, k):
     assert ulp.max() <= 1
 
 
-def test_router_logits():
+@pytest.mark.parametrize("t,h,e", [(300, 2048, 130), (300, 7168, 256), (1000, 2048, 128), (129, 1024, 8), (5, 256, 72)])
+def test_router_logits(t, h, e):
+    """e=130 takes the SIMT kernel, the others the tcgen05 bf16 kernel."""
     import kernelschema_b200 as ks
-    x = torch.randn(300, 2048).to(torch.bfloat16)
-    w = (torch.randn(130, 2048) * 0.02).to(torch.bfloat16)
+    x = torch.randn(t, h).to(torch.bfloat16)
+    w = (torch.randn(e, h) * 0.02).to(torch.bfloat16)
     got = ks.router_logits(x.cuda(), w.cuda()).cpu().numpy()
     ref = o.router_logits(x.float().numpy(), w.float().numpy())
     assert np.abs(got - ref).max() <= 1e-4 * np.abs(ref).max() + 1e-6    # fp32 accumulation vs fp64
