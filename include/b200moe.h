@@ -39,7 +39,7 @@ typedef struct {
   int32_t top_k;              /* routed slots per token */
   int32_t num_shared_experts; /* S experts every token also visits with weight 1; stored after the routed ones */
   int32_t max_tokens;         /* largest T a run may pass */
-  int32_t tile_n;             /* GEMM n-tile: 0 = default, else 128 or 256 */
+  int32_t tile_n;             /* GEMM tile: 0 = default; 128 or 256 = one CTA per 128 x tile_n tile; 512 = CTA pair per 256 x 256 tile */
   int32_t reserved[8];
 } b200moe_config;
 
@@ -78,7 +78,7 @@ typedef struct {
   int32_t* tile_expert;   /* [tile_capacity] */
   int32_t* tile_row0;     /* [tile_capacity] */
   int32_t* tile_rows;     /* [tile_capacity] */
-  int32_t* totals;        /* {m-tiles, permuted rows in use, valid routes} */
+  int32_t* totals;        /* {m-tiles, permuted rows in use, valid routes, 256-row pair items} */
   int32_t* row_of;        /* [T, top_k+S] permuted row of a route or -1 */
   int32_t* tok_of_row;    /* [row_capacity] token of a permuted row or -1 */
   float* weight_of_row;   /* [row_capacity] */
@@ -89,6 +89,9 @@ typedef struct {
   uint16_t* rout;         /* bf16 [row_capacity, H] per-route FC2 results */
   int64_t row_capacity;
   int64_t tile_capacity;
+  int32_t* pair_expert;   /* [tile_capacity] 256-row work items of the CTA-pair GEMM: expert, */
+  int32_t* pair_row0;     /*                 first permuted row,                               */
+  int32_t* pair_rows;     /*                 valid rows (1..256)                               */
 } b200moe_workspace_view;
 
 int b200moe_abi_version(void);
@@ -118,7 +121,7 @@ int b200moe_router_logits(const void* x, const void* gate_weight, int64_t num_to
 
 /* Dense NVFP4 GEMM: out[M,N] = bf16(alpha * A @ B^T), both operands NVFP4 with tiled scales. Contract of
  * DG/problem/reference.py:10-15 with the A operand quantised by b200moe_quantize_nvfp4; B rows are logical
- * (no shuffle). K % 256 == 0, N % tile_n == 0. status: optional device int32 that receives a non-zero code
+ * (no shuffle). K % 256 == 0; tile_n as in b200moe_config (N % tile_n == 0, N % 256 == 0 for 512). status: optional device int32 that receives a non-zero code
  * if a bounded device wait expired. */
 int b200moe_gemm_nvfp4(const void* a_q, const void* a_sf_tiled, const void* b_q, const void* b_sf_tiled, float alpha, void* out,
                        int64_t m, int64_t n, int64_t k, int64_t out_stride, int32_t tile_n, int32_t* status, void* stream);
@@ -146,7 +149,8 @@ int b200moe_combine(const void* rows, const int32_t* row_of, const float* weight
  * it does not own, under a framework allocator that forbids raw cudaMalloc, or in a latency-critical section
  * where an allocation would synchronise the device. This entry point has no counterpart in the reference.
  * It computes exactly what b200moe_route_map computes, but into caller-provided output arrays (sizes as in
- * b200moe_workspace_view; row_capacity >= (T*(top_k+num_shared)/128 + experts + 1) * 128) and keeps its only
+ * b200moe_workspace_view, totals holding 4 ints; row_capacity >= (T*(top_k+num_shared)/128 + experts + 1) * 128; the
+ * pair items are not produced) and keeps its only
  * scratch, the per-block histograms, in a fixed array inside the library: at most 264 experts (routed + shared)
  * and 524288 routes, larger problems are refused with code 770. It never calls cudaMalloc, cudaFree or any
  * allocating routine. The first call on each device looks up the device address of that array (a host-side

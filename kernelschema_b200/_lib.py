@@ -36,7 +36,8 @@ class WorkspaceView(C.Structure):
     _fields_ = [("counts", C.c_void_p), ("seg_start", C.c_void_p), ("tile_expert", C.c_void_p), ("tile_row0", C.c_void_p),
                 ("tile_rows", C.c_void_p), ("totals", C.c_void_p), ("row_of", C.c_void_p), ("tok_of_row", C.c_void_p),
                 ("weight_of_row", C.c_void_p), ("a_q", C.c_void_p), ("a_sf", C.c_void_p), ("act_q", C.c_void_p),
-                ("act_sf", C.c_void_p), ("rout", C.c_void_p), ("row_capacity", C.c_int64), ("tile_capacity", C.c_int64)]
+                ("act_sf", C.c_void_p), ("rout", C.c_void_p), ("row_capacity", C.c_int64), ("tile_capacity", C.c_int64),
+                ("pair_expert", C.c_void_p), ("pair_row0", C.c_void_p), ("pair_rows", C.c_void_p)]
 
 
 #: every exported symbol with (restype, argtypes); the CPU test checks the library exports exactly these

@@ -2,6 +2,7 @@
 // Declarations and the reference interfaces they replace are in include/b200moe.h.
 #include <stdarg.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include "../../include/b200moe.h"
@@ -40,8 +41,12 @@ struct b200moe_layer {
   __nv_bfloat16* rout;
   int32_t* status;
   CUtensorMap tm_a1, tm_a2, tm_b1, tm_b2;
+  CUtensorMap tm_sfa1, tm_sfa2, tm_sfb1, tm_sfb2;   // scale-factor maps of the CTA-pair GEMM
+  int n_clusters;                                    // CTA pairs that can be co-resident
   const void* b1_ptr;
   const void* b2_ptr;
+  const void* s1_ptr;
+  const void* s2_ptr;
 };
 
 namespace {
@@ -50,7 +55,7 @@ int64_t align_up(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
 
 struct Plan {
   int64_t row_capacity, tile_capacity, nblk;
-  int64_t off_block_hist, off_counts, off_seg, off_texp, off_trow0, off_trows, off_totals, off_row_of, off_tok, off_w, off_aq,
+  int64_t off_block_hist, off_counts, off_seg, off_texp, off_trow0, off_trows, off_pexp, off_prow0, off_prows, off_totals, off_row_of, off_tok, off_w, off_aq,
       off_asf, off_actq, off_actsf, off_rout, off_status, total;
 };
 
@@ -64,7 +69,8 @@ int check_cfg(const b200moe_config* c) {
     return fail(713, "config: num_experts + num_shared_experts must be in 1..1024");
   if (c->top_k < 0 || c->top_k > 32 || c->top_k + c->num_shared_experts <= 0) return fail(714, "config: top_k out of range");
   if (c->max_tokens <= 0) return fail(715, "config: max_tokens must be positive");
-  if (c->tile_n != 0 && c->tile_n != 128 && c->tile_n != 256) return fail(716, "config: tile_n must be 0, 128 or 256");
+  if (c->tile_n != 0 && c->tile_n != 128 && c->tile_n != 256 && c->tile_n != 512)
+    return fail(716, "config: tile_n must be 0, 128, 256 or 512");
   return 0;
 }
 
@@ -84,6 +90,9 @@ Plan make_plan(const b200moe_config& c) {
   p.off_texp = take(4 * p.tile_capacity);
   p.off_trow0 = take(4 * p.tile_capacity);
   p.off_trows = take(4 * p.tile_capacity);
+  p.off_pexp = take(4 * p.tile_capacity);
+  p.off_prow0 = take(4 * p.tile_capacity);
+  p.off_prows = take(4 * p.tile_capacity);
   p.off_totals = take(16);
   p.off_row_of = take(4 * routes);
   p.off_tok = take(4 * p.row_capacity);
@@ -137,15 +146,21 @@ int run_impl(b200moe_layer* h, const b200moe_args* a, cudaStream_t st, cudaEvent
                           h->rm.totals, c.hidden, h->row_capacity, h->a_q, h->a_sf, st);
   if (rc) return cuda_fail(rc, "permute");
   mark(2);
-  if (h->b1_ptr != a->gemm1_weights) {
-    rc = make_operand_map(&h->tm_b1, a->gemm1_weights, (uint64_t)h->etot * 2 * c.intermediate, c.hidden / 2, h->bn);
+  if (h->b1_ptr != a->gemm1_weights || h->s1_ptr != a->gemm1_weights_scale) {
+    rc = make_operand_map(&h->tm_b1, a->gemm1_weights, (uint64_t)h->etot * 2 * c.intermediate, c.hidden / 2, h->bn == 512 ? 128 : h->bn);
+    if (!rc && h->bn == 512)
+      rc = make_sf_map(&h->tm_sfb1, a->gemm1_weights_scale, (uint64_t)h->etot * 2 * c.intermediate / 128 * (c.hidden / 64));
     if (rc) return cuda_fail(rc, "FC1 weight tensor map");
     h->b1_ptr = a->gemm1_weights;
+    h->s1_ptr = a->gemm1_weights_scale;
   }
-  if (h->b2_ptr != a->gemm2_weights) {
-    rc = make_operand_map(&h->tm_b2, a->gemm2_weights, (uint64_t)h->etot * c.hidden, c.intermediate / 2, h->bn);
+  if (h->b2_ptr != a->gemm2_weights || h->s2_ptr != a->gemm2_weights_scale) {
+    rc = make_operand_map(&h->tm_b2, a->gemm2_weights, (uint64_t)h->etot * c.hidden, c.intermediate / 2, h->bn == 512 ? 128 : h->bn);
+    if (!rc && h->bn == 512)
+      rc = make_sf_map(&h->tm_sfb2, a->gemm2_weights_scale, (uint64_t)h->etot * c.hidden / 128 * (c.intermediate / 64));
     if (rc) return cuda_fail(rc, "FC2 weight tensor map");
     h->b2_ptr = a->gemm2_weights;
+    h->s2_ptr = a->gemm2_weights_scale;
   }
   GemmParams g;
   memset(&g, 0, sizeof(g));
@@ -171,7 +186,18 @@ int run_impl(b200moe_layer* h, const b200moe_args* a, cudaStream_t st, cudaEvent
     const int64_t worst_tiles = (int64_t)T * h->kk / 128 + h->etot;
     const int64_t items = worst_tiles * (g.N / h->bn);
     const int grid = (int)(items < h->sm_count ? items : h->sm_count);
-    rc = launch_gemm_nvfp4(kGemmFc1, h->bn, h->tm_a1, h->tm_b1, g, grid, st);
+    if (h->bn == 512) {
+      GemmParams gp = g;
+      gp.tile_expert = h->rm.pair_expert;
+      gp.tile_row0 = h->rm.pair_row0;
+      gp.tile_rows = h->rm.pair_rows;
+      gp.n_tiles_ptr = h->rm.totals + 3;
+      const int64_t pair_items = worst_tiles * (g.N / 256);
+      rc = launch_gemm_nvfp4_pair(kGemmFc1, h->tm_a1, h->tm_b1, h->tm_sfa1, h->tm_sfb1, gp,
+                                  (int)(pair_items < h->n_clusters ? pair_items : h->n_clusters), st);
+    } else {
+      rc = launch_gemm_nvfp4(kGemmFc1, h->bn, h->tm_a1, h->tm_b1, g, grid, st);
+    }
     if (rc) return cuda_fail(rc, "FC1");
   }
   mark(3);
@@ -187,7 +213,18 @@ int run_impl(b200moe_layer* h, const b200moe_args* a, cudaStream_t st, cudaEvent
     const int64_t worst_tiles = (int64_t)T * h->kk / 128 + h->etot;
     const int64_t items = worst_tiles * (g.N / h->bn);
     const int grid = (int)(items < h->sm_count ? items : h->sm_count);
-    rc = launch_gemm_nvfp4(kGemmFc2, h->bn, h->tm_a2, h->tm_b2, g, grid, st);
+    if (h->bn == 512) {
+      GemmParams gp = g;
+      gp.tile_expert = h->rm.pair_expert;
+      gp.tile_row0 = h->rm.pair_row0;
+      gp.tile_rows = h->rm.pair_rows;
+      gp.n_tiles_ptr = h->rm.totals + 3;
+      const int64_t pair_items = worst_tiles * (g.N / 256);
+      rc = launch_gemm_nvfp4_pair(kGemmFc2, h->tm_a2, h->tm_b2, h->tm_sfa2, h->tm_sfb2, gp,
+                                  (int)(pair_items < h->n_clusters ? pair_items : h->n_clusters), st);
+    } else {
+      rc = launch_gemm_nvfp4(kGemmFc2, h->bn, h->tm_a2, h->tm_b2, g, grid, st);
+    }
     if (rc) return cuda_fail(rc, "FC2");
   }
   mark(4);
@@ -243,8 +280,9 @@ int b200moe_router_logits(const void* x, const void* w, int64_t T, int32_t H, in
 int b200moe_gemm_nvfp4(const void* a_q, const void* a_sf, const void* b_q, const void* b_sf, float alpha, void* out, int64_t m,
                        int64_t n, int64_t k, int64_t out_stride, int32_t tile_n, int32_t* status, void* stream) {
   const int bn = tile_n ? tile_n : 128;
-  if (bn != 128 && bn != 256) return fail(760, "gemm: tile_n must be 0, 128 or 256");
-  if (m < 0 || n <= 0 || k <= 0 || k % 256 || n % bn) return fail(761, "gemm: need K %% 256 == 0 and N %% tile_n == 0");
+  if (bn != 128 && bn != 256 && bn != 512) return fail(760, "gemm: tile_n must be 0, 128, 256 or 512");
+  if (m < 0 || n <= 0 || k <= 0 || k % 256 || n % (bn == 512 ? 256 : bn))
+    return fail(761, "gemm: need K %% 256 == 0 and N %% tile_n == 0 (N %% 256 == 0 for the CTA-pair tile)");
   if (m == 0) return 0;
   if (!a_q || !a_sf || !b_q || !b_sf || !out) return fail(762, "gemm: null pointer");
   if (((uintptr_t)a_q | (uintptr_t)a_sf | (uintptr_t)b_q | (uintptr_t)b_sf | (uintptr_t)out) & 15)
@@ -253,7 +291,7 @@ int b200moe_gemm_nvfp4(const void* a_q, const void* a_sf, const void* b_q, const
   CUtensorMap ta, tb;
   int rc = make_operand_map(&ta, a_q, (uint64_t)m, (uint64_t)k / 2, 128);
   if (rc) return cuda_fail(rc, "gemm A tensor map");
-  rc = make_operand_map(&tb, b_q, (uint64_t)n, (uint64_t)k / 2, bn);
+  rc = make_operand_map(&tb, b_q, (uint64_t)n, (uint64_t)k / 2, bn == 512 ? 128 : bn);
   if (rc) return cuda_fail(rc, "gemm B tensor map");
   GemmParams g;
   memset(&g, 0, sizeof(g));
@@ -267,9 +305,20 @@ int b200moe_gemm_nvfp4(const void* a_q, const void* a_sf, const void* b_q, const
   g.out_stride = out_stride;
   g.dense_alpha = alpha;
   g.status = status;
+  if (const char* dbg = getenv("B200MOE_DBG")) g.dbg = atoi(dbg);   // timing experiments only
   int dev = 0, sms = 0;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (bn == 512) {
+    CUtensorMap tsa, tsb;
+    rc = make_sf_map(&tsa, a_sf, (uint64_t)((m + 127) / 128) * (k / 64));
+    if (!rc) rc = make_sf_map(&tsb, b_sf, (uint64_t)(n / 128) * (k / 64));
+    if (rc) return cuda_fail(rc, "gemm scale tensor maps");
+    g.n_tiles_static = (int)((m + 255) / 256);
+    const int64_t pair_items = (int64_t)g.n_tiles_static * (n / 256);
+    const int clusters = (int)(pair_items < sms / 2 ? pair_items : sms / 2);
+    return cuda_fail(launch_gemm_nvfp4_pair(kGemmDense, ta, tb, tsa, tsb, g, clusters, (cudaStream_t)stream), "gemm");
+  }
   const int64_t items = (int64_t)g.n_tiles_static * (n / bn);
   const int grid = (int)(items < sms ? items : sms);
   return cuda_fail(launch_gemm_nvfp4(kGemmDense, bn, ta, tb, g, grid, (cudaStream_t)stream), "gemm");
@@ -294,7 +343,8 @@ int b200moe_create(const b200moe_config* cfg, b200moe_handle* out) {
   h->row_capacity = p.row_capacity;
   h->tile_capacity = p.tile_capacity;
   h->bn = cfg->tile_n ? cfg->tile_n : 128;
-  if ((2 * cfg->intermediate) % h->bn || cfg->hidden % h->bn) {
+  h->n_clusters = 0;
+  if ((2 * cfg->intermediate) % (h->bn == 512 ? 256 : h->bn) || cfg->hidden % (h->bn == 512 ? 256 : h->bn)) {
     delete h;
     return fail(718, "create: tile_n=%d does not divide 2*intermediate and hidden", h->bn);
   }
@@ -315,6 +365,9 @@ int b200moe_create(const b200moe_config* cfg, b200moe_handle* out) {
   h->rm.tile_row0 = (int32_t*)(b + p.off_trow0);
   h->rm.tile_rows = (int32_t*)(b + p.off_trows);
   h->rm.totals = (int32_t*)(b + p.off_totals);
+  h->rm.pair_expert = (int32_t*)(b + p.off_pexp);
+  h->rm.pair_row0 = (int32_t*)(b + p.off_prow0);
+  h->rm.pair_rows = (int32_t*)(b + p.off_prows);
   h->rm.row_of = (int32_t*)(b + p.off_row_of);
   h->rm.tok_of_row = (int32_t*)(b + p.off_tok);
   h->rm.weight_of_row = (float*)(b + p.off_w);
@@ -334,6 +387,9 @@ int b200moe_create(const b200moe_config* cfg, b200moe_handle* out) {
   }
   rc = make_operand_map(&h->tm_a1, h->a_q, (uint64_t)p.row_capacity, cfg->hidden / 2, 128);
   if (!rc) rc = make_operand_map(&h->tm_a2, h->act_q, (uint64_t)p.row_capacity, cfg->intermediate / 2, 128);
+  if (!rc) rc = make_sf_map(&h->tm_sfa1, h->a_sf, (uint64_t)p.row_capacity / 128 * (cfg->hidden / 64));
+  if (!rc) rc = make_sf_map(&h->tm_sfa2, h->act_sf, (uint64_t)p.row_capacity / 128 * (cfg->intermediate / 64));
+  h->n_clusters = h->sm_count / 2;
   if (rc) {
     cudaFree(h->base);
     delete h;
@@ -368,6 +424,9 @@ int b200moe_workspace(b200moe_handle h, b200moe_workspace_view* v) {
   v->rout = (uint16_t*)h->rout;
   v->row_capacity = h->row_capacity;
   v->tile_capacity = h->tile_capacity;
+  v->pair_expert = h->rm.pair_expert;
+  v->pair_row0 = h->rm.pair_row0;
+  v->pair_rows = h->rm.pair_rows;
   return 0;
 }
 

@@ -27,6 +27,7 @@ constexpr int kBM = 128;
 constexpr int kStageK = 256;             // FP4 elements of K per pipeline stage (128 payload bytes per row)
 constexpr int kSfChunk = 512;            // bytes of one (128 rows x 64 K) scale-factor chunk
 constexpr int kNumSfBuf = 4;             // TMEM scale-factor buffers in rotation
+constexpr int kSfLead = 2;               // stages by which the scale-factor copies lead the MMAs (< kNumSfBuf, < stages)
 
 template <int BN>
 struct GemmCfg {
@@ -54,10 +55,215 @@ DEV float tanh_fast(float x) {
   return y;
 }
 
+// Epilogue of one 128 x BN accumulator tile for the calling warp's 32 TMEM lanes (one row per thread).
+// `release` is invoked once, as soon as the last TMEM read of the tile has completed.
+template <int MODE, int BN, class Release>
+DEV void epilogue_tile(const GemmParams& p, uint32_t taddr, int e, size_t row, bool live, int nt, Release release) {
+  if (p.dbg & 8) live = false;
+  if (MODE == kGemmFc1) {
+    const float s_up = p.scale_up ? p.scale_up[e] : 1.0f;
+    const float s_gate = p.scale_gate ? p.scale_gate[e] : 1.0f;
+    const float alpha = p.alpha ? p.alpha[e] : 1.0f;
+    const float beta = p.beta ? p.beta[e] : 0.0f;
+    const bool clamp = p.limit != nullptr;
+    const float limit = clamp ? p.limit[e] : 0.f;
+    const int half_i = p.N >> 2;                       // bytes of one row of packed activations (I / 2)
+    uint2 packed[BN / 32];
+    uint32_t sfbytes = 0;
+    uint32_t sfword[BN / 128];
+#pragma unroll
+    for (int cb = 0; cb < BN / 32; ++cb) {
+      float v[32];
+      tmem_ld32(taddr + cb * 32, v);
+      tmem_ld_wait();
+      float act[16];
+      float amax = 0.f;
+#pragma unroll
+      for (int c = 0; c < 2; ++c)
+#pragma unroll
+        for (int b = 0; b < 8; ++b) {
+          float up = v[16 * c + b] * s_up;
+          float gate = v[16 * c + 8 + b] * s_gate;
+          if (clamp) {
+            up = fminf(fmaxf(up, -limit), limit);
+            gate = fminf(gate, limit);
+          }
+          float a;
+          if (p.act_type == 10)
+            a = alpha * tanh_fast(__fdividef(gate, alpha)) * sigmoid_fast(gate) * (beta * tanh_fast(__fdividef(up, beta)));
+          else
+            a = gate * sigmoid_fast(alpha * gate) * (up + beta);
+          act[2 * b + c] = a;
+          amax = fmaxf(amax, fabsf(a));
+        }
+      // reference.py:40-42: sf = e4m3(clamp(amax * (1/6), 0, 448)); zero scale -> zero block
+      const float sfv = fminf(amax * (1.0f / 6.0f), 448.0f);
+      const uint32_t sb = cvt_e4m3(sfv);
+      const float sff = e4m3_to_f32(sb);
+      const float inv = sff > 0.f ? __frcp_rn(sff) : 0.f;
+      uint32_t w0 = 0, w1 = 0;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        w0 |= cvt_e2m1x2(act[2 * j] * inv, act[2 * j + 1] * inv) << (8 * j);
+        w1 |= cvt_e2m1x2(act[8 + 2 * j] * inv, act[8 + 2 * j + 1] * inv) << (8 * j);
+      }
+      packed[cb] = make_uint2(w0, w1);
+      sfbytes |= sb << (8 * (cb & 3));
+      if ((cb & 3) == 3) { sfword[cb >> 2] = sfbytes; sfbytes = 0; }
+    }
+    release();
+    if (live) {
+      const int i0 = (nt * BN) >> 1;                   // first intermediate channel of this tile
+      uint4* dst = reinterpret_cast<uint4*>(p.act_q + row * half_i + (i0 >> 1));
+#pragma unroll
+      for (int j = 0; j < BN / 64; ++j)
+        dst[j] = make_uint4(packed[2 * j].x, packed[2 * j].y, packed[2 * j + 1].x, packed[2 * j + 1].y);
+      // scale bytes of 64 channels = one 4-byte word of the 128x4-tiled layout [row/128][I/64][32][16]
+      const int chunks_i = p.N >> 7;                   // I / 64
+#pragma unroll
+      for (int j = 0; j < BN / 128; ++j) {
+        const size_t off = ((row >> 7) * chunks_i + (size_t)((i0 >> 6) + j)) * kSfChunk + (row & 31) * 16 + ((row >> 5) & 3) * 4;
+        *reinterpret_cast<uint32_t*>(p.act_sf + off) = sfword[j];
+      }
+    }
+  } else {
+    const float oscale = (MODE == kGemmFc2) ? (p.out_scale ? p.out_scale[e] : 1.0f) : p.dense_alpha;
+    __nv_bfloat16* dst_row = p.out + row * p.out_stride + (size_t)nt * BN;
+#pragma unroll
+    for (int cb = 0; cb < BN / 32; ++cb) {
+      float v[32];
+      tmem_ld32(taddr + cb * 32, v);
+      tmem_ld_wait();
+      if (cb == BN / 32 - 1) release();
+      if (live) {
+        uint32_t o[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          float x0, x1;
+          if (MODE == kGemmFc2) {           // output channel 4b+a lives in column 8a+b
+            const int h0 = 2 * j, h1 = 2 * j + 1;
+            x0 = v[8 * (h0 & 3) + (h0 >> 2)];
+            x1 = v[8 * (h1 & 3) + (h1 >> 2)];
+          } else {
+            x0 = v[2 * j];
+            x1 = v[2 * j + 1];
+          }
+          const __nv_bfloat162 pr = __floats2bfloat162_rn(x0 * oscale, x1 * oscale);
+          o[j] = *reinterpret_cast<const uint32_t*>(&pr);
+        }
+        uint4* d4 = reinterpret_cast<uint4*>(dst_row + cb * 32);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) d4[j] = make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
+      }
+    }
+  }
+}
+
+// Epilogue of 128 accumulator columns [col0, col0 + 128) of one tile for the calling warp's 32 TMEM lanes.
+// All 128 values are pulled into registers first and `release` is called right after the last TMEM read, so
+// the accumulator buffer is free again after a few hundred cycles and the arithmetic, the requantisation and the
+// global stores overlap the next tile's mainloop.
+template <int MODE, class Release>
+DEV void epilogue_cols128(const GemmParams& p, uint32_t taddr, int e, size_t row, bool live, int col0, Release release) {
+  if (p.dbg & 8) live = false;
+  float v[4][32];
+#pragma unroll
+  for (int cb = 0; cb < 4; ++cb) tmem_ld32(taddr + cb * 32, v[cb]);
+  tmem_ld_wait();
+  release();
+  if (MODE == kGemmFc1) {
+    const float s_up = p.scale_up ? p.scale_up[e] : 1.0f;
+    const float s_gate = p.scale_gate ? p.scale_gate[e] : 1.0f;
+    const float alpha = p.alpha ? p.alpha[e] : 1.0f;
+    const float beta = p.beta ? p.beta[e] : 0.0f;
+    const bool clamp = p.limit != nullptr;
+    const float limit = clamp ? p.limit[e] : 0.f;
+    uint2 packed[4];
+    uint32_t sfword = 0;
+#pragma unroll
+    for (int cb = 0; cb < 4; ++cb) {
+      float act[16];
+      float amax = 0.f;
+#pragma unroll
+      for (int c = 0; c < 2; ++c)
+#pragma unroll
+        for (int b = 0; b < 8; ++b) {
+          float up = v[cb][16 * c + b] * s_up;
+          float gate = v[cb][16 * c + 8 + b] * s_gate;
+          if (clamp) {
+            up = fminf(fmaxf(up, -limit), limit);
+            gate = fminf(gate, limit);
+          }
+          float a;
+          if (p.act_type == 10)
+            a = alpha * tanh_fast(__fdividef(gate, alpha)) * sigmoid_fast(gate) * (beta * tanh_fast(__fdividef(up, beta)));
+          else
+            a = gate * sigmoid_fast(alpha * gate) * (up + beta);
+          act[2 * b + c] = a;
+          amax = fmaxf(amax, fabsf(a));
+        }
+      // reference.py:40-42: sf = e4m3(clamp(amax * (1/6), 0, 448)); zero scale -> zero block
+      const float sfv = fminf(amax * (1.0f / 6.0f), 448.0f);
+      const uint32_t sb = cvt_e4m3(sfv);
+      const float sff = e4m3_to_f32(sb);
+      const float inv = sff > 0.f ? __frcp_rn(sff) : 0.f;
+      uint32_t w0 = 0, w1 = 0;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        w0 |= cvt_e2m1x2(act[2 * j] * inv, act[2 * j + 1] * inv) << (8 * j);
+        w1 |= cvt_e2m1x2(act[8 + 2 * j] * inv, act[8 + 2 * j + 1] * inv) << (8 * j);
+      }
+      packed[cb] = make_uint2(w0, w1);
+      sfword |= sb << (8 * cb);
+    }
+    if (live) {
+      const int half_i = p.N >> 2;                     // bytes of one row of packed activations (I / 2)
+      const int i0 = col0 >> 1;                        // first intermediate channel of these 128 columns (multiple of 64)
+      uint4* dst = reinterpret_cast<uint4*>(p.act_q + row * half_i + (i0 >> 1));
+      dst[0] = make_uint4(packed[0].x, packed[0].y, packed[1].x, packed[1].y);
+      dst[1] = make_uint4(packed[2].x, packed[2].y, packed[3].x, packed[3].y);
+      // scale bytes of 64 channels = one 4-byte word of the 128x4-tiled layout [row/128][I/64][32][16]
+      const size_t off = ((row >> 7) * (size_t)(p.N >> 7) + (size_t)(i0 >> 6)) * kSfChunk + (row & 31) * 16 + ((row >> 5) & 3) * 4;
+      *reinterpret_cast<uint32_t*>(p.act_sf + off) = sfword;
+    }
+  } else {
+    if (!live) return;
+    const float oscale = (MODE == kGemmFc2) ? (p.out_scale ? p.out_scale[e] : 1.0f) : p.dense_alpha;
+    __nv_bfloat16* dst_row = p.out + row * p.out_stride + col0;
+#pragma unroll
+    for (int cb = 0; cb < 4; ++cb) {
+      uint32_t o[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        float x0, x1;
+        if (MODE == kGemmFc2) {           // output channel 4b+a lives in column 8a+b
+          const int h0 = 2 * j, h1 = 2 * j + 1;
+          x0 = v[cb][8 * (h0 & 3) + (h0 >> 2)];
+          x1 = v[cb][8 * (h1 & 3) + (h1 >> 2)];
+        } else {
+          x0 = v[cb][2 * j];
+          x1 = v[cb][2 * j + 1];
+        }
+        const __nv_bfloat162 pr = __floats2bfloat162_rn(x0 * oscale, x1 * oscale);
+        o[j] = *reinterpret_cast<const uint32_t*>(&pr);
+      }
+      uint4* d4 = reinterpret_cast<uint4*>(dst_row + cb * 32);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) d4[j] = make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
+    }
+  }
+}
+
+// Warp roles: 0 = TMA producer, 1 = TMEM owner + MMA issuer, 2 = scale-factor copier (shared memory -> TMEM),
+// 3 .. 3 + BN/32 - 1 = epilogue; epilogue warp w owns TMEM lane quadrant w & 3 and the 128-column group (w - 3) / 4.
+template <int BN>
+constexpr int gemm_threads() { return 32 * (3 + BN / 32); }
+
 template <int MODE, int BN>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__(gemm_threads<BN>(), 1)
 k_gemm_nvfp4(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, const GemmParams p) {
   using C = GemmCfg<BN>;
+  constexpr int kEpiWarps = BN / 32;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t s_a = smem_base;
@@ -65,8 +271,9 @@ k_gemm_nvfp4(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
   const uint32_t s_sfa = s_b + C::kStages * C::kBBytes;
   const uint32_t s_sfb = s_sfa + C::kStages * C::kSfaBytes;
   const uint32_t s_bar = s_sfb + C::kStages * C::kSfbBytes;
-  const uint32_t bar_full = s_bar;                         // [kStages]
-  const uint32_t bar_empty = bar_full + 8 * C::kStages;    // [kStages]
+  const uint32_t bar_full = s_bar;                              // [kStages] TMA bytes landed
+  const uint32_t bar_sf = bar_full + 8 * C::kStages;            // [kStages] scale factors of the stage are in TMEM
+  const uint32_t bar_empty = bar_sf + 8 * C::kStages;           // [kStages] MMAs of the stage retired
   const uint32_t bar_acc_full = bar_empty + 8 * C::kStages;     // [kAccBufs]
   const uint32_t bar_acc_empty = bar_acc_full + 8 * C::kAccBufs;
   const uint32_t s_tmem_slot = bar_acc_empty + 8 * C::kAccBufs;
@@ -77,11 +284,12 @@ k_gemm_nvfp4(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::kStages; ++s) {
       mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_sf + 8 * s, 1);
       mbar_init(bar_empty + 8 * s, 1);
     }
     for (int b = 0; b < C::kAccBufs; ++b) {
       mbar_init(bar_acc_full + 8 * b, 1);
-      mbar_init(bar_acc_empty + 8 * b, 4);
+      mbar_init(bar_acc_empty + 8 * b, kEpiWarps);
     }
     mbar_init_fence();
     tma_prefetch_desc(&tm_a);
@@ -103,7 +311,7 @@ k_gemm_nvfp4(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      uint32_t g = 0;
+      uint32_t s = 0, ph = 1;
       bool ok = true;
       for (long long item = blockIdx.x; ok && item < total_items; item += gridDim.x) {
         const int mt = (int)(item / n_ntiles), nt = (int)(item % n_ntiles);
@@ -112,59 +320,93 @@ k_gemm_nvfp4(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
         const int brow0 = e * p.N + nt * BN;
         const uint8_t* sfa_src = p.sfa + (size_t)(row0 >> 7) * chunks_per_row * kSfChunk;
         const uint8_t* sfb_src = p.sfb + (size_t)(brow0 >> 7) * chunks_per_row * kSfChunk;
-        for (int ks = 0; ks < nk; ++ks, ++g) {
-          const uint32_t s = g % C::kStages;
-          if (!mbar_wait(bar_empty + 8 * s, ((g / C::kStages) & 1) ^ 1)) { report(p.status, 101); ok = false; break; }
+        for (int ks = 0; ks < nk; ++ks) {
+          if (!mbar_wait(bar_empty + 8 * s, ph)) { report(p.status, 101); ok = false; break; }
           const uint32_t full = bar_full + 8 * s;
-          mbar_expect_tx(full, C::kStageBytes);
-          tma_load_2d(s_a + s * C::kABytes, &tm_a, full, ks * 128, row0);
-          tma_load_2d(s_b + s * C::kBBytes, &tm_b, full, ks * 128, brow0);
-          bulk_load_1d(s_sfa + s * C::kSfaBytes, sfa_src + (size_t)ks * 4 * kSfChunk, 4 * kSfChunk, full);
+          if (p.dbg & 1) {
+            mbar_arrive(full);
+          } else {
+            mbar_expect_tx(full, C::kStageBytes);
+            tma_load_2d(s_a + s * C::kABytes, &tm_a, full, ks * 128, row0);
+            tma_load_2d(s_b + s * C::kBBytes, &tm_b, full, ks * 128, brow0);
+            bulk_load_1d(s_sfa + s * C::kSfaBytes, sfa_src + (size_t)ks * 4 * kSfChunk, 4 * kSfChunk, full);
 #pragma unroll
-          for (int h = 0; h < BN / 128; ++h)
-            bulk_load_1d(s_sfb + s * C::kSfbBytes + h * 4 * kSfChunk,
-                         sfb_src + ((size_t)h * chunks_per_row + (size_t)ks * 4) * kSfChunk, 4 * kSfChunk, full);
+            for (int h = 0; h < BN / 128; ++h)
+              bulk_load_1d(s_sfb + s * C::kSfbBytes + h * 4 * kSfChunk,
+                           sfb_src + ((size_t)h * chunks_per_row + (size_t)ks * 4) * kSfChunk, 4 * kSfChunk, full);
+          }
+          if (++s == C::kStages) { s = 0; ph ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 2) {
+    // ------------------------------------------------------------------ scale-factor copier: shared memory -> TMEM
+    // A separate issuing thread keeps the 8 or 12 tcgen05.cp per stage off the MMA thread's instruction stream;
+    // the commit that follows them arrives on bar_sf once the copies have landed.
+    if (lane == 0) {
+      constexpr uint32_t kHiSf = (128u >> 4) | (1u << 14);                 // SBO 128, descriptor version 1, no swizzle
+      const uint32_t sfa_lo0 = (s_sfa >> 4) & 0x3FFF, sfb_lo0 = (s_sfb >> 4) & 0x3FFF;
+      uint32_t s = 0, ph = 0, sfi = 0;
+      bool ok = true;
+      for (long long item = blockIdx.x; ok && item < total_items; item += gridDim.x) {
+        for (int ks = 0; ks < nk; ++ks) {
+          if (!mbar_wait(bar_full + 8 * s, ph)) { report(p.status, 105); ok = false; break; }
+          tc_fence_after();
+          if (!(p.dbg & 4)) {
+            const uint32_t sf_t = tmem + C::kSfBase + sfi * C::kSfCols;
+            const uint32_t sfa_lo = sfa_lo0 + s * (C::kSfaBytes >> 4), sfb_lo = sfb_lo0 + s * (C::kSfbBytes >> 4);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) tmem_cp_sf(sf_t + 4 * q, ((uint64_t)kHiSf << 32) | (sfa_lo + q * (kSfChunk >> 4)));
+#pragma unroll
+            for (int h = 0; h < BN / 128; ++h)
+#pragma unroll
+              for (int q = 0; q < 4; ++q)
+                tmem_cp_sf(sf_t + 16 + (BN / 128) * 4 * q + 4 * h, ((uint64_t)kHiSf << 32) | (sfb_lo + (h * 4 + q) * (kSfChunk >> 4)));
+          }
+          mma_commit(bar_sf + 8 * s);
+          if (++s == C::kStages) { s = 0; ph ^= 1; }
+          sfi = (sfi + 1) & (kNumSfBuf - 1);
         }
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
+      // One thread feeds the tensor pipe: everything is 32-bit, the stage ring is walked with counters and the
+      // shared-memory descriptors are base + stage * stride.
       constexpr uint32_t idesc = make_idesc_nvf4(kBM, BN);
-      uint32_t g = 0, it = 0;
+      constexpr uint32_t kHiOp = (1024u >> 4) | (1u << 14) | (2u << 29);   // SBO 1024, version 1, SWIZZLE_128B
+      const uint32_t a_lo0 = ((s_a >> 4) & 0x3FFF) | (1u << 16), b_lo0 = ((s_b >> 4) & 0x3FFF) | (1u << 16);
+      uint32_t s = 0, ph = 0, sfi = 0, it = 0;
       bool ok = true;
       for (long long item = blockIdx.x; ok && item < total_items; item += gridDim.x, ++it) {
         const uint32_t buf = it % C::kAccBufs;
         if (!mbar_wait(bar_acc_empty + 8 * buf, ((it / C::kAccBufs) & 1) ^ 1)) { report(p.status, 102); break; }
         tc_fence_after();
         const uint32_t acc = tmem + buf * BN;
-        for (int ks = 0; ks < nk; ++ks, ++g) {
-          const uint32_t s = g % C::kStages;
-          if (!mbar_wait(bar_full + 8 * s, (g / C::kStages) & 1)) { report(p.status, 103); ok = false; break; }
+        for (int ks = 0; ks < nk; ++ks) {
+          if (!mbar_wait(bar_sf + 8 * s, ph)) { report(p.status, 103); ok = false; break; }
           tc_fence_after();
-          const uint32_t sf_t = tmem + C::kSfBase + (g % kNumSfBuf) * C::kSfCols;
-          const uint32_t sfa_t = sf_t, sfb_t = sf_t + 16;
-          const uint32_t sfa_s = s_sfa + s * C::kSfaBytes, sfb_s = s_sfb + s * C::kSfbBytes;
+          if (!(p.dbg & 2)) {
+            const uint32_t sf_t = tmem + C::kSfBase + sfi * C::kSfCols;
+            const uint32_t a_lo = a_lo0 + s * (C::kABytes >> 4), b_lo = b_lo0 + s * (C::kBBytes >> 4);
+            mma_nvf4(acc, ((uint64_t)kHiOp << 32) | a_lo, ((uint64_t)kHiOp << 32) | b_lo, idesc, sf_t, sf_t + 16, ks ? 1u : 0u);
 #pragma unroll
-          for (int q = 0; q < 4; ++q) tmem_cp_sf(sfa_t + 4 * q, make_desc_sf(sfa_s + q * kSfChunk));
-#pragma unroll
-          for (int h = 0; h < BN / 128; ++h)
-#pragma unroll
-            for (int q = 0; q < 4; ++q)
-              tmem_cp_sf(sfb_t + (BN / 128) * 4 * q + 4 * h, make_desc_sf(sfb_s + (h * 4 + q) * kSfChunk));
-          const uint64_t a_d = make_desc_sw128(s_a + s * C::kABytes);
-          const uint64_t b_d = make_desc_sw128(s_b + s * C::kBBytes);
-#pragma unroll
-          for (int q = 0; q < 4; ++q)
-            mma_nvf4(acc, a_d + 2 * q, b_d + 2 * q, idesc, sfa_t + 4 * q, sfb_t + (BN / 128) * 4 * q, (ks | q) ? 1u : 0u);
+            for (int q = 1; q < 4; ++q)
+              mma_nvf4(acc, ((uint64_t)kHiOp << 32) | (a_lo + 2 * q), ((uint64_t)kHiOp << 32) | (b_lo + 2 * q), idesc, sf_t + 4 * q,
+                       sf_t + 16 + (BN / 128) * 4 * q, 1u);
+          }
           mma_commit(bar_empty + 8 * s);
+          if (++s == C::kStages) { s = 0; ph ^= 1; }
+          sfi = (sfi + 1) & (kNumSfBuf - 1);
         }
         if (ok) mma_commit(bar_acc_full + 8 * buf);
       }
     }
   } else {
-    // ------------------------------------------------------------------ epilogue (4 warps, one TMEM lane quadrant each)
+    // ------------------------------------------------------------------ epilogue
     const int quad = warp & 3;
+    const int group = (warp - 3) >> 2;               // which 128 accumulator columns
     const int r_in_tile = quad * 32 + lane;
     uint32_t it = 0;
     for (long long item = blockIdx.x; item < total_items; item += gridDim.x, ++it) {
@@ -178,113 +420,12 @@ k_gemm_nvfp4(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
       okw = __shfl_sync(0xFFFFFFFFu, okw, 0);
       if (!okw) { if (lane == 0) report(p.status, 104); break; }
       tc_fence_after();
-      const uint32_t taddr = tmem + ((uint32_t)(quad * 32) << 16) + buf * BN;
-      const bool live = r_in_tile < rows;
-      const size_t row = (size_t)row0 + r_in_tile;
-
-      if (MODE == kGemmFc1) {
-        const float s_up = p.scale_up ? p.scale_up[e] : 1.0f;
-        const float s_gate = p.scale_gate ? p.scale_gate[e] : 1.0f;
-        const float alpha = p.alpha ? p.alpha[e] : 1.0f;
-        const float beta = p.beta ? p.beta[e] : 0.0f;
-        const bool clamp = p.limit != nullptr;
-        const float limit = clamp ? p.limit[e] : 0.f;
-        const int half_i = p.N >> 2;                       // bytes of one row of packed activations (I / 2)
-        uint2 packed[BN / 32];
-        uint32_t sfbytes = 0;
-        uint32_t sfword[BN / 128];
-#pragma unroll
-        for (int cb = 0; cb < BN / 32; ++cb) {
-          float v[32];
-          tmem_ld32(taddr + cb * 32, v);
-          tmem_ld_wait();
-          float act[16];
-          float amax = 0.f;
-#pragma unroll
-          for (int c = 0; c < 2; ++c)
-#pragma unroll
-            for (int b = 0; b < 8; ++b) {
-              float up = v[16 * c + b] * s_up;
-              float gate = v[16 * c + 8 + b] * s_gate;
-              if (clamp) {
-                up = fminf(fmaxf(up, -limit), limit);
-                gate = fminf(gate, limit);
-              }
-              float a;
-              if (p.act_type == 10)
-                a = alpha * tanh_fast(__fdividef(gate, alpha)) * sigmoid_fast(gate) * (beta * tanh_fast(__fdividef(up, beta)));
-              else
-                a = gate * sigmoid_fast(alpha * gate) * (up + beta);
-              act[2 * b + c] = a;
-              amax = fmaxf(amax, fabsf(a));
-            }
-          // reference.py:40-42: sf = e4m3(clamp(amax * (1/6), 0, 448)); zero scale -> zero block
-          const float sfv = fminf(amax * (1.0f / 6.0f), 448.0f);
-          const uint32_t sb = cvt_e4m3(sfv);
-          const float sff = e4m3_to_f32(sb);
-          const float inv = sff > 0.f ? __frcp_rn(sff) : 0.f;
-          uint32_t w0 = 0, w1 = 0;
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            w0 |= cvt_e2m1x2(act[2 * j] * inv, act[2 * j + 1] * inv) << (8 * j);
-            w1 |= cvt_e2m1x2(act[8 + 2 * j] * inv, act[8 + 2 * j + 1] * inv) << (8 * j);
-          }
-          packed[cb] = make_uint2(w0, w1);
-          sfbytes |= sb << (8 * (cb & 3));
-          if ((cb & 3) == 3) { sfword[cb >> 2] = sfbytes; sfbytes = 0; }
-        }
+      const uint32_t taddr = tmem + ((uint32_t)(quad * 32) << 16) + buf * BN + group * 128;
+      epilogue_cols128<MODE>(p, taddr, e, (size_t)row0 + r_in_tile, r_in_tile < rows, nt * BN + group * 128, [&]() {
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_acc_empty + 8 * buf);
-        if (live) {
-          const int i0 = (nt * BN) >> 1;                   // first intermediate channel of this tile
-          uint4* dst = reinterpret_cast<uint4*>(p.act_q + row * half_i + (i0 >> 1));
-#pragma unroll
-          for (int j = 0; j < BN / 64; ++j)
-            dst[j] = make_uint4(packed[2 * j].x, packed[2 * j].y, packed[2 * j + 1].x, packed[2 * j + 1].y);
-          // scale bytes of 64 channels = one 4-byte word of the 128x4-tiled layout [row/128][I/64][32][16]
-          const int chunks_i = p.N >> 7;                   // I / 64
-#pragma unroll
-          for (int j = 0; j < BN / 128; ++j) {
-            const size_t off = ((row >> 7) * chunks_i + (size_t)((i0 >> 6) + j)) * kSfChunk + (row & 31) * 16 + ((row >> 5) & 3) * 4;
-            *reinterpret_cast<uint32_t*>(p.act_sf + off) = sfword[j];
-          }
-        }
-      } else {
-        const float oscale = (MODE == kGemmFc2) ? (p.out_scale ? p.out_scale[e] : 1.0f) : p.dense_alpha;
-        __nv_bfloat16* dst_row = p.out + row * p.out_stride + (size_t)nt * BN;
-#pragma unroll
-        for (int cb = 0; cb < BN / 32; ++cb) {
-          float v[32];
-          tmem_ld32(taddr + cb * 32, v);
-          tmem_ld_wait();
-          if (cb == BN / 32 - 1) {
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar_acc_empty + 8 * buf);
-          }
-          if (live) {
-            uint32_t o[16];
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              float x0, x1;
-              if (MODE == kGemmFc2) {           // output channel 4b+a lives in column 8a+b
-                const int h0 = 2 * j, h1 = 2 * j + 1;
-                x0 = v[8 * (h0 & 3) + (h0 >> 2)];
-                x1 = v[8 * (h1 & 3) + (h1 >> 2)];
-              } else {
-                x0 = v[2 * j];
-                x1 = v[2 * j + 1];
-              }
-              const __nv_bfloat162 pr = __floats2bfloat162_rn(x0 * oscale, x1 * oscale);
-              o[j] = *reinterpret_cast<const uint32_t*>(&pr);
-            }
-            uint4* d4 = reinterpret_cast<uint4*>(dst_row + cb * 32);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) d4[j] = make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
-          }
-        }
-      }
+      });
     }
   }
   tc_fence_before();
@@ -292,6 +433,175 @@ k_gemm_nvfp4(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
   if (warp == 1) {
     __syncwarp();
     tmem_dealloc<512>(tmem);
+  }
+}
+
+// ----------------------------------------------------------------------------- CTA-pair variant (256 x 256 tiles)
+// Two CTAs of a cluster work as one tcgen05 cta_group::2 unit: each loads its own 128 rows of A and its own 128
+// of the 256 weight rows (no multicast), so one byte fetched from L2 feeds twice the tensor work of a 128 x 256
+// single-CTA tile. Work item = (pair of consecutive 128-row m-tiles of one expert, 256 weight rows).
+// Barriers: `full` lives in the leader (2 producer arrivals + both CTAs' TMA bytes); `empty` and `acc_full` exist
+// in both CTAs and are signalled by the leader's tcgen05.commit to both; `acc_empty` lives in the leader and
+// collects the 8 epilogue warps of the pair.
+struct PairCfg {
+  static constexpr int kStages = 5;
+  static constexpr int kABytes = 128 * 128;
+  static constexpr int kBBytes = 128 * 128;
+  static constexpr int kSfaBytes = 4 * kSfChunk;
+  static constexpr int kSfbBytes = 2 * 4 * kSfChunk;
+  static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;   // per CTA
+  static constexpr int kSfCols = 48;
+  static constexpr int kSfBase = 256;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+};
+
+template <int MODE>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+k_gemm_nvfp4_pair(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                  const __grid_constant__ CUtensorMap tm_sfa, const __grid_constant__ CUtensorMap tm_sfb, const GemmParams p) {
+  using C = PairCfg;
+  constexpr int BN = 256;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t s_a = smem_base;
+  const uint32_t s_b = s_a + C::kStages * C::kABytes;
+  const uint32_t s_sfa = s_b + C::kStages * C::kBBytes;
+  const uint32_t s_sfb = s_sfa + C::kStages * C::kSfaBytes;
+  const uint32_t s_bar = s_sfb + C::kStages * C::kSfbBytes;
+  const uint32_t bar_full = s_bar;
+  const uint32_t bar_empty = bar_full + 8 * C::kStages;
+  const uint32_t bar_acc_full = bar_empty + 8 * C::kStages;
+  const uint32_t bar_acc_empty = bar_acc_full + 8;
+  const uint32_t s_tmem_slot = bar_acc_empty + 8;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::kStages; ++s) {
+      mbar_init(bar_full + 8 * s, 2);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    mbar_init(bar_acc_full, 1);
+    mbar_init(bar_acc_empty, 8);
+    mbar_init_fence();
+  }
+  if (warp == 1) tmem_alloc_pair<512>(s_tmem_slot);
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  tc_fence_after();
+  uint32_t tmem;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem) : "r"(s_tmem_slot));
+
+  const int n_pairs = p.n_tiles_ptr ? *p.n_tiles_ptr : p.n_tiles_static;
+  const int n_ntiles = p.N / BN;
+  const int nk = p.K / kStageK;
+  const long long total_items = (long long)n_pairs * n_ntiles;
+  const int chunks_per_row = p.K >> 6;
+  const long long first = blockIdx.x >> 1, stride = gridDim.x >> 1;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer (both CTAs, own halves)
+    if (lane == 0) {
+      uint32_t g = 0;
+      bool ok = true;
+      for (long long item = first; ok && item < total_items; item += stride) {
+        const int mt = (int)(item / n_ntiles), nt = (int)(item % n_ntiles);
+        const int e = p.tile_expert ? p.tile_expert[mt] : 0;
+        const int row0 = (p.tile_row0 ? p.tile_row0[mt] : mt * 256) + (int)rank * 128;
+        const int brow0 = e * p.N + nt * BN;
+        const int sfa_y = (row0 >> 7) * chunks_per_row;
+        const int sfb_y = (brow0 >> 7) * chunks_per_row;
+        for (int ks = 0; ks < nk; ++ks, ++g) {
+          const uint32_t s = g % C::kStages;
+          if (!mbar_wait(bar_empty + 8 * s, ((g / C::kStages) & 1) ^ 1)) { report(p.status, 201); ok = false; break; }
+          const uint32_t full = map_to_cta(bar_full + 8 * s, 0);
+          if (p.dbg & 1) { mbar_arrive_remote(full); continue; }
+          mbar_expect_tx_remote(full, C::kStageBytes);
+          tma_load_2d_pair(s_a + s * C::kABytes, &tm_a, full, ks * 128, row0);
+          tma_load_2d_pair(s_b + s * C::kBBytes, &tm_b, full, ks * 128, brow0 + (int)rank * 128);
+          tma_load_2d_pair(s_sfa + s * C::kSfaBytes, &tm_sfa, full, 0, sfa_y + ks * 4);
+          tma_load_2d_pair(s_sfb + s * C::kSfbBytes, &tm_sfb, full, 0, sfb_y + ks * 4);
+          tma_load_2d_pair(s_sfb + s * C::kSfbBytes + 4 * kSfChunk, &tm_sfb, full, 0, sfb_y + chunks_per_row + ks * 4);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (leader && lane == 0) {
+      constexpr uint32_t idesc = make_idesc_nvf4(256, BN);
+      constexpr uint32_t kHiOp = (1024u >> 4) | (1u << 14) | (2u << 29);
+      constexpr uint32_t kHiSf = (128u >> 4) | (1u << 14);
+      const uint32_t a_lo0 = ((s_a >> 4) & 0x3FFF) | (1u << 16), b_lo0 = ((s_b >> 4) & 0x3FFF) | (1u << 16);
+      const uint32_t sfa_lo0 = (s_sfa >> 4) & 0x3FFF, sfb_lo0 = (s_sfb >> 4) & 0x3FFF;
+      uint32_t s = 0, ph = 0, sfi = 0, it = 0;
+      bool ok = true;
+      for (long long item = first; ok && item < total_items; item += stride, ++it) {
+        if (!mbar_wait_cluster(bar_acc_empty, (it & 1) ^ 1)) { report(p.status, 202); break; }
+        tc_fence_after();
+        for (int ks = 0; ks < nk; ++ks) {
+          if (!mbar_wait_cluster(bar_full + 8 * s, ph)) { report(p.status, 203); ok = false; break; }
+          tc_fence_after();
+          const uint32_t sf_t = tmem + C::kSfBase + sfi * C::kSfCols;
+          if (!(p.dbg & 6)) {
+            const uint32_t sfa_lo = sfa_lo0 + s * (C::kSfaBytes >> 4), sfb_lo = sfb_lo0 + s * (C::kSfbBytes >> 4);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) tmem_cp_sf_pair(sf_t + 4 * q, ((uint64_t)kHiSf << 32) | (sfa_lo + q * (kSfChunk >> 4)));
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+              for (int q = 0; q < 4; ++q)
+                tmem_cp_sf_pair(sf_t + 16 + 8 * q + 4 * h, ((uint64_t)kHiSf << 32) | (sfb_lo + (h * 4 + q) * (kSfChunk >> 4)));
+          }
+          if (!(p.dbg & 2)) {
+            const uint32_t a_lo = a_lo0 + s * (C::kABytes >> 4), b_lo = b_lo0 + s * (C::kBBytes >> 4);
+            mma_nvf4_pair(tmem, ((uint64_t)kHiOp << 32) | a_lo, ((uint64_t)kHiOp << 32) | b_lo, idesc, sf_t, sf_t + 16, ks ? 1u : 0u);
+#pragma unroll
+            for (int q = 1; q < 4; ++q)
+              mma_nvf4_pair(tmem, ((uint64_t)kHiOp << 32) | (a_lo + 2 * q), ((uint64_t)kHiOp << 32) | (b_lo + 2 * q), idesc,
+                            sf_t + 4 * q, sf_t + 16 + 8 * q, 1u);
+          }
+          mma_commit_pair(bar_empty + 8 * s);
+          if (++s == C::kStages) { s = 0; ph ^= 1; }
+          sfi = (sfi + 1) & (kNumSfBuf - 1);
+        }
+        if (ok) mma_commit_pair(bar_acc_full);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (both CTAs: own 128 rows x 256 columns)
+    const int quad = warp & 3;
+    const int r_in_tile = quad * 32 + lane;
+    const uint32_t acc_empty_leader = map_to_cta(bar_acc_empty, 0);
+    uint32_t it = 0;
+    for (long long item = first; item < total_items; item += stride, ++it) {
+      const int mt = (int)(item / n_ntiles), nt = (int)(item % n_ntiles);
+      const int e = p.tile_expert ? p.tile_expert[mt] : 0;
+      const int row0 = (p.tile_row0 ? p.tile_row0[mt] : mt * 256) + (int)rank * 128;
+      const int pair_rows = p.tile_rows ? p.tile_rows[mt] : min(256, p.M - mt * 256);
+      const int rows = min(128, max(0, pair_rows - (int)rank * 128));
+      int okw = 1;
+      if (lane == 0) okw = mbar_wait_cluster(bar_acc_full, it & 1) ? 1 : 0;
+      okw = __shfl_sync(0xFFFFFFFFu, okw, 0);
+      if (!okw) { if (lane == 0) report(p.status, 204); break; }
+      tc_fence_after();
+      const uint32_t taddr = tmem + ((uint32_t)(quad * 32) << 16);
+      epilogue_tile<MODE, BN>(p, taddr, e, (size_t)row0 + r_in_tile, r_in_tile < rows, nt, [&]() {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_remote(acc_empty_leader);
+      });
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    __syncwarp();
+    tmem_dealloc_pair<512>(tmem);
   }
 }
 
@@ -326,6 +636,45 @@ int make_operand_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t
   return r == CUDA_SUCCESS ? 0 : 700 + (int)r;
 }
 
+// Scale-factor tiles as a 2-D tensor of 512-byte chunks: [n_chunks, 128 x u32]; a box is 4 consecutive chunks.
+int make_sf_map(CUtensorMap* map, const void* base, uint64_t n_chunks) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return 701;
+  cuuint64_t dims[2] = {128, n_chunks};
+  cuuint64_t strides[1] = {512};
+  cuuint32_t box[2] = {128, 4};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : 700 + (int)r;
+}
+
+template <int MODE>
+static int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tsa, const CUtensorMap& tsb,
+                       const GemmParams& p, int grid, cudaStream_t st) {
+  auto kern = k_gemm_nvfp4_pair<MODE>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg::kSmemBytes);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  kern<<<grid, kGemmThreads, PairCfg::kSmemBytes, st>>>(ta, tb, tsa, tsb, p);
+  return (int)cudaGetLastError();
+}
+
+// grid = 2 CTAs per work-item stream, at most one pair per two SMs
+int launch_gemm_nvfp4_pair(int mode, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tsa, const CUtensorMap& tsb,
+                           const GemmParams& p, int n_clusters, cudaStream_t st) {
+  if (n_clusters <= 0) return 0;
+  if (p.K % kStageK != 0 || p.N % 256 != 0) return 702;
+  const int grid = 2 * n_clusters;
+  if (mode == kGemmFc1) return launch_pair<kGemmFc1>(ta, tb, tsa, tsb, p, grid, st);
+  if (mode == kGemmFc2) return launch_pair<kGemmFc2>(ta, tb, tsa, tsb, p, grid, st);
+  return launch_pair<kGemmDense>(ta, tb, tsa, tsb, p, grid, st);
+}
+
 template <int MODE, int BN>
 static int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid, cudaStream_t st) {
   auto kern = k_gemm_nvfp4<MODE, BN>;
@@ -335,7 +684,7 @@ static int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const GemmPa
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  kern<<<grid, kGemmThreads, GemmCfg<BN>::kSmemBytes, st>>>(ta, tb, p);
+  kern<<<grid, gemm_threads<BN>(), GemmCfg<BN>::kSmemBytes, st>>>(ta, tb, p);
   return (int)cudaGetLastError();
 }
 

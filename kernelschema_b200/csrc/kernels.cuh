@@ -17,7 +17,10 @@ struct RouteMapBuffers {
   int32_t* tile_expert;    // [tile_capacity]
   int32_t* tile_row0;      // [tile_capacity]
   int32_t* tile_rows;      // [tile_capacity] valid rows of the tile (1..128)
-  int32_t* totals;         // {n_tiles, rows in use (multiple of 128), valid routes}
+  int32_t* totals;         // {n_tiles, rows in use (multiple of 128), valid routes, n_pairs}
+  int32_t* pair_expert;    // [tile_capacity] 256-row items of the CTA-pair GEMM (may be null: not built)
+  int32_t* pair_row0;      // [tile_capacity]
+  int32_t* pair_rows;      // [tile_capacity] valid rows of the pair (1..256)
   int32_t* row_of;         // [T, K'] permuted row of a route, -1 when invalid
   int32_t* tok_of_row;     // [row_capacity] token of a permuted row, -1 for padding
   float* weight_of_row;    // [row_capacity] routing weight of a permuted row
@@ -47,6 +50,7 @@ struct GemmParams {
   int act_type;                 // 3 = SwiGLU form gate*sigmoid(alpha*gate)*(up+beta); 10 = SiTU
   const float* out_scale;       // per expert multiplier of the FC2 accumulator (null = 1)
   float dense_alpha;
+  int dbg;                      // timing experiments only: 1 = no loads, 2 = no MMA/cp, 4 = no scale-factor cp, 8 = no epilogue stores
   int32_t* status;              // device word; first non-zero code sticks (bounded waits report here)
 };
 
@@ -66,6 +70,9 @@ int launch_gather_rows(const void* hid_q, const void* hid_sf, int hid_sf_tiled, 
 int launch_finalize(const void* rout, const int32_t* row_of, const float* weight_of_row, int64_t T, int KK, int H, void* out,
                     int64_t out_stride, cudaStream_t st);
 int make_operand_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_rows);
+int make_sf_map(CUtensorMap* map, const void* base, uint64_t n_chunks);
+int launch_gemm_nvfp4_pair(int mode, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tsa, const CUtensorMap& tsb,
+                           const GemmParams& p, int n_clusters, cudaStream_t st);
 int launch_gemm_nvfp4(int mode, int bn, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid,
                       cudaStream_t st);
 

@@ -66,11 +66,13 @@ __global__ void __launch_bounds__(256) k_route_hist(RouteView r, int etot, int32
 __global__ void __launch_bounds__(1024) k_route_scan(int etot, int nblk, int32_t* __restrict__ block_hist,
                                                      int32_t* __restrict__ counts, int32_t* __restrict__ seg_start,
                                                      int32_t* __restrict__ tile_expert, int32_t* __restrict__ tile_row0,
-                                                     int32_t* __restrict__ tile_rows, int32_t* __restrict__ totals) {
-  __shared__ int warp_pad[32], warp_tiles[32], warp_cnt[32];
-  __shared__ int carry[3];
+                                                     int32_t* __restrict__ tile_rows, int32_t* __restrict__ totals,
+                                                     int32_t* __restrict__ pair_expert, int32_t* __restrict__ pair_row0,
+                                                     int32_t* __restrict__ pair_rows) {
+  __shared__ int warp_pad[32], warp_tiles[32], warp_cnt[32], warp_pairs[32];
+  __shared__ int carry[4];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  if (threadIdx.x < 3) carry[threadIdx.x] = 0;
+  if (threadIdx.x < 4) carry[threadIdx.x] = 0;
   __syncthreads();
   for (int e0 = 0; e0 < etot; e0 += blockDim.x) {
     const int e = e0 + threadIdx.x;
@@ -85,20 +87,23 @@ __global__ void __launch_bounds__(1024) k_route_scan(int etot, int nblk, int32_t
     }
     const int ntile = (cnt + 127) >> 7;
     const int pad = ntile << 7;
-    int ip = pad, it = ntile, ic = cnt;        // inclusive warp scans
+    const int npair = (ntile + 1) >> 1;        // 256-row work items of the CTA-pair GEMM
+    int ip = pad, it = ntile, ic = cnt, iq = npair;        // inclusive warp scans
 #pragma unroll
     for (int off = 1; off < 32; off <<= 1) {
       const int a = __shfl_up_sync(0xFFFFFFFFu, ip, off);
       const int b = __shfl_up_sync(0xFFFFFFFFu, it, off);
       const int c = __shfl_up_sync(0xFFFFFFFFu, ic, off);
-      if (lane >= off) { ip += a; it += b; ic += c; }
+      const int d = __shfl_up_sync(0xFFFFFFFFu, iq, off);
+      if (lane >= off) { ip += a; it += b; ic += c; iq += d; }
     }
-    if (lane == 31) { warp_pad[warp] = ip; warp_tiles[warp] = it; warp_cnt[warp] = ic; }
+    if (lane == 31) { warp_pad[warp] = ip; warp_tiles[warp] = it; warp_cnt[warp] = ic; warp_pairs[warp] = iq; }
     __syncthreads();
-    int bp = carry[0], bt = carry[1];
-    for (int w = 0; w < warp; ++w) { bp += warp_pad[w]; bt += warp_tiles[w]; }
+    int bp = carry[0], bt = carry[1], bq = carry[3];
+    for (int w = 0; w < warp; ++w) { bp += warp_pad[w]; bt += warp_tiles[w]; bq += warp_pairs[w]; }
     const int start = bp + ip - pad;
     const int tile0 = bt + it - ntile;
+    const int pair0 = bq + iq - npair;
     if (e < etot) {
       seg_start[e] = start;
       for (int j = 0; j < ntile; ++j) {
@@ -106,6 +111,12 @@ __global__ void __launch_bounds__(1024) k_route_scan(int etot, int nblk, int32_t
         tile_row0[tile0 + j] = start + (j << 7);
         tile_rows[tile0 + j] = min(128, cnt - (j << 7));
       }
+      if (pair_expert)
+        for (int j = 0; j < npair; ++j) {
+          pair_expert[pair0 + j] = e;
+          pair_row0[pair0 + j] = start + (j << 8);
+          pair_rows[pair0 + j] = min(256, cnt - (j << 8));
+        }
     }
     __syncthreads();
     if (threadIdx.x == blockDim.x - 1) {
@@ -114,6 +125,7 @@ __global__ void __launch_bounds__(1024) k_route_scan(int etot, int nblk, int32_t
       carry[0] = bp + ip;
       carry[1] = bt + it;
       carry[2] += tc;
+      carry[3] = bq + iq;
     }
     __syncthreads();
   }
@@ -122,6 +134,7 @@ __global__ void __launch_bounds__(1024) k_route_scan(int etot, int nblk, int32_t
     totals[0] = carry[1];   // number of 128-row tiles
     totals[1] = carry[0];   // rows of the permuted buffer in use (multiple of 128)
     totals[2] = carry[2];   // valid routes
+    totals[3] = carry[3];   // number of 256-row pair items
   }
 }
 
@@ -177,7 +190,7 @@ int launch_route_map(const int32_t* ids, const float* scores, int64_t T, int K, 
   const size_t smem = sizeof(int) * kRouteWarps * (size_t)etot;
   if (nblk > 0) k_route_hist<<<nblk, 256, smem, st>>>(r, etot, b.block_hist);
   k_route_scan<<<1, 1024, 0, st>>>(etot, nblk, b.block_hist, b.counts, b.seg_start, b.tile_expert, b.tile_row0, b.tile_rows,
-                                   b.totals);
+                                   b.totals, b.pair_expert, b.pair_row0, b.pair_rows);
   if (nblk > 0)
     k_route_scatter<<<nblk, 256, smem, st>>>(r, scores, etot, b.block_hist, b.seg_start, b.row_of, b.tok_of_row,
                                             b.weight_of_row);

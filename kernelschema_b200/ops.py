@@ -188,7 +188,10 @@ class MoELayer:
             tile_expert=view(v.tile_expert, 4 * tiles, torch.int32, (tiles,)),
             tile_row0=view(v.tile_row0, 4 * tiles, torch.int32, (tiles,)),
             tile_rows=view(v.tile_rows, 4 * tiles, torch.int32, (tiles,)),
-            totals=view(v.totals, 12, torch.int32, (3,)),
+            totals=view(v.totals, 16, torch.int32, (4,)),
+            pair_expert=view(v.pair_expert, 4 * tiles, torch.int32, (tiles,)),
+            pair_row0=view(v.pair_row0, 4 * tiles, torch.int32, (tiles,)),
+            pair_rows=view(v.pair_rows, 4 * tiles, torch.int32, (tiles,)),
             row_of=view(v.row_of, 4 * c.max_tokens * kk, torch.int32, (c.max_tokens, kk)),
             tok_of_row=view(v.tok_of_row, 4 * rows, torch.int32, (rows,)),
             weight_of_row=view(v.weight_of_row, 4 * rows, torch.float32, (rows,)),

@@ -35,7 +35,7 @@ def test_struct_sizes_match_header(lib):
     from kernelschema_b200 import _lib
     assert C.sizeof(_lib.Config) == 16 * 4
     assert C.sizeof(_lib.Args) == 8 + 8 * 4 + 8 + 8 * 10 + 8 + 16
-    assert C.sizeof(_lib.WorkspaceView) == 14 * 8 + 16
+    assert C.sizeof(_lib.WorkspaceView) == 14 * 8 + 16 + 24
 
 
 def test_bad_config_is_refused_without_a_device(lib):

@@ -114,7 +114,17 @@ def test_route_map_matches_oracle(t, k, e, shared, offset):
     torch.cuda.synchronize()
     ws = layer.workspace()
     m = o.route_map(ids, e, 128, expert_offset=offset, shared_experts=shared)
-    n_tiles, rows, valid = (int(v) for v in ws["totals"].cpu())
+    n_tiles, rows, valid, n_pairs = (int(v) for v in ws["totals"].cpu())
+    # 256-row pair items: consecutive tile pairs of one expert
+    pe, pr0, prw = [], [], []
+    for e_ in range(e + shared):
+        c = int(m["counts"][e_])
+        for j in range(0, c, 256):
+            pe.append(e_); pr0.append(int(m["seg_start"][e_]) + j); prw.append(min(256, c - j))
+    assert n_pairs == len(pe)
+    assert ws["pair_expert"][:n_pairs].cpu().tolist() == pe
+    assert ws["pair_row0"][:n_pairs].cpu().tolist() == pr0
+    assert ws["pair_rows"][:n_pairs].cpu().tolist() == prw
     assert n_tiles == len(m["tile_expert"]) and rows == m["seg_start"][-1] and valid == (m["row_of"] >= 0).sum()
     assert np.array_equal(ws["counts"].cpu().numpy(), m["counts"])
     assert np.array_equal(ws["seg_start"].cpu().numpy(), m["seg_start"])
@@ -136,6 +146,6 @@ def test_route_map_all_invalid():
     layer.route_map(ids, torch.zeros(64, 8, device="cuda"))
     torch.cuda.synchronize()
     ws = layer.workspace()
-    assert ws["totals"].cpu().tolist() == [0, 0, 0]
+    assert ws["totals"].cpu().tolist() == [0, 0, 0, 0]
     assert bool((ws["row_of"][:64] == -1).all())
     layer.close()

@@ -31,7 +31,9 @@ def _dense_case(m, n, k, seed, tile_n, alpha=1.0, a_scale=1.0):
 
 @pytest.mark.parametrize("m,n,k,tile_n", [(128, 128, 256, 128), (128, 256, 256, 256), (192, 256, 512, 128),
                                           (192, 256, 512, 256), (1000, 1024, 2048, 128), (1000, 1024, 2048, 256),
-                                          (5, 128, 7168, 128), (2048, 2048, 2048, 256)])
+                                          (5, 128, 7168, 128), (2048, 2048, 2048, 256), (256, 256, 256, 512),
+                                          (192, 256, 512, 512), (1000, 1024, 2048, 512), (5, 256, 7168, 512),
+                                          (2048, 2048, 2048, 512), (4096 + 128, 512, 1024, 512)])
 def test_dense_gemm_matches_oracle(m, n, k, tile_n):
     got, ref = _dense_case(m, n, k, seed=m + n + k, tile_n=tile_n, alpha=0.75)
     r = compare_outputs(got, ref)

@@ -110,13 +110,13 @@ def test_layer_matches_oracle_extensions(kw):
     assert_layer_parity(got, o.moe_expected(p), str(kw))
 
 
-def test_tile_n_256_variant_agrees():
+def test_tile_variants_agree():
     import kernelschema_b200 as ks
     from gpu_util import to_dev
     p = make_moe_case(5, 400, 512, 256, 8, 2)
     ref = o.moe_expected(p)
     ids, w = p["topk_ids"]
-    for bn in (128, 256):
+    for bn in (128, 256, 512):
         layer = ks.MoELayer(512, 256, 8, 2, 400, tile_n=bn)
         out = torch.empty(400, 512, dtype=torch.bfloat16, device="cuda")
         layer.run(to_dev(ids), to_dev(w), to_dev(p["hidden_states"]), to_dev(p["hidden_states_scale"]),
