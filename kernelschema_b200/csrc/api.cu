@@ -279,7 +279,7 @@ int b200moe_router_logits(const void* x, const void* w, int64_t T, int32_t H, in
 
 int b200moe_gemm_nvfp4(const void* a_q, const void* a_sf, const void* b_q, const void* b_sf, float alpha, void* out, int64_t m,
                        int64_t n, int64_t k, int64_t out_stride, int32_t tile_n, int32_t* status, void* stream) {
-  const int bn = tile_n ? tile_n : 128;
+  const int bn = tile_n ? tile_n : (n % 256 == 0 ? 256 : 128);
   if (bn != 128 && bn != 256 && bn != 512) return fail(760, "gemm: tile_n must be 0, 128, 256 or 512");
   if (m < 0 || n <= 0 || k <= 0 || k % 256 || n % (bn == 512 ? 256 : bn))
     return fail(761, "gemm: need K %% 256 == 0 and N %% tile_n == 0 (N %% 256 == 0 for the CTA-pair tile)");
@@ -342,7 +342,7 @@ int b200moe_create(const b200moe_config* cfg, b200moe_handle* out) {
   h->kk = cfg->top_k + cfg->num_shared_experts;
   h->row_capacity = p.row_capacity;
   h->tile_capacity = p.tile_capacity;
-  h->bn = cfg->tile_n ? cfg->tile_n : 128;
+  h->bn = cfg->tile_n ? cfg->tile_n : ((2 * cfg->intermediate) % 256 == 0 && cfg->hidden % 256 == 0 ? 256 : 128);
   h->n_clusters = 0;
   if ((2 * cfg->intermediate) % (h->bn == 512 ? 256 : h->bn) || cfg->hidden % (h->bn == 512 ? 256 : h->bn)) {
     delete h;

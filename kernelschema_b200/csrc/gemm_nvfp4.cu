@@ -455,8 +455,10 @@ struct PairCfg {
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
 };
 
+constexpr int kPairThreads = 32 * 11;    // TMA, MMA, scale-factor copier, 8 epilogue warps
+
 template <int MODE>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
 k_gemm_nvfp4_pair(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                   const __grid_constant__ CUtensorMap tm_sfa, const __grid_constant__ CUtensorMap tm_sfb, const GemmParams p) {
   using C = PairCfg;
@@ -468,10 +470,11 @@ k_gemm_nvfp4_pair(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   const uint32_t s_sfa = s_b + C::kStages * C::kBBytes;
   const uint32_t s_sfb = s_sfa + C::kStages * C::kSfaBytes;
   const uint32_t s_bar = s_sfb + C::kStages * C::kSfbBytes;
-  const uint32_t bar_full = s_bar;
-  const uint32_t bar_empty = bar_full + 8 * C::kStages;
-  const uint32_t bar_acc_full = bar_empty + 8 * C::kStages;
-  const uint32_t bar_acc_empty = bar_acc_full + 8;
+  const uint32_t bar_full = s_bar;                            // leader: 2 producer arrivals + both CTAs' TMA bytes
+  const uint32_t bar_sf = bar_full + 8 * C::kStages;          // leader: scale factors copied into both CTAs' TMEM
+  const uint32_t bar_empty = bar_sf + 8 * C::kStages;         // both CTAs: MMAs of the stage retired
+  const uint32_t bar_acc_full = bar_empty + 8 * C::kStages;   // both CTAs
+  const uint32_t bar_acc_empty = bar_acc_full + 8;            // leader: 16 epilogue warps of the pair
   const uint32_t s_tmem_slot = bar_acc_empty + 8;
 
   const int warp = threadIdx.x >> 5;
@@ -482,10 +485,11 @@ k_gemm_nvfp4_pair(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::kStages; ++s) {
       mbar_init(bar_full + 8 * s, 2);
+      mbar_init(bar_sf + 8 * s, 1);
       mbar_init(bar_empty + 8 * s, 1);
     }
     mbar_init(bar_acc_full, 1);
-    mbar_init(bar_acc_empty, 8);
+    mbar_init(bar_acc_empty, 16);
     mbar_init_fence();
   }
   if (warp == 1) tmem_alloc_pair<512>(s_tmem_slot);
@@ -506,8 +510,9 @@ k_gemm_nvfp4_pair(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer (both CTAs, own halves)
     if (lane == 0) {
-      uint32_t g = 0;
+      uint32_t s = 0, ph = 1;
       bool ok = true;
+      const uint32_t full0 = map_to_cta(bar_full, 0);
       for (long long item = first; ok && item < total_items; item += stride) {
         const int mt = (int)(item / n_ntiles), nt = (int)(item % n_ntiles);
         const int e = p.tile_expert ? p.tile_expert[mt] : 0;
@@ -515,38 +520,36 @@ k_gemm_nvfp4_pair(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         const int brow0 = e * p.N + nt * BN;
         const int sfa_y = (row0 >> 7) * chunks_per_row;
         const int sfb_y = (brow0 >> 7) * chunks_per_row;
-        for (int ks = 0; ks < nk; ++ks, ++g) {
-          const uint32_t s = g % C::kStages;
-          if (!mbar_wait(bar_empty + 8 * s, ((g / C::kStages) & 1) ^ 1)) { report(p.status, 201); ok = false; break; }
-          const uint32_t full = map_to_cta(bar_full + 8 * s, 0);
-          if (p.dbg & 1) { mbar_arrive_remote(full); continue; }
-          mbar_expect_tx_remote(full, C::kStageBytes);
-          tma_load_2d_pair(s_a + s * C::kABytes, &tm_a, full, ks * 128, row0);
-          tma_load_2d_pair(s_b + s * C::kBBytes, &tm_b, full, ks * 128, brow0 + (int)rank * 128);
-          tma_load_2d_pair(s_sfa + s * C::kSfaBytes, &tm_sfa, full, 0, sfa_y + ks * 4);
-          tma_load_2d_pair(s_sfb + s * C::kSfbBytes, &tm_sfb, full, 0, sfb_y + ks * 4);
-          tma_load_2d_pair(s_sfb + s * C::kSfbBytes + 4 * kSfChunk, &tm_sfb, full, 0, sfb_y + chunks_per_row + ks * 4);
+        for (int ks = 0; ks < nk; ++ks) {
+          if (!mbar_wait(bar_empty + 8 * s, ph)) { report(p.status, 201); ok = false; break; }
+          const uint32_t full = full0 + 8 * s;
+          if (p.dbg & 1) {
+            mbar_arrive_remote(full);
+          } else {
+            mbar_expect_tx_remote(full, C::kStageBytes);
+            tma_load_2d_pair(s_a + s * C::kABytes, &tm_a, full, ks * 128, row0);
+            tma_load_2d_pair(s_b + s * C::kBBytes, &tm_b, full, ks * 128, brow0 + (int)rank * 128);
+            tma_load_2d_pair(s_sfa + s * C::kSfaBytes, &tm_sfa, full, 0, sfa_y + ks * 4);
+            tma_load_2d_pair(s_sfb + s * C::kSfbBytes, &tm_sfb, full, 0, sfb_y + ks * 4);
+            tma_load_2d_pair(s_sfb + s * C::kSfbBytes + 4 * kSfChunk, &tm_sfb, full, 0, sfb_y + chunks_per_row + ks * 4);
+          }
+          if (++s == C::kStages) { s = 0; ph ^= 1; }
         }
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer (leader CTA only)
+  } else if (warp == 2) {
+    // ------------------------------------------------------------------ scale-factor copier (leader; acts on both CTAs)
     if (leader && lane == 0) {
-      constexpr uint32_t idesc = make_idesc_nvf4(256, BN);
-      constexpr uint32_t kHiOp = (1024u >> 4) | (1u << 14) | (2u << 29);
       constexpr uint32_t kHiSf = (128u >> 4) | (1u << 14);
-      const uint32_t a_lo0 = ((s_a >> 4) & 0x3FFF) | (1u << 16), b_lo0 = ((s_b >> 4) & 0x3FFF) | (1u << 16);
       const uint32_t sfa_lo0 = (s_sfa >> 4) & 0x3FFF, sfb_lo0 = (s_sfb >> 4) & 0x3FFF;
-      uint32_t s = 0, ph = 0, sfi = 0, it = 0;
+      uint32_t s = 0, ph = 0, sfi = 0;
       bool ok = true;
-      for (long long item = first; ok && item < total_items; item += stride, ++it) {
-        if (!mbar_wait_cluster(bar_acc_empty, (it & 1) ^ 1)) { report(p.status, 202); break; }
-        tc_fence_after();
+      for (long long item = first; ok && item < total_items; item += stride) {
         for (int ks = 0; ks < nk; ++ks) {
-          if (!mbar_wait_cluster(bar_full + 8 * s, ph)) { report(p.status, 203); ok = false; break; }
+          if (!mbar_wait_cluster(bar_full + 8 * s, ph)) { report(p.status, 205); ok = false; break; }
           tc_fence_after();
-          const uint32_t sf_t = tmem + C::kSfBase + sfi * C::kSfCols;
-          if (!(p.dbg & 6)) {
+          if (!(p.dbg & 4)) {
+            const uint32_t sf_t = tmem + C::kSfBase + sfi * C::kSfCols;
             const uint32_t sfa_lo = sfa_lo0 + s * (C::kSfaBytes >> 4), sfb_lo = sfb_lo0 + s * (C::kSfbBytes >> 4);
 #pragma unroll
             for (int q = 0; q < 4; ++q) tmem_cp_sf_pair(sf_t + 4 * q, ((uint64_t)kHiSf << 32) | (sfa_lo + q * (kSfChunk >> 4)));
@@ -556,7 +559,28 @@ k_gemm_nvfp4_pair(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
               for (int q = 0; q < 4; ++q)
                 tmem_cp_sf_pair(sf_t + 16 + 8 * q + 4 * h, ((uint64_t)kHiSf << 32) | (sfb_lo + (h * 4 + q) * (kSfChunk >> 4)));
           }
+          mma_commit_pair_local(bar_sf + 8 * s);
+          if (++s == C::kStages) { s = 0; ph ^= 1; }
+          sfi = (sfi + 1) & (kNumSfBuf - 1);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (leader && lane == 0) {
+      constexpr uint32_t idesc = make_idesc_nvf4(256, BN);
+      constexpr uint32_t kHiOp = (1024u >> 4) | (1u << 14) | (2u << 29);
+      const uint32_t a_lo0 = ((s_a >> 4) & 0x3FFF) | (1u << 16), b_lo0 = ((s_b >> 4) & 0x3FFF) | (1u << 16);
+      uint32_t s = 0, ph = 0, sfi = 0, it = 0;
+      bool ok = true;
+      for (long long item = first; ok && item < total_items; item += stride, ++it) {
+        if (!mbar_wait_cluster(bar_acc_empty, (it & 1) ^ 1)) { report(p.status, 202); break; }
+        tc_fence_after();
+        for (int ks = 0; ks < nk; ++ks) {
+          if (!mbar_wait(bar_sf + 8 * s, ph)) { report(p.status, 203); ok = false; break; }
+          tc_fence_after();
           if (!(p.dbg & 2)) {
+            const uint32_t sf_t = tmem + C::kSfBase + sfi * C::kSfCols;
             const uint32_t a_lo = a_lo0 + s * (C::kABytes >> 4), b_lo = b_lo0 + s * (C::kBBytes >> 4);
             mma_nvf4_pair(tmem, ((uint64_t)kHiOp << 32) | a_lo, ((uint64_t)kHiOp << 32) | b_lo, idesc, sf_t, sf_t + 16, ks ? 1u : 0u);
 #pragma unroll
@@ -574,6 +598,7 @@ k_gemm_nvfp4_pair(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   } else {
     // ------------------------------------------------------------------ epilogue (both CTAs: own 128 rows x 256 columns)
     const int quad = warp & 3;
+    const int group = (warp - 3) >> 2;
     const int r_in_tile = quad * 32 + lane;
     const uint32_t acc_empty_leader = map_to_cta(bar_acc_empty, 0);
     uint32_t it = 0;
@@ -588,8 +613,8 @@ k_gemm_nvfp4_pair(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       okw = __shfl_sync(0xFFFFFFFFu, okw, 0);
       if (!okw) { if (lane == 0) report(p.status, 204); break; }
       tc_fence_after();
-      const uint32_t taddr = tmem + ((uint32_t)(quad * 32) << 16);
-      epilogue_tile<MODE, BN>(p, taddr, e, (size_t)row0 + r_in_tile, r_in_tile < rows, nt, [&]() {
+      const uint32_t taddr = tmem + ((uint32_t)(quad * 32) << 16) + group * 128;
+      epilogue_cols128<MODE>(p, taddr, e, (size_t)row0 + r_in_tile, r_in_tile < rows, nt * BN + group * 128, [&]() {
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive_remote(acc_empty_leader);
@@ -660,7 +685,7 @@ static int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUten
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  kern<<<grid, kGemmThreads, PairCfg::kSmemBytes, st>>>(ta, tb, tsa, tsb, p);
+  kern<<<grid, kPairThreads, PairCfg::kSmemBytes, st>>>(ta, tb, tsa, tsb, p);
   return (int)cudaGetLastError();
 }
 

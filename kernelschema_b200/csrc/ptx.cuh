@@ -149,8 +149,9 @@ DEV uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
   return r;
 }
+// No release semantics needed: the bytes announced here are written by TMA, which orders them with its own completion.
 DEV void mbar_expect_tx_remote(uint32_t cluster_bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.release.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(cluster_bar), "r"(bytes) : "memory");
+  asm volatile("mbarrier.arrive.expect_tx.relaxed.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(cluster_bar), "r"(bytes) : "memory");
 }
 DEV void mbar_arrive_remote(uint32_t cluster_bar) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
@@ -199,6 +200,10 @@ DEV void mma_nvf4_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32
 }
 DEV void tmem_cp_sf_pair(uint32_t dst_tmem, uint64_t sdesc) {   // in each CTA: own shared memory -> own TMEM
   asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(dst_tmem), "l"(sdesc) : "memory");
+}
+// Arrive on one barrier (cluster address, here always the issuing CTA's own) once all tcgen05 ops issued so far are done.
+DEV void mma_commit_pair_local(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 // Arrive on the barrier at the same shared-memory offset in both CTAs of the pair once all tcgen05 ops issued so far are done.
 DEV void mma_commit_pair(uint32_t bar) {
