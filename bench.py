@@ -347,6 +347,34 @@ def run_gpu(args, wl):
         dist.destroy_process_group()
 
 
+def run_dense(args):
+    """Single-expert dense NVFP4 GEMM (A quantised on the device, B pre-quantised): the mainloop in isolation."""
+    import torch
+    import kernelschema_b200 as ks
+    m, n, k = (int(v) for v in args.dense.split(","))
+    a = torch.randn(m, k, device="cuda").to(torch.bfloat16)
+    b = (torch.randn(n, k, device="cuda") * 0.02).to(torch.bfloat16)
+    bq, bsf = ks.nvfp4_quantize(b, 1.0, tiled_scales=True)
+    aq, asf = ks.nvfp4_quantize(a, 1.0, tiled_scales=True)
+    out = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+    for _ in range(max(3, args.warmup)):
+        ks.mm_nvfp4(aq, asf, bq, bsf, out=out, tile_n=args.tile_n)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        ks.mm_nvfp4(aq, asf, bq, bsf, out=out, tile_n=args.tile_n)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    tf = 2.0 * m * n * k / (ms * 1e-3) / 1e12
+    print(json.dumps(dict(metric="nvfp4_dense_gemm_tflops", value=tf, unit="TFLOP/s", n_gpus=1, steps=args.steps, warmup=args.warmup,
+                          ms_per_step=ms, higher_is_better=True, dtype="nvfp4", data="synthetic",
+                          config=dict(workload=f"dense_nvfp4_gemm_{m}x{n}x{k}", tile_n=args.tile_n,
+                                      kernel_switches=os.environ.get("B200MOE_DBG", "0")),
+                          frac_of_nominal_fp4=tf / FP4_NOMINAL_TFLOPS)))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -355,7 +383,11 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="dsv3", choices=sorted(WORKLOADS))
     ap.add_argument("--zipf", type=float, default=None, help="override the workload's Zipf exponent of the router bias (0 = uniform)")
+    ap.add_argument("--dense", default=None, metavar="M,N,K", help="time the dense NVFP4 GEMM of this shape instead of the layer")
+    ap.add_argument("--tile-n", type=int, default=0, help="GEMM tile for --dense (0 = default, 128, 256, 512 = CTA pair)")
     args = ap.parse_args()
+    if args.dense:
+        return run_dense(args)
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     wl = dict(WORKLOADS[args.workload])
     if args.zipf is not None:
