@@ -320,6 +320,12 @@ def run_gpu(args, wl):
                     peak_source=f"4 x bf16_tflops_sustained of {pk['source']} MEASURED_PEAKS (FP4:bf16 nominal ratio)",
                     frac_of_nominal_fp4=achieved / FP4_NOMINAL_TFLOPS, traffic=None,
                     layer_frac_of_nominal_fp4=tflops / FP4_NOMINAL_TFLOPS)
+    ep_stage = None
+    if world > 1:
+        owner.profile = True
+        resident()
+        ep_stage = owner.stage_ms()
+        owner.profile = False
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -335,6 +341,8 @@ def run_gpu(args, wl):
                 e2e=dict(value=tflops_e2e, unit="TFLOP/s", h2d_bytes_per_step=x_host.numel() * 2, d2h_bytes_per_step=out_host.numel() * 2,
                          ms_per_step=ms_e2e / args.steps),
                 gpu_launches=launches * args.steps, device_status=status, clocks=clocks)
+    if ep_stage:
+        line["stage_ms"] = ep_stage
     if stage:
         line["stage_ms"] = stage
     if roof:

@@ -60,6 +60,7 @@ class ExpertParallelMoE:
         self._combine_rows = combine_rows or self._cuda_combine_rows
         self._shared_rows = shared_rows or self._cuda_shared_rows
         self._routed = self._shared = None
+        self.profile = False
         # route map memset+3, permute, FC1, FC2, combine for the routed rows (+ the same for the shared expert) + final combine
         self.launches_per_step = 7 * (2 if num_shared_experts else 1) + 1
 
@@ -88,6 +89,11 @@ class ExpertParallelMoE:
         from .ops import combine
         combine(rows, row_of, weight_of_row, out)
 
+    def _side_stream(self, dev):
+        if getattr(self, "_side", None) is None:
+            self._side = torch.cuda.Stream(device=dev)
+        return self._side
+
     def status(self) -> int:
         code = 0
         for layer in (self._routed, self._shared):
@@ -102,6 +108,15 @@ class ExpertParallelMoE:
         scale_gate, scale_out) for the same experts. Returns bf16 [T, H]."""
         dev = hq.device
         t = hq.shape[0]
+        marks = []
+
+        def mark(name):
+            if self.profile and dev.type == "cuda":
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record()
+                marks.append((name, ev))
+
+        mark("start")
         plan = build_dispatch(ids, self.e_local, self.world)
         send_counts_t = plan["send_counts"]
         recv_counts_t = torch.empty_like(send_counts_t)
@@ -111,27 +126,54 @@ class ExpertParallelMoE:
         n_send, n_recv = sum(send_counts), sum(recv_counts)
         if n_recv > self.recv_capacity:
             raise RuntimeError(f"rank {self.rank} received {n_recv} rows, capacity is {self.recv_capacity}")
+        mark("plan+counts")
+        slots = self.k + (1 if self.s else 0)
+        rows_all = torch.empty((n_send + t * (1 if self.s else 0), self.h), dtype=torch.bfloat16, device=dev)
+        side = None
+        if self.s:
+            # the shared experts only need this rank's own tokens: run them on a side stream under the exchange
+            if dev.type == "cuda":
+                side = self._side_stream(dev)
+                side.wait_stream(torch.cuda.current_stream(dev))
+                with torch.cuda.stream(side):
+                    self._shared_rows(hq, hs, w1q, w1s, w2q, w2s, rows_all[n_send:], kw)
+            else:
+                self._shared_rows(hq, hs, w1q, w1s, w2q, w2s, rows_all[n_send:], kw)
         tok = plan["order"] // self.k
         rows_q = exchange(hq.index_select(0, tok), send_counts, recv_counts, self.group)
         rows_sf = exchange(hs.index_select(0, tok), send_counts, recv_counts, self.group)
         local_e = exchange(plan["local_expert"], send_counts, recv_counts, self.group)
+        mark("dispatch")
         # result rows of the routed experts for the rows received, then back to their sources
         res = torch.empty((n_recv, self.h), dtype=torch.bfloat16, device=dev)
         if n_recv:
             self._expert_rows(rows_q, rows_sf, local_e, w1q, w1s, w2q, w2s, res, kw)
-        # returned rows first, the shared experts' rows for the own tokens after them
-        rows_all = torch.empty((n_send + t * (1 if self.s else 0), self.h), dtype=torch.bfloat16, device=dev)
-        back = exchange(res, recv_counts, send_counts, self.group)
-        rows_all[:n_send] = back
-        slots = self.k + (1 if self.s else 0)
+        mark("experts")
+        # returned rows first (received in place), the shared experts' rows for the own tokens after them
+        dist.all_to_all_single(rows_all[:n_send], res, output_split_sizes=send_counts, input_split_sizes=recv_counts,
+                               group=self.group)
+        mark("combine_a2a")
         row_of = torch.full((t, slots), -1, dtype=torch.int32, device=dev)
         row_of[:, :self.k] = plan["pos_of_route"]
         w_rows = torch.ones(rows_all.shape[0], dtype=torch.float32, device=dev)
         w_rows[:n_send] = weights.reshape(-1)[plan["order"]]
         if self.s:
-            self._shared_rows(hq, hs, w1q, w1s, w2q, w2s, rows_all[n_send:], kw)
             row_of[:, self.k] = n_send + torch.arange(t, dtype=torch.int32, device=dev)
+            if side is not None:
+                torch.cuda.current_stream(dev).wait_stream(side)
         if out is None:
             out = torch.empty((t, self.h), dtype=torch.bfloat16, device=dev)
+            mark("shared")
         self._combine_rows(rows_all, row_of, w_rows, out)
+        mark("combine")
+        if marks:
+            self._pending_marks = marks
         return out
+
+    def stage_ms(self):
+        """Durations (ms) between the profiling marks of the last forward (set `profile = True` first); synchronises."""
+        marks = getattr(self, "_pending_marks", None)
+        if not marks:
+            return {}
+        marks[-1][1].synchronize()
+        return {marks[i + 1][0]: marks[i][1].elapsed_time(marks[i + 1][1]) for i in range(len(marks) - 1)}
