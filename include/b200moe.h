@@ -121,7 +121,7 @@ int b200moe_router_logits(const void* x, const void* gate_weight, int64_t num_to
 
 /* Dense NVFP4 GEMM: out[M,N] = bf16(alpha * A @ B^T), both operands NVFP4 with tiled scales. Contract of
  * DG/problem/reference.py:10-15 with the A operand quantised by b200moe_quantize_nvfp4; B rows are logical
- * (no shuffle). K % 256 == 0; tile_n as in b200moe_config (N % tile_n == 0, N % 256 == 0 for 512). status: optional device int32 that receives a non-zero code
+ * (no shuffle). K % 256 == 0; out 32-byte aligned with out_stride % 16 == 0; tile_n as in b200moe_config (N % tile_n == 0, N % 256 == 0 for 512). status: optional device int32 that receives a non-zero code
  * if a bounded device wait expired. */
 int b200moe_gemm_nvfp4(const void* a_q, const void* a_sf_tiled, const void* b_q, const void* b_sf_tiled, float alpha, void* out,
                        int64_t m, int64_t n, int64_t k, int64_t out_stride, int32_t tile_n, int32_t* status, void* stream);

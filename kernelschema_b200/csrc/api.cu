@@ -287,7 +287,8 @@ int b200moe_gemm_nvfp4(const void* a_q, const void* a_sf, const void* b_q, const
   if (!a_q || !a_sf || !b_q || !b_sf || !out) return fail(762, "gemm: null pointer");
   if (((uintptr_t)a_q | (uintptr_t)a_sf | (uintptr_t)b_q | (uintptr_t)b_sf | (uintptr_t)out) & 15)
     return fail(763, "gemm: operands must be 16-byte aligned");
-  if (out_stride < n || out_stride % 8) return fail(764, "gemm: out_stride must be >= N and a multiple of 8");
+  if (out_stride < n || out_stride % 16 || ((uintptr_t)out & 31))
+    return fail(764, "gemm: out must be 32-byte aligned, out_stride >= N and a multiple of 16");
   CUtensorMap ta, tb;
   int rc = make_operand_map(&ta, a_q, (uint64_t)m, (uint64_t)k / 2, 128);
   if (rc) return cuda_fail(rc, "gemm A tensor map");

@@ -219,9 +219,10 @@ DEV void epilogue_cols128(const GemmParams& p, uint32_t taddr, int e, size_t row
     if (live) {
       const int half_i = p.N >> 2;                     // bytes of one row of packed activations (I / 2)
       const int i0 = col0 >> 1;                        // first intermediate channel of these 128 columns (multiple of 64)
-      uint4* dst = reinterpret_cast<uint4*>(p.act_q + row * half_i + (i0 >> 1));
-      dst[0] = make_uint4(packed[0].x, packed[0].y, packed[1].x, packed[1].y);
-      dst[1] = make_uint4(packed[2].x, packed[2].y, packed[3].x, packed[3].y);
+      asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p.act_q + row * half_i + (i0 >> 1)), "r"(packed[0].x),
+                   "r"(packed[0].y), "r"(packed[1].x), "r"(packed[1].y), "r"(packed[2].x), "r"(packed[2].y), "r"(packed[3].x),
+                   "r"(packed[3].y)
+                   : "memory");
       // scale bytes of 64 channels = one 4-byte word of the 128x4-tiled layout [row/128][I/64][32][16]
       const size_t off = ((row >> 7) * (size_t)(p.N >> 7) + (size_t)(i0 >> 6)) * kSfChunk + (row & 31) * 16 + ((row >> 5) & 3) * 4;
       *reinterpret_cast<uint32_t*>(p.act_sf + off) = sfword;
@@ -247,9 +248,13 @@ DEV void epilogue_cols128(const GemmParams& p, uint32_t taddr, int e, size_t row
         const __nv_bfloat162 pr = __floats2bfloat162_rn(x0 * oscale, x1 * oscale);
         o[j] = *reinterpret_cast<const uint32_t*>(&pr);
       }
-      uint4* d4 = reinterpret_cast<uint4*>(dst_row + cb * 32);
+      // 256-bit stores: one full 32-byte sector per thread and instruction
+      __nv_bfloat16* d = dst_row + cb * 32;
 #pragma unroll
-      for (int j = 0; j < 4; ++j) d4[j] = make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
+      for (int j = 0; j < 2; ++j)
+        asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(d + 16 * j), "r"(o[8 * j]), "r"(o[8 * j + 1]),
+                     "r"(o[8 * j + 2]), "r"(o[8 * j + 3]), "r"(o[8 * j + 4]), "r"(o[8 * j + 5]), "r"(o[8 * j + 6]), "r"(o[8 * j + 7])
+                     : "memory");
     }
   }
 }
