@@ -17,6 +17,7 @@ from __future__ import annotations
 import argparse
 import json
 import os
+import re
 import subprocess
 import sys
 import threading
@@ -36,6 +37,9 @@ WORKLOADS = {
 }
 ACT_GLOBAL_SCALE = 1.0 / 448.0     # static (calibrated) activation global scale: amax 6 -> 6/(6*448)
 FP4_NOMINAL_TFLOPS = 9000.0
+# dram__bytes_read.sum + dram__bytes_write.sum of one FC1 launch, from the ncu captures summarised under profiles/
+# (workload -> bytes); null for workloads that were not captured.
+FC1_DRAM_TRAFFIC = {"dsv3": 4966850048 + 79877632, "qwen3": 386940416 + 49309952}
 L2_BYTES = 126e6
 
 
@@ -314,11 +318,24 @@ def run_gpu(args, wl):
         stage["tile_fill"] = totals[2] / max(1, totals[0] * 128)
         pk = peaks()
         fc1_flops = flops * 2.0 / 3.0
+        rows_used = totals[1]
+        fc1_bytes = (int((owner.workspace()["counts"].cpu() > 0).sum()) * 2 * wl["i"] * h * 9 / 16      # weights of the experts touched
+                     + rows_used * h * 9 / 16 + rows_used * wl["i"] * 9 / 16)                           # permuted rows in, activations out
         achieved = fc1_flops / (stage["fc1"] * 1e-3) / 1e12
         peak = 4.0 * pk["bf16_sustained"]
+        counts = owner.workspace()["counts"].cpu()
+        touched = int((counts > 0).sum())
+        weight_bytes = touched * 3 * wl["i"] * h * 9 / 16
+        act_bytes = t * h * 2 * 2 + t * h * 9 / 16
+        stage["experts_touched"] = touched
+        stage["hbm_algorithmic_gbs"] = (weight_bytes + act_bytes) / (per_step * 1e-3) / 1e9
+        stage["hbm_frac_of_measured"] = stage["hbm_algorithmic_gbs"] / pk["hbm_gbs"]
         roof = dict(bound="tensor", kernel="k_gemm_nvfp4<FC1>", achieved=achieved, peak=peak, unit="TFLOP/s", frac=achieved / peak,
                     peak_source=f"4 x bf16_tflops_sustained of {pk['source']} MEASURED_PEAKS (FP4:bf16 nominal ratio)",
-                    frac_of_nominal_fp4=achieved / FP4_NOMINAL_TFLOPS, traffic=None,
+                    frac_of_nominal_fp4=achieved / FP4_NOMINAL_TFLOPS,
+                    traffic=FC1_DRAM_TRAFFIC.get(args.workload) if args.tokens is None and args.zipf is None else None,
+                    traffic_unit="bytes of DRAM traffic per FC1 launch (ncu)",
+                    algorithmic_bytes=fc1_bytes,
                     layer_frac_of_nominal_fp4=tflops / FP4_NOMINAL_TFLOPS)
     ep_stage = None
     if world > 1:
@@ -391,6 +408,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="dsv3", choices=sorted(WORKLOADS))
     ap.add_argument("--zipf", type=float, default=None, help="override the workload's Zipf exponent of the router bias (0 = uniform)")
+    ap.add_argument("--tokens", type=int, default=None, help="override the workload's tokens per GPU (e.g. 64 or 256 for decode)")
     ap.add_argument("--dense", default=None, metavar="M,N,K", help="time the dense NVFP4 GEMM of this shape instead of the layer")
     ap.add_argument("--tile-n", type=int, default=0, help="GEMM tile for --dense (0 = default, 128, 256, 512 = CTA pair)")
     args = ap.parse_args()
@@ -398,6 +416,9 @@ def main():
         return run_dense(args)
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     wl = dict(WORKLOADS[args.workload])
+    if args.tokens is not None:
+        wl["t"] = args.tokens
+        wl["label"] = re.sub(r"_T\d+", f"_T{args.tokens}", wl["label"])
     if args.zipf is not None:
         wl["zipf"] = args.zipf
         wl["label"] += f"_zipf{args.zipf:g}_override"
