@@ -252,7 +252,7 @@ DEV void epilogue_cols128(const GemmParams& p, uint32_t taddr, int e, size_t row
       __nv_bfloat16* d = dst_row + cb * 32;
 #pragma unroll
       for (int j = 0; j < 2; ++j)
-        asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(d + 16 * j), "r"(o[8 * j]), "r"(o[8 * j + 1]),
+        asm volatile("st.global.L1::no_allocate.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(d + 16 * j), "r"(o[8 * j]), "r"(o[8 * j + 1]),
                      "r"(o[8 * j + 2]), "r"(o[8 * j + 3]), "r"(o[8 * j + 4]), "r"(o[8 * j + 5]), "r"(o[8 * j + 6]), "r"(o[8 * j + 7])
                      : "memory");
     }

@@ -21,11 +21,10 @@ template <bool GLOBAL_SCALE>
 __global__ void __launch_bounds__(256) k_quantize_nvfp4(const __nv_bfloat16* __restrict__ x, int64_t rows, int64_t cols,
                                                         int64_t row_stride, float gs, uint8_t* __restrict__ payload,
                                                         uint8_t* __restrict__ scales, int sf_layout) {
-  const int64_t blocks_per_row = cols >> 4;
-  const int64_t total = rows * blocks_per_row;
-  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t row = idx / blocks_per_row;
-    const int64_t blk = idx - row * blocks_per_row;
+  // One block walks rows, its threads walk the 16-element blocks of a row: no integer division anywhere.
+  const int blocks_per_row = (int)(cols >> 4);
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x)
+  for (int blk = threadIdx.x; blk < blocks_per_row; blk += blockDim.x) {
     const uint4* src = reinterpret_cast<const uint4*>(x + row * row_stride + blk * 16);
     uint4 raw[2];
     raw[0] = __ldg(src);
@@ -77,7 +76,7 @@ __global__ void __launch_bounds__(256) k_quantize_nvfp4(const __nv_bfloat16* __r
         packed[h] = word;
       }
     }
-    *reinterpret_cast<uint2*>(payload + row * (cols >> 1) + blk * 8) = make_uint2(packed[0], packed[1]);
+    *reinterpret_cast<uint2*>(payload + row * (cols >> 1) + (int64_t)blk * 8) = make_uint2(packed[0], packed[1]);
     if (sf_layout == 0)
       scales[row * blocks_per_row + blk] = (uint8_t)sbyte;
     else
@@ -101,12 +100,13 @@ __global__ void k_sf_to_tiles(const uint8_t* __restrict__ src, int64_t rows, int
 
 int launch_quantize_nvfp4(const void* x, int64_t rows, int64_t cols, int64_t row_stride, float gs, void* payload, void* scales,
                           int sf_layout, cudaStream_t st) {
-  const int64_t total = rows * (cols >> 4);
-  if (total == 0) return 0;
-  const int threads = 256;
-  int64_t blocks = (total + threads - 1) / threads;
-  const int64_t cap = 148LL * 8 * 4;
-  if (blocks > cap) blocks = cap;
+  if (rows == 0) return 0;
+  const int bpr = (int)(cols >> 4);
+  // threads = blocks per row rounded up to a warp, split into equal passes of at most 256 threads
+  const int passes = (bpr + 255) / 256;
+  int threads = ((bpr + passes - 1) / passes + 31) / 32 * 32;
+  if (threads > 256) threads = 256;
+  const int64_t blocks = rows < 148LL * 32 ? rows : 148LL * 32;
   if (gs == 1.0f)
     k_quantize_nvfp4<false><<<(unsigned)blocks, threads, 0, st>>>((const __nv_bfloat16*)x, rows, cols, row_stride, gs,
                                                                  (uint8_t*)payload, (uint8_t*)scales, sf_layout);
