@@ -65,7 +65,10 @@ typedef struct {
   const float* output1_scale_gate_scalar; /* [E+S] multiplier of the FC1 "gate" accumulator, or NULL (=1) */
   const float* output2_scale_scalar;      /* [E+S] multiplier of the FC2 accumulator, or NULL (=1) */
   int32_t local_expert_offset;       /* id of this instance's first routed expert */
-  int32_t reserved0;
+  int32_t direct_rows;               /* 0 = weighted combine (default). 1 = every token has at most one route (top_k == 1,
+                                        no shared experts): FC2 writes bf16(fc2) of the token's route straight into
+                                        output[t] (weights ignored, tokens without a route are left untouched) and the
+                                        combine pass is skipped; used by the expert-parallel wrapper on received rows */
   void* output;                      /* bf16 [T, H]; the only caller memory that is written */
   int64_t output_stride;             /* elements between output rows (H when contiguous) */
 } b200moe_args;

@@ -28,7 +28,7 @@ class Args(C.Structure):
                 ("gemm2_weights", C.c_void_p), ("gemm2_weights_scale", C.c_void_p), ("gemm1_alpha", C.c_void_p),
                 ("gemm1_beta", C.c_void_p), ("gemm1_clamp_limit", C.c_void_p), ("output1_scale_scalar", C.c_void_p),
                 ("output1_scale_gate_scalar", C.c_void_p), ("output2_scale_scalar", C.c_void_p),
-                ("local_expert_offset", C.c_int32), ("reserved0", C.c_int32), ("output", C.c_void_p),
+                ("local_expert_offset", C.c_int32), ("direct_rows", C.c_int32), ("output", C.c_void_p),
                 ("output_stride", C.c_int64)]
 
 

@@ -128,6 +128,10 @@ int check_args(const b200moe_layer* h, const b200moe_args* a) {
        (uintptr_t)a->gemm1_weights_scale | (uintptr_t)a->gemm2_weights_scale) & 15)
     return fail(730, "run: tensors must be 16-byte aligned");
   if (((uintptr_t)a->hidden_states_scale) & 3) return fail(731, "run: hidden_states_scale must be 4-byte aligned");
+  if (a->direct_rows && (h->cfg.top_k != 1 || h->cfg.num_shared_experts != 0))
+    return fail(733, "run: direct_rows needs top_k == 1 and no shared experts");
+  if (a->direct_rows && (((uintptr_t)a->output & 31) || a->output_stride % 16))
+    return fail(734, "run: direct_rows needs a 32-byte aligned output with output_stride %% 16 == 0");
   return 0;
 }
 
@@ -209,6 +213,11 @@ int run_impl(b200moe_layer* h, const b200moe_args* a, cudaStream_t st, cudaEvent
   g.out = h->rout;
   g.out_stride = c.hidden;
   g.out_scale = a->output2_scale_scalar;
+  if (a->direct_rows) {
+    g.out = (__nv_bfloat16*)a->output;
+    g.out_stride = a->output_stride;
+    g.out_row_index = h->rm.tok_of_row;
+  }
   {
     const int64_t worst_tiles = (int64_t)T * h->kk / 128 + h->etot;
     const int64_t items = worst_tiles * (g.N / h->bn);
@@ -228,6 +237,10 @@ int run_impl(b200moe_layer* h, const b200moe_args* a, cudaStream_t st, cudaEvent
     if (rc) return cuda_fail(rc, "FC2");
   }
   mark(4);
+  if (a->direct_rows) {
+    mark(5);
+    return 0;
+  }
   rc = launch_finalize(h->rout, h->rm.row_of, h->rm.weight_of_row, T, h->kk, c.hidden, a->output, a->output_stride, st);
   if (rc) return cuda_fail(rc, "combine");
   mark(5);

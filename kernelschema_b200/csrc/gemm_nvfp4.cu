@@ -230,7 +230,8 @@ DEV void epilogue_cols128(const GemmParams& p, uint32_t taddr, int e, size_t row
   } else {
     if (!live) return;
     const float oscale = (MODE == kGemmFc2) ? (p.out_scale ? p.out_scale[e] : 1.0f) : p.dense_alpha;
-    __nv_bfloat16* dst_row = p.out + row * p.out_stride + col0;
+    const size_t orow = (MODE == kGemmFc2 && p.out_row_index) ? (size_t)p.out_row_index[row] : row;
+    __nv_bfloat16* dst_row = p.out + orow * p.out_stride + col0;
 #pragma unroll
     for (int cb = 0; cb < 4; ++cb) {
       uint32_t o[16];

@@ -42,6 +42,7 @@ struct GemmParams {
   uint8_t* act_sf;              // FC1 out: activation scales, 128x4 tiles [rows/128][I/64][512]
   __nv_bfloat16* out;           // FC2 / dense out
   int64_t out_stride;           // elements between output rows
+  const int32_t* out_row_index; // FC2 only: output row of permuted row r is out_row_index[r] (null = r itself)
   const float* scale_up;        // per expert multipliers of the FC1 accumulators (null = 1)
   const float* scale_gate;
   const float* alpha;           // per expert activation parameters (null = 1 / 0 / no clamp)

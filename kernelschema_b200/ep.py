@@ -74,8 +74,9 @@ class ExpertParallelMoE:
             self._routed = MoELayer(self.h, self.i, self.e_local, 1, max(n, self.recv_capacity))
         ones = torch.ones((n, 1), dtype=torch.float32, device=rows_q.device)
         e = self.e_local
+        # top-1 "routing" of every received row to its local expert; FC2 writes the per-route rows straight into out_rows
         self._routed.run(local_expert.view(n, 1), ones, rows_q, rows_sf, w1q[:e], w1s[:e], w2q[:e], w2s[:e], out_rows,
-                         **{k: (None if v is None else v[:e]) for k, v in kw.items()})
+                         direct_rows=True, **{k: (None if v is None else v[:e]) for k, v in kw.items()})
 
     def _cuda_shared_rows(self, hq, hs, w1q, w1s, w2q, w2s, out_rows, kw):
         from .ops import MoELayer

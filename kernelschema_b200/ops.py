@@ -136,7 +136,7 @@ class MoELayer:
 
     # ------------------------------------------------------------------ building blocks
     def _args(self, ids, weights, hidden_states, hidden_states_scale, w1, s1, w2, s2, out, *, alpha=None, beta=None, limit=None,
-              scale_up=None, scale_gate=None, scale_out=None, activation_type=3, expert_offset=0, scale_layout=2):
+              scale_up=None, scale_gate=None, scale_out=None, activation_type=3, expert_offset=0, scale_layout=2, direct_rows=False):
         t = hidden_states.shape[0]
         a = _lib.Args(struct_size=C.sizeof(_lib.Args), num_tokens=t, topk_ids=_ptr(ids), topk_weights=_ptr(weights),
                       hidden_states=_ptr(hidden_states), hidden_states_scale=_ptr(hidden_states_scale),
@@ -144,7 +144,8 @@ class MoELayer:
                       gemm1_weights_scale=_ptr(s1), gemm2_weights=_ptr(w2), gemm2_weights_scale=_ptr(s2),
                       gemm1_alpha=_ptr(alpha), gemm1_beta=_ptr(beta), gemm1_clamp_limit=_ptr(limit),
                       output1_scale_scalar=_ptr(scale_up), output1_scale_gate_scalar=_ptr(scale_gate),
-                      output2_scale_scalar=_ptr(scale_out), local_expert_offset=expert_offset, output=_ptr(out),
+                      output2_scale_scalar=_ptr(scale_out), local_expert_offset=expert_offset, direct_rows=int(direct_rows),
+                      output=_ptr(out),
                       output_stride=out.stride(0))
         return a
 

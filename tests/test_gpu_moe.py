@@ -157,3 +157,27 @@ def test_model_rejects_bad_shapes():
         run_model(bad)
     with pytest.raises(ValueError):
         ks.MoELayer(100, 256, 4, 2, 8)
+
+
+def test_direct_rows_mode_writes_per_route_results():
+    """direct_rows: top-1 routing, FC2 stores bf16(fc2) of the token's route straight into the output (no combine pass)."""
+    import kernelschema_b200 as ks
+    from gpu_util import to_dev
+    p = make_moe_case(17, 300, 256, 256, 8, 1)
+    ids, w = p["topk_ids"]
+    ids = ids.copy()
+    ids[::7] = -1                                    # tokens without a route stay untouched
+    q = dict(p, topk_ids=(ids, np.ones_like(w)))
+    ref = o.moe_expected(q)
+    layer = ks.MoELayer(256, 256, 8, 1, 300)
+    out = torch.full((300, 256), -17.0, dtype=torch.bfloat16, device="cuda")
+    layer.run(to_dev(ids), to_dev(np.ones_like(w)), to_dev(p["hidden_states"]), to_dev(p["hidden_states_scale"]),
+              to_dev(p["gemm1_weights"]), to_dev(p["gemm1_weights_scale"]), to_dev(p["gemm2_weights"]),
+              to_dev(p["gemm2_weights_scale"]), out, direct_rows=True)
+    torch.cuda.synchronize()
+    assert layer.status() == 0
+    got = out.float().cpu().numpy()
+    routed = ids[:, 0] >= 0
+    assert np.all(got[~routed] == -17.0)
+    assert_layer_parity(got[routed], ref[routed], "direct_rows")
+    layer.close()
