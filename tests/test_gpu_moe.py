@@ -181,3 +181,31 @@ def test_direct_rows_mode_writes_per_route_results():
     assert np.all(got[~routed] == -17.0)
     assert_layer_parity(got[routed], ref[routed], "direct_rows")
     layer.close()
+
+
+def test_layer_is_cuda_graph_capturable():
+    """The forward allocates nothing and never synchronises after warm-up, so a caller can capture it in a CUDA graph."""
+    import kernelschema_b200 as ks
+    from gpu_util import to_dev
+    p = make_moe_case(23, 64, 512, 256, 8, 2, shared=1)
+    ids, w = p["topk_ids"]
+    args = [to_dev(ids), to_dev(w), to_dev(p["hidden_states"]), to_dev(p["hidden_states_scale"]), to_dev(p["gemm1_weights"]),
+            to_dev(p["gemm1_weights_scale"]), to_dev(p["gemm2_weights"]), to_dev(p["gemm2_weights_scale"])]
+    layer = ks.MoELayer(512, 256, 8, 2, 64, num_shared_experts=1)
+    out = torch.zeros(64, 512, dtype=torch.bfloat16, device="cuda")
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        layer.run(*args, out)                      # warm-up: tensor maps, kernel attributes
+        side.synchronize()
+        eager = out.clone()
+        out.zero_()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            layer.run(*args, out)
+        out.zero_()
+        graph.replay()
+        side.synchronize()
+    assert layer.status() == 0
+    assert torch.equal(out, eager)
+    assert_layer_parity(out.float().cpu().numpy(), o.moe_expected(p), "graph replay")
+    layer.close()
