@@ -12,6 +12,7 @@ from concurrent.futures import ThreadPoolExecutor
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libb200moe.so")
+SHIM = os.path.join(HERE, "_b200moe_shim.so")
 SOURCES = ["quantize.cu", "router.cu", "route_map.cu", "gather.cu", "finalize.cu", "gemm_nvfp4.cu", "api.cu"]
 HEADERS = ["kernels.cuh", "ptx.cuh", os.path.join("..", "..", "include", "b200moe.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
@@ -60,7 +61,22 @@ def build(force: bool = False, verbose: bool = False) -> str:
         res = subprocess.run(cmd, capture_output=True, text=True)
         if res.returncode != 0:
             raise RuntimeError("link failed:\n" + res.stderr)
+    build_shim(force)
     return LIB
+
+
+def build_shim(force: bool = False) -> str:
+    """Compile the pybind11 shim (plain C++, links against the in-tree libb200moe.so through $ORIGIN)."""
+    import sysconfig
+    import pybind11
+    src = os.path.join(CSRC, "shim.cpp")
+    if force or _stale(SHIM, [src, LIB, os.path.join(CSRC, "..", "..", "include", "b200moe.h")]):
+        cmd = ["g++", "-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden", "-I", pybind11.get_include(), "-I",
+               sysconfig.get_paths()["include"], src, "-o", SHIM, "-L", HERE, "-lb200moe", "-Wl,-rpath,$ORIGIN"]
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode != 0:
+            raise RuntimeError("shim build failed:\n" + res.stderr)
+    return SHIM
 
 
 if __name__ == "__main__":

@@ -9,6 +9,22 @@ import torch
 from . import _lib
 
 
+_shim_mod = None
+
+
+def _shim():
+    """The pybind11 binding (built next to the library by ``python -m kernelschema_b200.build``)."""
+    global _shim_mod
+    if _shim_mod is None:
+        _lib.load()
+        try:
+            from . import _b200moe_shim
+        except ImportError as exc:
+            raise RuntimeError("kernelschema_b200/_b200moe_shim.so is missing: run `python -m kernelschema_b200.build`") from exc
+        _shim_mod = _b200moe_shim
+    return _shim_mod
+
+
 def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
@@ -149,11 +165,15 @@ class MoELayer:
                       output_stride=out.stride(0))
         return a
 
-    def run(self, ids, weights, hidden_states, hidden_states_scale, w1, s1, w2, s2, out, **kw):
-        """Asynchronous forward on the current stream; writes ``out`` (bf16 [T, H]) in place."""
+    def run(self, ids, weights, hidden_states, hidden_states_scale, w1, s1, w2, s2, out, *, alpha=None, beta=None, limit=None,
+            scale_up=None, scale_gate=None, scale_out=None, activation_type=3, expert_offset=0, scale_layout=2, direct_rows=False):
+        """Asynchronous forward on the current stream; writes ``out`` (bf16 [T, H]) in place. The hot call goes through
+        the pybind11 shim (one positional C++ call, no ctypes struct marshalling)."""
         _need_cuda(hidden_states, hidden_states_scale, w1, s1, w2, s2, out)
-        a = self._args(ids, weights, hidden_states, hidden_states_scale, w1, s1, w2, s2, out, **kw)
-        _lib.check(_lib.load().b200moe_run(self._h, C.byref(a), _stream()), "b200moe_run")
+        p = lambda t: 0 if t is None else t.data_ptr()
+        _shim().run(self._h.value, hidden_states.shape[0], p(ids), p(weights), p(hidden_states), p(hidden_states_scale),
+                    scale_layout, activation_type, p(w1), p(s1), p(w2), p(s2), p(alpha), p(beta), p(limit), p(scale_up),
+                    p(scale_gate), p(scale_out), expert_offset, int(direct_rows), p(out), out.stride(0), _stream())
         return out
 
     def run_profiled(self, ids, weights, hidden_states, hidden_states_scale, w1, s1, w2, s2, out, **kw):

@@ -72,3 +72,14 @@ def test_model_refuses_cpu_tensors():
           output1_scale_scalar=None, output1_scale_gate_scalar=None, output2_scale_scalar=None, num_experts=4, top_k=2,
           n_group=None, topk_group=None, intermediate_size=256, local_expert_offset=0, local_num_experts=4,
           routed_scaling_factor=1.0, output=torch.zeros(2, 256, dtype=torch.bfloat16))
+
+
+def test_pybind_shim_loads_and_maps_errors(lib):
+    from kernelschema_b200 import _lib
+    from kernelschema_b200.ops import _shim
+    shim = _shim()
+    assert shim.abi_version() == _lib.ABI_VERSION
+    with pytest.raises(ValueError):
+        shim.create(100, 256, 4, 2, 0, 8, 0)
+    with pytest.raises(ValueError):
+        shim.run(0, 1, *([0] * 21))
