@@ -18,7 +18,6 @@ import argparse
 import json
 import os
 import re
-import subprocess
 import sys
 import threading
 import time
@@ -40,7 +39,6 @@ FP4_NOMINAL_TFLOPS = 9000.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one FC1 launch, from the ncu captures summarised under profiles/
 # (workload -> bytes); null for workloads that were not captured.
 FC1_DRAM_TRAFFIC = {"dsv3": 4966850048 + 79877632, "qwen3": 386940416 + 49309952}
-L2_BYTES = 126e6
 
 
 def peaks():

@@ -14,20 +14,17 @@
 //        32-column block is exactly one 16-channel NVFP4 block of the intermediate activation;
 //   FC2: column 8a+b is output channel 4b+a.
 //
-// Warp roles (192 threads, one CTA per SM): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer,
-// warps 2..5 = epilogue (TMEM lane quadrant = warp & 3). Stage = 256 FP4 of K: A 16 KB, B BN*128 B,
-// scale factors 2 KB per 128 rows. Accumulators are double buffered when BN = 128.
+// One CTA per SM, warp-specialised: TMA producer, MMA issuer, scale-factor copier, epilogue warps (roles are listed
+// at each kernel). Stage = 256 FP4 of K: A 16 KB, B BN*128 B, scale factors 2 KB per 128 rows.
 #include "kernels.cuh"
 #include "ptx.cuh"
 
 namespace b200 {
 
-constexpr int kGemmThreads = 192;
 constexpr int kBM = 128;
 constexpr int kStageK = 256;             // FP4 elements of K per pipeline stage (128 payload bytes per row)
 constexpr int kSfChunk = 512;            // bytes of one (128 rows x 64 K) scale-factor chunk
 constexpr int kNumSfBuf = 4;             // TMEM scale-factor buffers in rotation
-constexpr int kSfLead = 2;               // stages by which the scale-factor copies lead the MMAs (< kNumSfBuf, < stages)
 
 template <int BN>
 struct GemmCfg {
@@ -53,110 +50,6 @@ DEV float tanh_fast(float x) {
   float y;
   asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
-}
-
-// Epilogue of one 128 x BN accumulator tile for the calling warp's 32 TMEM lanes (one row per thread).
-// `release` is invoked once, as soon as the last TMEM read of the tile has completed.
-template <int MODE, int BN, class Release>
-DEV void epilogue_tile(const GemmParams& p, uint32_t taddr, int e, size_t row, bool live, int nt, Release release) {
-  if (p.dbg & 8) live = false;
-  if (MODE == kGemmFc1) {
-    const float s_up = p.scale_up ? p.scale_up[e] : 1.0f;
-    const float s_gate = p.scale_gate ? p.scale_gate[e] : 1.0f;
-    const float alpha = p.alpha ? p.alpha[e] : 1.0f;
-    const float beta = p.beta ? p.beta[e] : 0.0f;
-    const bool clamp = p.limit != nullptr;
-    const float limit = clamp ? p.limit[e] : 0.f;
-    const int half_i = p.N >> 2;                       // bytes of one row of packed activations (I / 2)
-    uint2 packed[BN / 32];
-    uint32_t sfbytes = 0;
-    uint32_t sfword[BN / 128];
-#pragma unroll
-    for (int cb = 0; cb < BN / 32; ++cb) {
-      float v[32];
-      tmem_ld32(taddr + cb * 32, v);
-      tmem_ld_wait();
-      float act[16];
-      float amax = 0.f;
-#pragma unroll
-      for (int c = 0; c < 2; ++c)
-#pragma unroll
-        for (int b = 0; b < 8; ++b) {
-          float up = v[16 * c + b] * s_up;
-          float gate = v[16 * c + 8 + b] * s_gate;
-          if (clamp) {
-            up = fminf(fmaxf(up, -limit), limit);
-            gate = fminf(gate, limit);
-          }
-          float a;
-          if (p.act_type == 10)
-            a = alpha * tanh_fast(__fdividef(gate, alpha)) * sigmoid_fast(gate) * (beta * tanh_fast(__fdividef(up, beta)));
-          else
-            a = gate * sigmoid_fast(alpha * gate) * (up + beta);
-          act[2 * b + c] = a;
-          amax = fmaxf(amax, fabsf(a));
-        }
-      // reference.py:40-42: sf = e4m3(clamp(amax * (1/6), 0, 448)); zero scale -> zero block
-      const float sfv = fminf(amax * (1.0f / 6.0f), 448.0f);
-      const uint32_t sb = cvt_e4m3(sfv);
-      const float sff = e4m3_to_f32(sb);
-      const float inv = sff > 0.f ? __frcp_rn(sff) : 0.f;
-      uint32_t w0 = 0, w1 = 0;
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        w0 |= cvt_e2m1x2(act[2 * j] * inv, act[2 * j + 1] * inv) << (8 * j);
-        w1 |= cvt_e2m1x2(act[8 + 2 * j] * inv, act[8 + 2 * j + 1] * inv) << (8 * j);
-      }
-      packed[cb] = make_uint2(w0, w1);
-      sfbytes |= sb << (8 * (cb & 3));
-      if ((cb & 3) == 3) { sfword[cb >> 2] = sfbytes; sfbytes = 0; }
-    }
-    release();
-    if (live) {
-      const int i0 = (nt * BN) >> 1;                   // first intermediate channel of this tile
-      uint4* dst = reinterpret_cast<uint4*>(p.act_q + row * half_i + (i0 >> 1));
-#pragma unroll
-      for (int j = 0; j < BN / 64; ++j)
-        dst[j] = make_uint4(packed[2 * j].x, packed[2 * j].y, packed[2 * j + 1].x, packed[2 * j + 1].y);
-      // scale bytes of 64 channels = one 4-byte word of the 128x4-tiled layout [row/128][I/64][32][16]
-      const int chunks_i = p.N >> 7;                   // I / 64
-#pragma unroll
-      for (int j = 0; j < BN / 128; ++j) {
-        const size_t off = ((row >> 7) * chunks_i + (size_t)((i0 >> 6) + j)) * kSfChunk + (row & 31) * 16 + ((row >> 5) & 3) * 4;
-        *reinterpret_cast<uint32_t*>(p.act_sf + off) = sfword[j];
-      }
-    }
-  } else {
-    const float oscale = (MODE == kGemmFc2) ? (p.out_scale ? p.out_scale[e] : 1.0f) : p.dense_alpha;
-    __nv_bfloat16* dst_row = p.out + row * p.out_stride + (size_t)nt * BN;
-#pragma unroll
-    for (int cb = 0; cb < BN / 32; ++cb) {
-      float v[32];
-      tmem_ld32(taddr + cb * 32, v);
-      tmem_ld_wait();
-      if (cb == BN / 32 - 1) release();
-      if (live) {
-        uint32_t o[16];
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          float x0, x1;
-          if (MODE == kGemmFc2) {           // output channel 4b+a lives in column 8a+b
-            const int h0 = 2 * j, h1 = 2 * j + 1;
-            x0 = v[8 * (h0 & 3) + (h0 >> 2)];
-            x1 = v[8 * (h1 & 3) + (h1 >> 2)];
-          } else {
-            x0 = v[2 * j];
-            x1 = v[2 * j + 1];
-          }
-          const __nv_bfloat162 pr = __floats2bfloat162_rn(x0 * oscale, x1 * oscale);
-          o[j] = *reinterpret_cast<const uint32_t*>(&pr);
-        }
-        uint4* d4 = reinterpret_cast<uint4*>(dst_row + cb * 32);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) d4[j] = make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
-      }
-    }
-  }
 }
 
 // Epilogue of 128 accumulator columns [col0, col0 + 128) of one tile for the calling warp's 32 TMEM lanes.
