@@ -163,7 +163,7 @@ def make_step(wl, L, world, device):
         layer = ks.MoELayer(h, i, L["e_local"], k, t, num_shared_experts=s, tile_n=int(os.environ.get("B200MOE_TILE_N", "0")))
         out = torch.empty((t, h), dtype=torch.bfloat16, device=device)
 
-        def step(x):
+        def step(x, out=out):
             hq, hs = ks.nvfp4_quantize(x, ACT_GLOBAL_SCALE)
             ids, w = ks.route_topk(ks.router_logits(x, L["gate_w"]), k, L["bias"])
             layer.run(ids, w, hq, hs.view(torch.uint8), L["w1q"], L["w1s"], L["w2q"], L["w2s"], out, scale_up=L["scale_fc1"],
@@ -174,11 +174,11 @@ def make_step(wl, L, world, device):
     from kernelschema_b200.ep import ExpertParallelMoE
     ep = ExpertParallelMoE(h, i, wl["e"], k, t, num_shared_experts=s)
 
-    def step(x):
+    def step(x, out=None):
         hq, hs = ks.nvfp4_quantize(x, ACT_GLOBAL_SCALE)
         ids, w = ks.route_topk(ks.router_logits(x, L["gate_w"]), k, L["bias"])
-        out = ep.forward(ids, w, hq, hs.view(torch.uint8), L["w1q"], L["w1s"], L["w2q"], L["w2s"], scale_up=L["scale_fc1"],
-                         scale_gate=L["scale_fc1"], scale_out=L["scale_fc2"])
+        out = ep.forward(ids, w, hq, hs.view(torch.uint8), L["w1q"], L["w1s"], L["w2q"], L["w2s"], out=out,
+                         scale_up=L["scale_fc1"], scale_gate=L["scale_fc1"], scale_out=L["scale_fc2"])
         return out, ids
 
     return step, ep, ep.launches_per_step + 3
@@ -258,14 +258,18 @@ def run_gpu(args, wl):
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed(fn, steps, warmup):
+    def timed(fn, steps, warmup, finish=None):
         for _ in range(warmup):
             fn()
+        if finish:
+            finish()
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for _ in range(steps):
             fn()
+        if finish:
+            finish()
         e1.record()
         barrier()
         ms = torch.tensor([e0.elapsed_time(e1)], device=device)
@@ -278,17 +282,50 @@ def run_gpu(args, wl):
     def resident():
         state["out"], state["ids"] = step(x_dev)
 
+    # End to end: every step copies its tokens from pinned host memory and its bf16 output back to pinned host memory.
+    # The three legs run on three streams with two buffer slots, so step i's copies overlap step i+1's compute
+    # (a serving loop would do the same); the timed region ends when the last output has reached the host.
+    s_in, s_out = torch.cuda.Stream(device), torch.cuda.Stream(device)
+    slots = 2
+    xs = [x_stage, torch.empty_like(x_dev)]
+    outs = [torch.empty((t, h), dtype=torch.bfloat16, device=device) for _ in range(slots)]
+    out_hosts = [out_host, torch.empty((t, h), dtype=torch.bfloat16).pin_memory()]
+    ev_in = [torch.cuda.Event() for _ in range(slots)]
+    ev_comp = [torch.cuda.Event() for _ in range(slots)]
+    ev_out = [torch.cuda.Event() for _ in range(slots)]
+    counter = {"i": 0}
+
     def end_to_end():
-        x_stage.copy_(x_host, non_blocking=True)
-        out, _ = step(x_stage)
-        out_host.copy_(out, non_blocking=True)
+        i = counter["i"]
+        counter["i"] += 1
+        k2 = i % slots
+        cur = torch.cuda.current_stream(device)
+        with torch.cuda.stream(s_in):
+            if i >= slots:
+                s_in.wait_event(ev_comp[k2])          # the compute that read this token buffer has finished
+            xs[k2].copy_(x_host, non_blocking=True)
+            ev_in[k2].record(s_in)
+        cur.wait_event(ev_in[k2])
+        if i >= slots:
+            cur.wait_event(ev_out[k2])                # this output buffer has been copied out
+        step(xs[k2], outs[k2])
+        ev_comp[k2].record(cur)
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(ev_comp[k2])
+            out_hosts[k2].copy_(outs[k2], non_blocking=True)
+            ev_out[k2].record(s_out)
+
+    def e2e_finish():
+        cur = torch.cuda.current_stream(device)
+        cur.wait_stream(s_in)
+        cur.wait_stream(s_out)
 
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
     ms = timed(resident, args.steps, args.warmup)
     clocks = sampler.stop() if rank == 0 else None
-    ms_e2e = timed(end_to_end, args.steps, max(1, args.warmup))
+    ms_e2e = timed(end_to_end, args.steps, max(1, args.warmup), finish=e2e_finish)
     status = owner.status()
 
     valid = (state["ids"] >= 0).sum().to(torch.float64)

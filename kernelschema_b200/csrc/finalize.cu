@@ -13,7 +13,7 @@ __global__ void __launch_bounds__(128) k_finalize(const __nv_bfloat16* __restric
                                                   __nv_bfloat16* __restrict__ out, int64_t out_stride) {
   const int vecs = H >> 3;
   for (int64_t t = blockIdx.x; t < T; t += gridDim.x) {
-    for (int v = threadIdx.x; v < vecs; v += blockDim.x) {
+    for (int v = blockIdx.y * blockDim.x + threadIdx.x; v < vecs; v += gridDim.y * blockDim.x) {
       float acc[8];
 #pragma unroll
       for (int i = 0; i < 8; ++i) acc[i] = 0.f;
@@ -44,8 +44,11 @@ __global__ void __launch_bounds__(128) k_finalize(const __nv_bfloat16* __restric
 int launch_finalize(const void* rout, const int32_t* row_of, const float* weight_of_row, int64_t T, int KK, int H, void* out,
                     int64_t out_stride, cudaStream_t st) {
   if (T == 0) return 0;
-  int64_t blocks = T < 148 * 16 ? T : 148 * 16;
-  k_finalize<<<(unsigned)blocks, 128, 0, st>>>((const __nv_bfloat16*)rout, row_of, weight_of_row, T, KK, H, (__nv_bfloat16*)out,
+  const int64_t blocks = T < 148 * 16 ? T : 148 * 16;
+  // few tokens: spread each token's row over several blocks so that the whole GPU pulls on HBM
+  const int chunks = (H / 8 + 127) / 128;
+  const int by = blocks >= 148 * 4 ? 1 : (int)(chunks < (148 * 4 + blocks - 1) / blocks ? chunks : (148 * 4 + blocks - 1) / blocks);
+  k_finalize<<<dim3((unsigned)blocks, (unsigned)by), 128, 0, st>>>((const __nv_bfloat16*)rout, row_of, weight_of_row, T, KK, H, (__nv_bfloat16*)out,
                                               out_stride);
   return (int)cudaGetLastError();
 }

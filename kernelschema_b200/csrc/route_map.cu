@@ -179,12 +179,110 @@ __global__ void __launch_bounds__(256) k_route_scatter(RouteView r, const float*
   }
 }
 
+// Whole build in one block when all routes fit one chunk (decode sizes): histogram, scan, tile list, stable scatter,
+// and -1 marks for the padding rows, without the memset and the two extra launches of the general path.
+__global__ void __launch_bounds__(256) k_route_single(RouteView r, const float* __restrict__ scores, int etot, RouteMapBuffers b) {
+  extern __shared__ int hist[];                    // [kRouteWarps][etot], then the running bases
+  __shared__ int warp_pad[8], warp_tiles[8], warp_pairs[8], warp_cnt[8];
+  __shared__ int carry[4];
+  const int kk = r.K + r.S;
+  const int64_t total = r.T * kk;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  chunk_histogram(r, total, etot, hist);
+  if (threadIdx.x < 4) carry[threadIdx.x] = 0;
+  __syncthreads();
+  for (int e0 = 0; e0 < etot; e0 += blockDim.x) {
+    const int e = e0 + threadIdx.x;
+    int cnt = 0;
+    if (e < etot)
+#pragma unroll
+      for (int w = 0; w < kRouteWarps; ++w) cnt += hist[w * etot + e];
+    const int ntile = (cnt + 127) >> 7, pad = ntile << 7, npair = (ntile + 1) >> 1;
+    int ip = pad, it = ntile, ic = cnt, iq = npair;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const int a = __shfl_up_sync(0xFFFFFFFFu, ip, off), c2 = __shfl_up_sync(0xFFFFFFFFu, it, off);
+      const int c3 = __shfl_up_sync(0xFFFFFFFFu, ic, off), c4 = __shfl_up_sync(0xFFFFFFFFu, iq, off);
+      if (lane >= off) { ip += a; it += c2; ic += c3; iq += c4; }
+    }
+    if (lane == 31) { warp_pad[warp] = ip; warp_tiles[warp] = it; warp_cnt[warp] = ic; warp_pairs[warp] = iq; }
+    __syncthreads();
+    int bp = carry[0], bt = carry[1], bq = carry[3];
+    for (int w = 0; w < warp; ++w) { bp += warp_pad[w]; bt += warp_tiles[w]; bq += warp_pairs[w]; }
+    const int start = bp + ip - pad, tile0 = bt + it - ntile, pair0 = bq + iq - npair;
+    if (e < etot) {
+      b.counts[e] = cnt;
+      b.seg_start[e] = start;
+      for (int j = 0; j < ntile; ++j) {
+        b.tile_expert[tile0 + j] = e;
+        b.tile_row0[tile0 + j] = start + (j << 7);
+        b.tile_rows[tile0 + j] = min(128, cnt - (j << 7));
+      }
+      if (b.pair_expert)
+        for (int j = 0; j < npair; ++j) {
+          b.pair_expert[pair0 + j] = e;
+          b.pair_row0[pair0 + j] = start + (j << 8);
+          b.pair_rows[pair0 + j] = min(256, cnt - (j << 8));
+        }
+      for (int rr = start + cnt; rr < start + pad; ++rr) b.tok_of_row[rr] = -1;     // padding rows of the segment
+      int run = start;                               // per-warp bases of this expert, in place of the counts
+#pragma unroll
+      for (int w = 0; w < kRouteWarps; ++w) {
+        const int c = hist[w * etot + e];
+        hist[w * etot + e] = run;
+        run += c;
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x == blockDim.x - 1) {
+      int tc = 0;
+      for (int w = 0; w < (int)(blockDim.x >> 5); ++w) tc += warp_cnt[w];
+      carry[0] = bp + ip;
+      carry[1] = bt + it;
+      carry[2] += tc;
+      carry[3] = bq + iq;
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    b.seg_start[etot] = carry[0];
+    b.totals[0] = carry[1];
+    b.totals[1] = carry[0];
+    b.totals[2] = carry[2];
+    b.totals[3] = carry[3];
+  }
+  const int64_t base = (int64_t)warp * (kRouteChunk / kRouteWarps);
+  for (int step = 0; step < kRouteChunk / kRouteWarps / 32; ++step) {
+    const int64_t f = base + step * 32 + lane;
+    const int e = route_expert(r, f, total);
+    const unsigned m = __match_any_sync(0xFFFFFFFFu, e);
+    int pos = -1;
+    if (e >= 0) pos = hist[warp * etot + e] + __popc(m & ((1u << lane) - 1u));
+    __syncwarp();
+    if (e >= 0 && lane == (__ffs(m) - 1)) hist[warp * etot + e] += __popc(m);
+    __syncwarp();
+    if (f < total) {
+      b.row_of[f] = pos;
+      if (pos >= 0) {
+        const int64_t t = f / kk;
+        const int k = (int)(f - t * kk);
+        b.tok_of_row[pos] = (int32_t)t;
+        b.weight_of_row[pos] = (k < r.K) ? (scores ? scores[t * r.K + k] : 1.0f) : 1.0f;
+      }
+    }
+  }
+}
+
 int launch_route_map(const int32_t* ids, const float* scores, int64_t T, int K, int S, int E, int expert_offset, RouteMapBuffers b,
                      cudaStream_t st) {
   const int etot = E + S;
   const int64_t total = T * (K + S);
   const int nblk = (int)((total + kRouteChunk - 1) / kRouteChunk);
   RouteView r{ids, T, K, S, E, expert_offset};
+  if (nblk == 1) {
+    k_route_single<<<1, 256, sizeof(int) * kRouteWarps * (size_t)etot, st>>>(r, scores, etot, b);
+    return (int)cudaGetLastError();
+  }
   cudaError_t err = cudaMemsetAsync(b.tok_of_row, 0xFF, sizeof(int32_t) * (size_t)b.row_capacity, st);
   if (err != cudaSuccess) return (int)err;
   const size_t smem = sizeof(int) * kRouteWarps * (size_t)etot;
