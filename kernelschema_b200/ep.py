@@ -1,12 +1,20 @@
 """Expert-parallel wrapper: experts sharded contiguously over the ranks of one box, tokens data-parallel.
 
-Per step and rank: bucket the (token, slot) routes by destination rank -> dispatch all-to-all of the NVFP4 rows
-(payload + scale bytes + local expert id) -> grouped FC1/FC2 on the rows received (top-1 "routing" to the local
-expert, weight 1, so the result rows are the per-route bf16 FC2 results of reference.py:91) -> combine all-to-all
-of the bf16 rows back to the source -> routing-weighted sum in slot order on the source (b200moe_combine). The
-shared expert runs on each rank's own tokens. The reference has no multi-GPU path for this operator; its result
-is defined as the single-GPU result. The exchange is `torch.distributed.all_to_all_single` (NCCL over NVLink on
-GPUs; the same code runs on gloo for the CPU tests, where the two compute hooks are replaced by a checker).
+Per step and rank:
+  1. plan: a token goes ONCE to every rank that owns at least one of its experts (not once per route);
+  2. dispatch all-to-all of the NVFP4 rows (payload, scale bytes) with the token's local expert ids and weights;
+  3. the receiving rank runs the ordinary layer on the tokens it got (top-k routing restricted to its experts,
+     ids of foreign experts = -1), i.e. it already applies the routing weights and sums over its own experts:
+     one bf16 partial row per (token, rank);
+  4. combine all-to-all of those partial rows back to the source, received in place;
+  5. the source adds the partial rows (and the shared experts' row, computed locally on a side stream under the
+     exchange) in rank order with `b200moe_combine` and rounds once to bf16.
+A token that visits r ranks costs r rows in each direction instead of top_k: 5.25 instead of 8 on average at
+8 ranks with uniform top-8 routing, at most 2 at 2 ranks. The partial rows are rounded to bf16 before they travel, so
+the result differs from the single-GPU layer by one extra bf16 rounding per visited rank (well inside the
+operator's tolerance). The reference has no multi-GPU path for this operator; its result is defined as the
+single-GPU result. The exchange is `torch.distributed.all_to_all_single` (NCCL over NVLink on GPUs; the same code
+runs on gloo for the CPU tests, where the compute hooks are replaced by a checker).
 """
 from __future__ import annotations
 
@@ -17,21 +25,25 @@ import torch.distributed as dist
 def build_dispatch(ids: torch.Tensor, experts_per_rank: int, world: int):
     """Index plan of one rank. ids int32 [T, K] hold global expert ids (-1 = no route).
 
-    Returns dict: order (flat route indices sorted by destination rank, stable), send_counts [world] (int64, on
-    the ids' device), local_expert (expert id relative to its owner, in send order), pos_of_route [T, K]
-    (position of a route in send order, -1 if invalid).
+    Returns dict: tok (token of every (rank, token) pair to send, sorted by rank then token), dest (its rank),
+    send_counts [world] (int64, on the ids' device), local_ids int32 [n, K] (the token's expert ids relative to the
+    destination rank, -1 for experts that live elsewhere), pos_of_pair int32 [T, world] (position of the pair in
+    send order, -1 if the token does not visit that rank).
     """
-    flat = ids.reshape(-1).to(torch.int64)
-    valid = (flat >= 0) & (flat < experts_per_rank * world)
-    dest = torch.where(valid, flat // experts_per_rank, torch.full_like(flat, world))
-    order = torch.sort(dest, stable=True).indices
-    n_valid = int(valid.sum())
-    order = order[:n_valid]
-    send_counts = torch.bincount(dest[order], minlength=world)[:world]
-    local_expert = (flat[order] % experts_per_rank).to(torch.int32)
-    pos = torch.full_like(flat, -1, dtype=torch.int32)
-    pos[order] = torch.arange(n_valid, dtype=torch.int32, device=ids.device)
-    return dict(order=order, send_counts=send_counts, local_expert=local_expert, pos_of_route=pos.view(ids.shape))
+    t, k = ids.shape
+    idl = ids.to(torch.int64)
+    valid = (idl >= 0) & (idl < experts_per_rank * world)
+    dest_of_route = torch.where(valid, idl // experts_per_rank, torch.full_like(idl, -1))          # [T, K]
+    ranks = torch.arange(world, device=ids.device)
+    visits = (dest_of_route.unsqueeze(-1) == ranks).any(dim=1)                                     # [T, world]
+    pairs = visits.t().nonzero()                                                                   # sorted by rank, then token
+    dest, tok = pairs[:, 0], pairs[:, 1]
+    send_counts = visits.sum(0)
+    on_dest = dest_of_route[tok] == dest.unsqueeze(-1)
+    local_ids = torch.where(on_dest, idl[tok] % experts_per_rank, torch.full_like(idl[tok], -1)).to(torch.int32)
+    pos = torch.full((world, t), -1, dtype=torch.int32, device=ids.device)
+    pos[dest, tok] = torch.arange(tok.numel(), dtype=torch.int32, device=ids.device)
+    return dict(tok=tok, dest=dest, send_counts=send_counts, local_ids=local_ids, pos_of_pair=pos.t().contiguous())
 
 
 def exchange(send: torch.Tensor, send_counts: list[int], recv_counts: list[int], group=None) -> torch.Tensor:
@@ -42,8 +54,8 @@ def exchange(send: torch.Tensor, send_counts: list[int], recv_counts: list[int],
 
 
 class ExpertParallelMoE:
-    """Layer instance on one rank. `expert_rows` and `combine_rows` are the two compute hooks; by default they run
-    libb200moe on the current CUDA device."""
+    """Layer instance on one rank. `expert_rows`, `shared_rows` and `combine_rows` are the compute hooks; by default
+    they run libb200moe on the current CUDA device."""
 
     def __init__(self, hidden, intermediate, num_experts, top_k, tokens_per_rank, num_shared_experts=0, group=None,
                  expert_rows=None, combine_rows=None, shared_rows=None, recv_capacity=None):
@@ -55,28 +67,27 @@ class ExpertParallelMoE:
         self.h, self.i, self.k, self.s = hidden, intermediate, top_k, num_shared_experts
         self.e_local = num_experts // self.world
         self.t = tokens_per_rank
-        self.recv_capacity = recv_capacity or self.world * tokens_per_rank * top_k
+        self.recv_capacity = recv_capacity or self.world * tokens_per_rank      # every token of every rank, at worst
         self._expert_rows = expert_rows or self._cuda_expert_rows
         self._combine_rows = combine_rows or self._cuda_combine_rows
         self._shared_rows = shared_rows or self._cuda_shared_rows
         self._routed = self._shared = None
         self.profile = False
-        # route map memset+3, permute, FC1, FC2, combine for the routed rows (+ the same for the shared expert) + final combine
+        # quantise/route launches are the caller's; here: (route map 3 + permute + FC1 + FC2 + combine) for the received
+        # tokens, the same for the shared experts, and the final combine
         self.launches_per_step = 7 * (2 if num_shared_experts else 1) + 1
 
     # ------------------------------------------------------------------ CUDA hooks
-    def _cuda_expert_rows(self, rows_q, rows_sf, local_expert, w1q, w1s, w2q, w2s, out_rows, kw):
+    def _cuda_expert_rows(self, rows_q, rows_sf, local_ids, weights, w1q, w1s, w2q, w2s, out_rows, kw):
         from .ops import MoELayer
         n = rows_q.shape[0]
         if self._routed is None or self._routed.cfg.max_tokens < n:
             if self._routed is not None:
                 self._routed.close()
-            self._routed = MoELayer(self.h, self.i, self.e_local, 1, max(n, self.recv_capacity))
-        ones = torch.ones((n, 1), dtype=torch.float32, device=rows_q.device)
+            self._routed = MoELayer(self.h, self.i, self.e_local, self.k, max(n, self.recv_capacity))
         e = self.e_local
-        # top-1 "routing" of every received row to its local expert; FC2 writes the per-route rows straight into out_rows
-        self._routed.run(local_expert.view(n, 1), ones, rows_q, rows_sf, w1q[:e], w1s[:e], w2q[:e], w2s[:e], out_rows,
-                         direct_rows=True, **{k: (None if v is None else v[:e]) for k, v in kw.items()})
+        self._routed.run(local_ids, weights, rows_q, rows_sf, w1q[:e], w1s[:e], w2q[:e], w2s[:e], out_rows,
+                         **{k: (None if v is None else v[:e]) for k, v in kw.items()})
 
     def _cuda_shared_rows(self, hq, hs, w1q, w1s, w2q, w2s, out_rows, kw):
         from .ops import MoELayer
@@ -126,10 +137,10 @@ class ExpertParallelMoE:
         recv_counts = recv_counts_t.tolist()
         n_send, n_recv = sum(send_counts), sum(recv_counts)
         if n_recv > self.recv_capacity:
-            raise RuntimeError(f"rank {self.rank} received {n_recv} rows, capacity is {self.recv_capacity}")
+            raise RuntimeError(f"rank {self.rank} received {n_recv} tokens, capacity is {self.recv_capacity}")
         mark("plan+counts")
-        slots = self.k + (1 if self.s else 0)
-        rows_all = torch.empty((n_send + t * (1 if self.s else 0), self.h), dtype=torch.bfloat16, device=dev)
+        shared_slot = 1 if self.s else 0
+        rows_all = torch.empty((n_send + t * shared_slot, self.h), dtype=torch.bfloat16, device=dev)
         side = None
         if self.s:
             # the shared experts only need this rank's own tokens: run them on a side stream under the exchange
@@ -140,31 +151,31 @@ class ExpertParallelMoE:
                     self._shared_rows(hq, hs, w1q, w1s, w2q, w2s, rows_all[n_send:], kw)
             else:
                 self._shared_rows(hq, hs, w1q, w1s, w2q, w2s, rows_all[n_send:], kw)
-        tok = plan["order"] // self.k
+        tok = plan["tok"]
         rows_q = exchange(hq.index_select(0, tok), send_counts, recv_counts, self.group)
         rows_sf = exchange(hs.index_select(0, tok), send_counts, recv_counts, self.group)
-        local_e = exchange(plan["local_expert"], send_counts, recv_counts, self.group)
+        ids_recv = exchange(plan["local_ids"], send_counts, recv_counts, self.group)
+        w_recv = exchange(weights.index_select(0, tok), send_counts, recv_counts, self.group)
         mark("dispatch")
-        # result rows of the routed experts for the rows received, then back to their sources
+        # one partial row per token received: routing-weighted sum over this rank's experts, rounded to bf16
         res = torch.empty((n_recv, self.h), dtype=torch.bfloat16, device=dev)
         if n_recv:
-            self._expert_rows(rows_q, rows_sf, local_e, w1q, w1s, w2q, w2s, res, kw)
+            self._expert_rows(rows_q, rows_sf, ids_recv, w_recv, w1q, w1s, w2q, w2s, res, kw)
         mark("experts")
-        # returned rows first (received in place), the shared experts' rows for the own tokens after them
+        # partial rows return to their sources (received in place), the shared experts' rows come after them
         dist.all_to_all_single(rows_all[:n_send], res, output_split_sizes=send_counts, input_split_sizes=recv_counts,
                                group=self.group)
         mark("combine_a2a")
-        row_of = torch.full((t, slots), -1, dtype=torch.int32, device=dev)
-        row_of[:, :self.k] = plan["pos_of_route"]
+        row_of = torch.full((t, self.world + shared_slot), -1, dtype=torch.int32, device=dev)
+        row_of[:, :self.world] = plan["pos_of_pair"]
         w_rows = torch.ones(rows_all.shape[0], dtype=torch.float32, device=dev)
-        w_rows[:n_send] = weights.reshape(-1)[plan["order"]]
         if self.s:
-            row_of[:, self.k] = n_send + torch.arange(t, dtype=torch.int32, device=dev)
+            row_of[:, self.world] = n_send + torch.arange(t, dtype=torch.int32, device=dev)
             if side is not None:
                 torch.cuda.current_stream(dev).wait_stream(side)
+            mark("shared")
         if out is None:
             out = torch.empty((t, self.h), dtype=torch.bfloat16, device=dev)
-            mark("shared")
         self._combine_rows(rows_all, row_of, w_rows, out)
         mark("combine")
         if marks:
