@@ -407,6 +407,62 @@ def run_gpu(args, wl):
         dist.destroy_process_group()
 
 
+def run_reference_gpu(args, wl):
+    """A/B on identical device inputs: the reference's own Blackwell kernel (oracle/_ref, large-batch chain) against this
+    library, routed experts only (the reference has no shared expert and reads no scale scalars). Not part of the
+    default line; the reference arm proper (`--impl reference`) is the CPU path."""
+    import torch
+    import kernelschema_b200 as ks
+    from oracle import ref_kernel
+    if not ref_kernel.available():
+        print(json.dumps(dict(impl="reference-gpu-kernel", unavailable="oracle/_ref/libnvfp4_moe_ref.so was not built (needs the reference checkout)")))
+        return
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    wl = dict(wl, s=0)
+    L = build_layer(wl, 0, 1, device)
+    t, h, k = wl["t"], wl["h"], wl["k"]
+    x = torch.randn((t, h), device=device).to(torch.bfloat16)
+    hq, hs = ks.nvfp4_quantize(x)
+    ids, w = ks.route_topk(ks.router_logits(x, L["gate_w"]), k, L["bias"])
+    hs8 = hs.view(torch.uint8)
+    alpha = torch.ones(wl["e"], device=device)
+    beta = torch.zeros(wl["e"], device=device)
+    out_ref = torch.zeros((t, h), dtype=torch.bfloat16, device=device)
+    out_mine = torch.zeros((t, h), dtype=torch.bfloat16, device=device)
+    rk = ref_kernel.ReferenceKernel()
+    layer = ks.MoELayer(h, wl["i"], wl["e"], k, t)
+
+    def run_ref():
+        rk.run(ids, w, hq, hs8, L["w1q"], L["w1s"], L["w2q"], L["w2s"], alpha, beta, None, out_ref)
+
+    def run_mine():
+        layer.run(ids, w, hq, hs8, L["w1q"], L["w1s"], L["w2q"], L["w2s"], out_mine, alpha=alpha, beta=beta)
+
+    res = {}
+    for name, fn in (("reference", run_ref), ("this_library", run_mine)):
+        for _ in range(max(3, args.warmup)):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        res[name] = e0.elapsed_time(e1) / args.steps
+    flops = 6.0 * float((ids >= 0).sum()) * wl["i"] * h
+    diff = (out_ref.float() - out_mine.float())
+    rel_l2 = float(diff.norm() / out_ref.float().norm().clamp_min(1e-30))
+    print(json.dumps(dict(impl="reference-gpu-kernel", metric="nvfp4_moe_layer_tflops", unit="TFLOP/s",
+                          value=flops / (res["reference"] * 1e-3) / 1e12, ms_per_step=res["reference"], n_gpus=1,
+                          steps=args.steps, warmup=args.warmup, higher_is_better=True, data="synthetic",
+                          config=dict(workload=wl["label"] + "_routed_experts_only", chain="GEMM1 rung 97, GEMM2 rung 81, graph replay off"),
+                          this_library_same_inputs=dict(value=flops / (res["this_library"] * 1e-3) / 1e12, ms_per_step=res["this_library"],
+                                                        rel_l2_vs_reference_kernel=rel_l2, device_status=layer.status()),
+                          speedup_over_reference_kernel=res["reference"] / res["this_library"])))
+
+
 def run_dense(args):
     """Single-expert dense NVFP4 GEMM (A quantised on the device, B pre-quantised): the mainloop in isolation."""
     import torch
@@ -440,7 +496,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference", "reference-gpu"])
     ap.add_argument("--workload", default="dsv3", choices=sorted(WORKLOADS))
     ap.add_argument("--zipf", type=float, default=None, help="override the workload's Zipf exponent of the router bias (0 = uniform)")
     ap.add_argument("--tokens", type=int, default=None, help="override the workload's tokens per GPU (e.g. 64 or 256 for decode)")
@@ -457,7 +513,9 @@ def main():
     if args.zipf is not None:
         wl["zipf"] = args.zipf
         wl["label"] += f"_zipf{args.zipf:g}_override"
-    if args.impl == "reference":
+    if args.impl == "reference-gpu":
+        run_reference_gpu(args, wl)
+    elif args.impl == "reference":
         run_reference(args, wl)
     else:
         run_gpu(args, wl)
