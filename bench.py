@@ -114,7 +114,7 @@ class ClockSampler:
 
 
 # --------------------------------------------------------------------------------------------- synthetic layer
-def build_layer(wl, rank, world, device):
+def build_layer(wl, rank, world, device, global_scales=True):
     """Random-init weights of the named geometry, quantised on the device with per-expert global scales
     amax/(6*448); the routed experts are sharded contiguously over the ranks, the shared expert is replicated."""
     import torch
@@ -135,12 +135,12 @@ def build_layer(wl, rank, world, device):
         else:
             gen_j = gen
         w = (torch.randn((2 * i, h), device=device, generator=gen_j) * 0.02).to(torch.bfloat16)
-        g1[j] = w.float().abs().max() / (6.0 * 448.0)
+        g1[j] = w.float().abs().max() / (6.0 * 448.0) if global_scales else 1.0
         q, sf = ks.nvfp4_quantize(w, float(g1[j]), tiled_scales=True)
         w1q[j] = q
         w1s[j] = sf.reshape(2 * i, h // 16)
         w = (torch.randn((h, i), device=device, generator=gen_j) * 0.02).to(torch.bfloat16)
-        g2[j] = w.float().abs().max() / (6.0 * 448.0)
+        g2[j] = w.float().abs().max() / (6.0 * 448.0) if global_scales else 1.0
         q, sf = ks.nvfp4_quantize(w, float(g2[j]), tiled_scales=True)
         w2q[j] = q
         w2s[j] = sf.reshape(h, i // 16)
@@ -420,7 +420,7 @@ def run_reference_gpu(args, wl):
     device = torch.device("cuda", 0)
     torch.cuda.set_device(0)
     wl = dict(wl, s=0)
-    L = build_layer(wl, 0, 1, device)
+    L = build_layer(wl, 0, 1, device, global_scales=False)      # the reference reads no scale scalars
     t, h, k = wl["t"], wl["h"], wl["k"]
     x = torch.randn((t, h), device=device).to(torch.bfloat16)
     hq, hs = ks.nvfp4_quantize(x)
@@ -459,7 +459,9 @@ def run_reference_gpu(args, wl):
                           steps=args.steps, warmup=args.warmup, higher_is_better=True, data="synthetic",
                           config=dict(workload=wl["label"] + "_routed_experts_only", chain="GEMM1 rung 97, GEMM2 rung 81, graph replay off"),
                           this_library_same_inputs=dict(value=flops / (res["this_library"] * 1e-3) / 1e12, ms_per_step=res["this_library"],
-                                                        rel_l2_vs_reference_kernel=rel_l2, device_status=layer.status()),
+                                                        rel_l2_vs_reference_kernel=rel_l2, device_status=layer.status(),
+                                                        output_rms=float(out_mine.float().pow(2).mean().sqrt()),
+                                                        reference_output_rms=float(out_ref.float().pow(2).mean().sqrt())),
                           speedup_over_reference_kernel=res["reference"] / res["this_library"])))
 
 
