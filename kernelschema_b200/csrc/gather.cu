@@ -9,31 +9,34 @@
 
 namespace b200 {
 
-__global__ void __launch_bounds__(128) k_gather_rows(const uint8_t* __restrict__ hid_q, const uint8_t* __restrict__ hid_sf,
+__global__ void __launch_bounds__(256) k_gather_rows(const uint8_t* __restrict__ hid_q, const uint8_t* __restrict__ hid_sf,
                                                      int hid_sf_tiled, const int32_t* __restrict__ tok_of_row,
                                                      const int32_t* __restrict__ totals, int H, uint8_t* __restrict__ a_q,
                                                      uint8_t* __restrict__ a_sf) {
+  // one warp per permuted row, 16 bytes per lane and step
   const int rows = totals[1];
+  const int lane = threadIdx.x & 31;
   const int vec_per_row = H >> 5;      // 16-byte vectors of payload per row (H/2 bytes)
   const int words_per_row = H >> 6;    // 4-byte scale words per row (H/16 bytes)
-  for (int r = blockIdx.x; r < rows; r += gridDim.x) {
+  const int warps = (gridDim.x * blockDim.x) >> 5;
+  for (int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < rows; r += warps) {
     const int tok = tok_of_row[r];
     uint32_t* sf_dst = reinterpret_cast<uint32_t*>(a_sf + (size_t)(r >> 7) * words_per_row * 512 + (size_t)(r & 31) * 16 +
                                                    (size_t)((r >> 5) & 3) * 4);
     if (tok < 0) {
-      for (int w = threadIdx.x; w < words_per_row; w += blockDim.x) sf_dst[(size_t)w * 128] = 0u;
+      for (int w = lane; w < words_per_row; w += 32) sf_dst[(size_t)w * 128] = 0u;
       continue;
     }
     const uint4* src = reinterpret_cast<const uint4*>(hid_q + (size_t)tok * (H >> 1));
     uint4* dst = reinterpret_cast<uint4*>(a_q + (size_t)r * (H >> 1));
-    for (int v = threadIdx.x; v < vec_per_row; v += blockDim.x) dst[v] = __ldg(src + v);
+    for (int v = lane; v < vec_per_row; v += 32) dst[v] = __ldg(src + v);
     if (hid_sf_tiled) {
       const uint32_t* sf_src = reinterpret_cast<const uint32_t*>(hid_sf + (size_t)(tok >> 7) * words_per_row * 512 +
                                                                  (size_t)(tok & 31) * 16 + (size_t)((tok >> 5) & 3) * 4);
-      for (int w = threadIdx.x; w < words_per_row; w += blockDim.x) sf_dst[(size_t)w * 128] = __ldg(sf_src + (size_t)w * 128);
+      for (int w = lane; w < words_per_row; w += 32) sf_dst[(size_t)w * 128] = __ldg(sf_src + (size_t)w * 128);
     } else {
       const uint32_t* sf_src = reinterpret_cast<const uint32_t*>(hid_sf + (size_t)tok * (H >> 4));
-      for (int w = threadIdx.x; w < words_per_row; w += blockDim.x) sf_dst[(size_t)w * 128] = __ldg(sf_src + w);
+      for (int w = lane; w < words_per_row; w += 32) sf_dst[(size_t)w * 128] = __ldg(sf_src + w);
     }
   }
 }
@@ -41,8 +44,9 @@ __global__ void __launch_bounds__(128) k_gather_rows(const uint8_t* __restrict__
 int launch_gather_rows(const void* hid_q, const void* hid_sf, int hid_sf_tiled, const int32_t* tok_of_row, const int32_t* totals,
                        int H, int64_t row_capacity, void* a_q, void* a_sf, cudaStream_t st) {
   if (row_capacity == 0) return 0;
-  int64_t blocks = row_capacity < 148 * 16 ? row_capacity : 148 * 16;
-  k_gather_rows<<<(unsigned)blocks, 128, 0, st>>>((const uint8_t*)hid_q, (const uint8_t*)hid_sf, hid_sf_tiled, tok_of_row, totals,
+  int64_t blocks = (row_capacity + 7) / 8;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  k_gather_rows<<<(unsigned)blocks, 256, 0, st>>>((const uint8_t*)hid_q, (const uint8_t*)hid_sf, hid_sf_tiled, tok_of_row, totals,
                                                  H, (uint8_t*)a_q, (uint8_t*)a_sf);
   return (int)cudaGetLastError();
 }

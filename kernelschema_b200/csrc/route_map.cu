@@ -78,10 +78,17 @@ __global__ void __launch_bounds__(1024) k_route_scan(int etot, int nblk, int32_t
     const int e = e0 + threadIdx.x;
     int cnt = 0;
     if (e < etot) {
-      for (int b = 0; b < nblk; ++b) {
-        const int v = block_hist[(int64_t)b * etot + e];
-        block_hist[(int64_t)b * etot + e] = cnt;
-        cnt += v;
+      // exclusive prefix over the blocks; loads run 8 ahead of the stores so their latencies overlap
+      for (int b0 = 0; b0 < nblk; b0 += 8) {
+        int v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = (b0 + j < nblk) ? block_hist[(int64_t)(b0 + j) * etot + e] : 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (b0 + j < nblk) {
+            block_hist[(int64_t)(b0 + j) * etot + e] = cnt;
+            cnt += v[j];
+          }
       }
       counts[e] = cnt;
     }

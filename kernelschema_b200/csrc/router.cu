@@ -10,20 +10,19 @@
 
 namespace b200 {
 
-constexpr int kMaxExpertsPerLane = 32;   // E <= 1024
-
+// PL = logits kept per lane (experts <= 32 * PL); the loops are unrolled for the instantiated size only.
+template <int PL>
 __global__ void __launch_bounds__(256) k_route_topk(const float* __restrict__ logits, const float* __restrict__ bias, int64_t T,
                                                     int E, int K, int32_t* __restrict__ ids, float* __restrict__ weights) {
   const int lane = threadIdx.x & 31;
   const int64_t tok = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   if (tok >= T) return;
-  float v[kMaxExpertsPerLane];
-  const int per_lane = (E + 31) >> 5;
+  float v[PL];
 #pragma unroll
-  for (int i = 0; i < kMaxExpertsPerLane; ++i) {
+  for (int i = 0; i < PL; ++i) {
     const int e = i * 32 + lane;
     float x = -INFINITY;
-    if (i < per_lane && e < E) {
+    if (e < E) {
       x = logits[tok * E + e];
       if (bias) x = __fadd_rn(x, bias[e]);
     }
@@ -35,11 +34,9 @@ __global__ void __launch_bounds__(256) k_route_topk(const float* __restrict__ lo
     float best = -INFINITY;
     int best_e = 0x7FFFFFFF;
 #pragma unroll
-    for (int i = 0; i < kMaxExpertsPerLane; ++i) {
-      if (i < per_lane) {
-        const int e = i * 32 + lane;
-        if (e < E && (v[i] > best)) { best = v[i]; best_e = e; }
-      }
+    for (int i = 0; i < PL; ++i) {
+      const int e = i * 32 + lane;
+      if (e < E && (v[i] > best)) { best = v[i]; best_e = e; }
     }
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) {
@@ -50,7 +47,7 @@ __global__ void __launch_bounds__(256) k_route_topk(const float* __restrict__ lo
     if (lane == k) { sel = best; sel_id = best_e; }
     if ((best_e & 31) == lane) {
 #pragma unroll
-      for (int i = 0; i < kMaxExpertsPerLane; ++i)
+      for (int i = 0; i < PL; ++i)
         if (i == (best_e >> 5)) v[i] = -INFINITY;
     }
   }
@@ -236,8 +233,14 @@ int launch_router_logits_tc(const void* x, const void* w, int64_t T, int H, int 
 int launch_route_topk(const float* logits, const float* bias, int64_t T, int E, int K, int32_t* ids, float* weights,
                       cudaStream_t st) {
   if (T == 0) return 0;
-  const int64_t blocks = (T * 32 + 255) / 256;
-  k_route_topk<<<(unsigned)blocks, 256, 0, st>>>(logits, bias, T, E, K, ids, weights);
+  const unsigned blocks = (unsigned)((T * 32 + 255) / 256);
+  const int per_lane = (E + 31) / 32;
+  if (per_lane <= 1) k_route_topk<1><<<blocks, 256, 0, st>>>(logits, bias, T, E, K, ids, weights);
+  else if (per_lane <= 2) k_route_topk<2><<<blocks, 256, 0, st>>>(logits, bias, T, E, K, ids, weights);
+  else if (per_lane <= 4) k_route_topk<4><<<blocks, 256, 0, st>>>(logits, bias, T, E, K, ids, weights);
+  else if (per_lane <= 8) k_route_topk<8><<<blocks, 256, 0, st>>>(logits, bias, T, E, K, ids, weights);
+  else if (per_lane <= 16) k_route_topk<16><<<blocks, 256, 0, st>>>(logits, bias, T, E, K, ids, weights);
+  else k_route_topk<32><<<blocks, 256, 0, st>>>(logits, bias, T, E, K, ids, weights);
   return (int)cudaGetLastError();
 }
 
