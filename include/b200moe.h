@@ -83,7 +83,7 @@ typedef struct {
   int32_t* tile_rows;     /* [tile_capacity] */
   int32_t* totals;        /* {m-tiles, permuted rows in use, valid routes, 256-row pair items} */
   int32_t* row_of;        /* [T, top_k+S] permuted row of a route or -1 */
-  int32_t* tok_of_row;    /* [row_capacity] token of a permuted row or -1 */
+  int32_t* tok_of_row;    /* [row_capacity] token of a permuted row; defined for the first tile_rows[r/128] rows of each 128-row tile */
   float* weight_of_row;   /* [row_capacity] */
   uint8_t* a_q;           /* [row_capacity, H/2] permuted activations */
   uint8_t* a_sf;          /* tiled scales of a_q */

@@ -147,7 +147,7 @@ int run_impl(b200moe_layer* h, const b200moe_args* a, cudaStream_t st, cudaEvent
   if (rc) return cuda_fail(rc, "route map");
   mark(1);
   rc = launch_gather_rows(a->hidden_states, a->hidden_states_scale, a->hidden_states_scale_layout == 1, h->rm.tok_of_row,
-                          h->rm.totals, c.hidden, h->row_capacity, h->a_q, h->a_sf, st);
+                          h->rm.tile_rows, h->rm.totals, c.hidden, h->row_capacity, h->a_q, h->a_sf, st);
   if (rc) return cuda_fail(rc, "permute");
   mark(2);
   if (h->b1_ptr != a->gemm1_weights || h->s1_ptr != a->gemm1_weights_scale) {

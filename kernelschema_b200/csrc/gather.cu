@@ -11,6 +11,7 @@ namespace b200 {
 
 __global__ void __launch_bounds__(256) k_gather_rows(const uint8_t* __restrict__ hid_q, const uint8_t* __restrict__ hid_sf,
                                                      int hid_sf_tiled, const int32_t* __restrict__ tok_of_row,
+                                                     const int32_t* __restrict__ tile_rows,
                                                      const int32_t* __restrict__ totals, int H, uint8_t* __restrict__ a_q,
                                                      uint8_t* __restrict__ a_sf) {
   // one warp per permuted row, 16 bytes per lane and step
@@ -20,7 +21,8 @@ __global__ void __launch_bounds__(256) k_gather_rows(const uint8_t* __restrict__
   const int words_per_row = H >> 6;    // 4-byte scale words per row (H/16 bytes)
   const int warps = (gridDim.x * blockDim.x) >> 5;
   for (int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < rows; r += warps) {
-    const int tok = tok_of_row[r];
+    // segments are 128-row aligned and consecutive, so row r belongs to tile r / 128; rows past the tile's count are padding
+    const int tok = ((r & 127) < tile_rows[r >> 7]) ? tok_of_row[r] : -1;
     uint32_t* sf_dst = reinterpret_cast<uint32_t*>(a_sf + (size_t)(r >> 7) * words_per_row * 512 + (size_t)(r & 31) * 16 +
                                                    (size_t)((r >> 5) & 3) * 4);
     if (tok < 0) {
@@ -41,13 +43,14 @@ __global__ void __launch_bounds__(256) k_gather_rows(const uint8_t* __restrict__
   }
 }
 
-int launch_gather_rows(const void* hid_q, const void* hid_sf, int hid_sf_tiled, const int32_t* tok_of_row, const int32_t* totals,
+int launch_gather_rows(const void* hid_q, const void* hid_sf, int hid_sf_tiled, const int32_t* tok_of_row, const int32_t* tile_rows,
+                       const int32_t* totals,
                        int H, int64_t row_capacity, void* a_q, void* a_sf, cudaStream_t st) {
   if (row_capacity == 0) return 0;
   int64_t blocks = (row_capacity + 7) / 8;
-  if (blocks > 148 * 16) blocks = 148 * 16;
-  k_gather_rows<<<(unsigned)blocks, 256, 0, st>>>((const uint8_t*)hid_q, (const uint8_t*)hid_sf, hid_sf_tiled, tok_of_row, totals,
-                                                 H, (uint8_t*)a_q, (uint8_t*)a_sf);
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  k_gather_rows<<<(unsigned)blocks, 256, 0, st>>>((const uint8_t*)hid_q, (const uint8_t*)hid_sf, hid_sf_tiled, tok_of_row, tile_rows,
+                                                 totals, H, (uint8_t*)a_q, (uint8_t*)a_sf);
   return (int)cudaGetLastError();
 }
 

@@ -22,7 +22,7 @@ struct RouteMapBuffers {
   int32_t* pair_row0;      // [tile_capacity]
   int32_t* pair_rows;      // [tile_capacity] valid rows of the pair (1..256)
   int32_t* row_of;         // [T, K'] permuted row of a route, -1 when invalid
-  int32_t* tok_of_row;     // [row_capacity] token of a permuted row, -1 for padding
+  int32_t* tok_of_row;     // [row_capacity] token of a permuted row; padding rows (past tile_rows of tile row/128) are unspecified
   float* weight_of_row;    // [row_capacity] routing weight of a permuted row
   int64_t row_capacity;
 };
@@ -66,7 +66,8 @@ int launch_route_map(const int32_t* ids, const float* scores, int64_t T, int K, 
                      cudaStream_t st);
 int launch_route_map_static(const int32_t* ids, const float* scores, int64_t T, int K, int S, int E, int expert_offset,
                             RouteMapBuffers b, cudaStream_t st);
-int launch_gather_rows(const void* hid_q, const void* hid_sf, int hid_sf_tiled, const int32_t* tok_of_row, const int32_t* totals,
+int launch_gather_rows(const void* hid_q, const void* hid_sf, int hid_sf_tiled, const int32_t* tok_of_row, const int32_t* tile_rows,
+                       const int32_t* totals,
                        int H, int64_t row_capacity, void* a_q, void* a_sf, cudaStream_t st);
 int launch_finalize(const void* rout, const int32_t* row_of, const float* weight_of_row, int64_t T, int KK, int H, void* out,
                     int64_t out_stride, cudaStream_t st);

@@ -34,16 +34,25 @@ DEV int route_expert(const RouteView& r, int64_t f, int64_t total) {
   return (e >= 0 && e < r.E) ? e : -1;
 }
 
+constexpr int kRouteSteps = kRouteChunk / kRouteWarps / 32;   // routes per lane in a chunk
+
+// Expert of each of this lane's routes in the block's chunk: all loads are issued before any is used.
+DEV void load_chunk(const RouteView& r, int64_t total, int64_t chunk_base, int (&e)[kRouteSteps]) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t base = chunk_base + warp * (kRouteChunk / kRouteWarps);
+#pragma unroll
+  for (int step = 0; step < kRouteSteps; ++step) e[step] = route_expert(r, base + step * 32 + lane, total);
+}
+
 // Per-warp histograms of this block's chunk into hist[warp][e]; each warp owns its row, so no atomics.
-DEV void chunk_histogram(const RouteView& r, int64_t total, int etot, int* hist) {
+DEV void chunk_histogram(const int (&e)[kRouteSteps], int etot, int* hist) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   for (int i = threadIdx.x; i < kRouteWarps * etot; i += blockDim.x) hist[i] = 0;
   __syncthreads();
-  const int64_t base = (int64_t)blockIdx.x * kRouteChunk + warp * (kRouteChunk / kRouteWarps);
-  for (int step = 0; step < kRouteChunk / kRouteWarps / 32; ++step) {
-    const int e = route_expert(r, base + step * 32 + lane, total);
-    const unsigned m = __match_any_sync(0xFFFFFFFFu, e);
-    if (e >= 0 && lane == (__ffs(m) - 1)) hist[warp * etot + e] += __popc(m);
+#pragma unroll
+  for (int step = 0; step < kRouteSteps; ++step) {
+    const unsigned m = __match_any_sync(0xFFFFFFFFu, e[step]);
+    if (e[step] >= 0 && lane == (__ffs(m) - 1)) hist[warp * etot + e[step]] += __popc(m);
     __syncwarp();
   }
   __syncthreads();
@@ -52,7 +61,9 @@ DEV void chunk_histogram(const RouteView& r, int64_t total, int etot, int* hist)
 __global__ void __launch_bounds__(256) k_route_hist(RouteView r, int etot, int32_t* __restrict__ block_hist) {
   extern __shared__ int hist[];
   const int64_t total = r.T * (r.K + r.S);
-  chunk_histogram(r, total, etot, hist);
+  int ex[kRouteSteps];
+  load_chunk(r, total, (int64_t)blockIdx.x * kRouteChunk, ex);
+  chunk_histogram(ex, etot, hist);
   for (int e = threadIdx.x; e < etot; e += blockDim.x) {
     int s = 0;
 #pragma unroll
@@ -152,7 +163,9 @@ __global__ void __launch_bounds__(256) k_route_scatter(RouteView r, const float*
   extern __shared__ int hist[];
   const int kk = r.K + r.S;
   const int64_t total = r.T * kk;
-  chunk_histogram(r, total, etot, hist);
+  int ex[kRouteSteps];
+  load_chunk(r, total, (int64_t)blockIdx.x * kRouteChunk, ex);
+  chunk_histogram(ex, etot, hist);
   for (int e = threadIdx.x; e < etot; e += blockDim.x) {
     int run = seg_start[e] + block_base[(int64_t)blockIdx.x * etot + e];
 #pragma unroll
@@ -165,9 +178,10 @@ __global__ void __launch_bounds__(256) k_route_scatter(RouteView r, const float*
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t base = (int64_t)blockIdx.x * kRouteChunk + warp * (kRouteChunk / kRouteWarps);
-  for (int step = 0; step < kRouteChunk / kRouteWarps / 32; ++step) {
+#pragma unroll
+  for (int step = 0; step < kRouteSteps; ++step) {
     const int64_t f = base + step * 32 + lane;
-    const int e = route_expert(r, f, total);
+    const int e = ex[step];
     const unsigned m = __match_any_sync(0xFFFFFFFFu, e);
     int pos = -1;
     if (e >= 0) pos = hist[warp * etot + e] + __popc(m & ((1u << lane) - 1u));
@@ -187,7 +201,7 @@ __global__ void __launch_bounds__(256) k_route_scatter(RouteView r, const float*
 }
 
 // Whole build in one block when all routes fit one chunk (decode sizes): histogram, scan, tile list, stable scatter,
-// and -1 marks for the padding rows, without the memset and the two extra launches of the general path.
+// in one launch instead of three.
 __global__ void __launch_bounds__(256) k_route_single(RouteView r, const float* __restrict__ scores, int etot, RouteMapBuffers b) {
   extern __shared__ int hist[];                    // [kRouteWarps][etot], then the running bases
   __shared__ int warp_pad[8], warp_tiles[8], warp_pairs[8], warp_cnt[8];
@@ -195,7 +209,9 @@ __global__ void __launch_bounds__(256) k_route_single(RouteView r, const float* 
   const int kk = r.K + r.S;
   const int64_t total = r.T * kk;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  chunk_histogram(r, total, etot, hist);
+  int ex[kRouteSteps];
+  load_chunk(r, total, 0, ex);
+  chunk_histogram(ex, etot, hist);
   if (threadIdx.x < 4) carry[threadIdx.x] = 0;
   __syncthreads();
   for (int e0 = 0; e0 < etot; e0 += blockDim.x) {
@@ -231,7 +247,6 @@ __global__ void __launch_bounds__(256) k_route_single(RouteView r, const float* 
           b.pair_row0[pair0 + j] = start + (j << 8);
           b.pair_rows[pair0 + j] = min(256, cnt - (j << 8));
         }
-      for (int rr = start + cnt; rr < start + pad; ++rr) b.tok_of_row[rr] = -1;     // padding rows of the segment
       int run = start;                               // per-warp bases of this expert, in place of the counts
 #pragma unroll
       for (int w = 0; w < kRouteWarps; ++w) {
@@ -259,9 +274,10 @@ __global__ void __launch_bounds__(256) k_route_single(RouteView r, const float* 
     b.totals[3] = carry[3];
   }
   const int64_t base = (int64_t)warp * (kRouteChunk / kRouteWarps);
-  for (int step = 0; step < kRouteChunk / kRouteWarps / 32; ++step) {
+#pragma unroll
+  for (int step = 0; step < kRouteSteps; ++step) {
     const int64_t f = base + step * 32 + lane;
-    const int e = route_expert(r, f, total);
+    const int e = ex[step];
     const unsigned m = __match_any_sync(0xFFFFFFFFu, e);
     int pos = -1;
     if (e >= 0) pos = hist[warp * etot + e] + __popc(m & ((1u << lane) - 1u));
@@ -290,8 +306,6 @@ int launch_route_map(const int32_t* ids, const float* scores, int64_t T, int K, 
     k_route_single<<<1, 256, sizeof(int) * kRouteWarps * (size_t)etot, st>>>(r, scores, etot, b);
     return (int)cudaGetLastError();
   }
-  cudaError_t err = cudaMemsetAsync(b.tok_of_row, 0xFF, sizeof(int32_t) * (size_t)b.row_capacity, st);
-  if (err != cudaSuccess) return (int)err;
   const size_t smem = sizeof(int) * kRouteWarps * (size_t)etot;
   if (nblk > 0) k_route_hist<<<nblk, 256, smem, st>>>(r, etot, b.block_hist);
   k_route_scan<<<1, 1024, 0, st>>>(etot, nblk, b.block_hist, b.counts, b.seg_start, b.tile_expert, b.tile_row0, b.tile_rows,
