@@ -5,6 +5,8 @@
 //   gemm/dense/bf16_nvfp4_gemm/problem/input.py:40-64     (global scale != 1)
 // One thread owns one 16-element block: two 128-bit loads, one 64-bit payload store, one scale byte.
 // HBM-bound: 2 B read + 0.5625 B written per element.
+#include <math.h>
+
 #include "kernels.cuh"
 #include "ptx.cuh"
 
@@ -17,9 +19,11 @@ DEV size_t sf_tiled_offset(int64_t row, int64_t blk, int64_t chunks_per_row) {
          (size_t)(blk & 3);
 }
 
+// GLOBAL_SCALE = false also serves power-of-two global scales: dividing by 2^k is exact, so
+// quantize(x, 2^k) == quantize(x * 2^-k, 1) bit for bit and `prescale` = 2^-k is applied to the loaded values.
 template <bool GLOBAL_SCALE>
 __global__ void __launch_bounds__(256) k_quantize_nvfp4(const __nv_bfloat16* __restrict__ x, int64_t rows, int64_t cols,
-                                                        int64_t row_stride, float gs, uint8_t* __restrict__ payload,
+                                                        int64_t row_stride, float gs, float prescale, uint8_t* __restrict__ payload,
                                                         uint8_t* __restrict__ scales, int sf_layout) {
   // One block walks rows, its threads walk the 16-element blocks of a row: no integer division anywhere.
   const int blocks_per_row = (int)(cols >> 4);
@@ -35,6 +39,7 @@ __global__ void __launch_bounds__(256) k_quantize_nvfp4(const __nv_bfloat16* __r
     for (int i = 0; i < 8; ++i) {
       v[2 * i] = __uint_as_float(w[i] << 16);
       v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+      if (!GLOBAL_SCALE) { v[2 * i] *= prescale; v[2 * i + 1] *= prescale; }
     }
     float peak = 0.f;
 #pragma unroll
@@ -107,11 +112,14 @@ int launch_quantize_nvfp4(const void* x, int64_t rows, int64_t cols, int64_t row
   int threads = ((bpr + passes - 1) / passes + 31) / 32 * 32;
   if (threads > 256) threads = 256;
   const int64_t blocks = rows < 148LL * 32 ? rows : 148LL * 32;
-  if (gs == 1.0f)
+  int exp2 = 0;
+  const bool pow2 = frexpf(gs, &exp2) == 0.5f && exp2 > -100 && exp2 < 100;     // gs = 2^(exp2-1): exact pre-scaling
+  if (pow2)
     k_quantize_nvfp4<false><<<(unsigned)blocks, threads, 0, st>>>((const __nv_bfloat16*)x, rows, cols, row_stride, gs,
-                                                                 (uint8_t*)payload, (uint8_t*)scales, sf_layout);
+                                                                 ldexpf(1.0f, 1 - exp2), (uint8_t*)payload, (uint8_t*)scales,
+                                                                 sf_layout);
   else
-    k_quantize_nvfp4<true><<<(unsigned)blocks, threads, 0, st>>>((const __nv_bfloat16*)x, rows, cols, row_stride, gs,
+    k_quantize_nvfp4<true><<<(unsigned)blocks, threads, 0, st>>>((const __nv_bfloat16*)x, rows, cols, row_stride, gs, 1.0f,
                                                                 (uint8_t*)payload, (uint8_t*)scales, sf_layout);
   return (int)cudaGetLastError();
 }

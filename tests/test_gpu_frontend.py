@@ -36,11 +36,11 @@ def test_quantize_matches_oracle(rows, cols, scale):
     assert np.array_equal(q.cpu().numpy(), oq)
     assert np.array_equal(s.view(torch.uint8).cpu().numpy(), os_)
     if rows:
-        gs = float(x.float().abs().max() / (6 * 448))
-        q, s = ks.nvfp4_quantize(x.cuda(), gs)
-        oq, os_ = o.quantize(x.float().numpy(), 16, gs)
-        assert np.array_equal(q.cpu().numpy(), oq)
-        assert np.array_equal(s.view(torch.uint8).cpu().numpy(), os_)
+        for gs in (float(x.float().abs().max() / (6 * 448)), 2.0 ** -9, 4.0):      # general, and exact power-of-two scales
+            q, s = ks.nvfp4_quantize(x.cuda(), gs)
+            oq, os_ = o.quantize(x.float().numpy(), 16, gs)
+            assert np.array_equal(q.cpu().numpy(), oq), gs
+            assert np.array_equal(s.view(torch.uint8).cpu().numpy(), os_), gs
         # tiled scale layout = block_scales() of the row-major bytes
         q2, st = ks.nvfp4_quantize(x.cuda(), 1.0, tiled_scales=True)
         ref_t = o.block_scales(o.quantize(x.float().numpy())[1][None])[0]
