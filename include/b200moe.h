@@ -22,7 +22,7 @@
 extern "C" {
 #endif
 
-#define B200MOE_ABI_VERSION 1
+#define B200MOE_ABI_VERSION 2
 
 /* Scale-factor layouts. */
 #define B200MOE_SF_ROW_MAJOR 0 /* [rows, cols/16]                                   */
@@ -71,6 +71,9 @@ typedef struct {
                                         combine pass is skipped; used by the expert-parallel wrapper on received rows */
   void* output;                      /* bf16 [T, H]; the only caller memory that is written */
   int64_t output_stride;             /* elements between output rows (H when contiguous) */
+  int64_t hidden_states_stride;      /* bytes between payload rows; 0 = H/2 (contiguous). Multiple of 16 */
+  int64_t hidden_states_scale_stride;/* bytes between row-major scale rows; 0 = H/16. Multiple of 4; layout 2 only */
+  int64_t topk_stride;               /* elements between the rows of topk_ids / topk_weights; 0 = top_k */
 } b200moe_args;
 
 /* Device pointers into the library-owned workspace of a layer, for tests and for the expert-parallel
@@ -147,6 +150,22 @@ int b200moe_route_map(b200moe_handle h, const int32_t* topk_ids, const float* to
  * wrapper calls it on the rows returned by the combine all-to-all. */
 int b200moe_combine(const void* rows, const int32_t* row_of, const float* weight_of_row, int64_t num_tokens, int32_t slots,
                     int32_t hidden, void* out, int64_t out_stride, void* stream);
+
+/* Expert-parallel dispatch helpers (the reference has no multi-GPU path; no counterpart there).
+ * ep_visits: rank_slots[t, r] = r if token t has a route to an expert owned by rank r (experts are sharded
+ * contiguously, experts_per_rank each), else -1. Feeding rank_slots to b200moe_route_map of a "plan" layer created with
+ * num_experts = world and top_k = world yields the send order (tok_of_row), the 128-row aligned per-rank segments
+ * (seg_start) and the position of every (token, rank) pair (row_of).
+ * ep_pack: gathers one message row per pair of that plan into `out` ([rows, row_bytes] bytes): payload H/2 | scale
+ * bytes H/16 | top_k local expert ids (int32, -1 for experts of other ranks) | top_k weights (fp32); padding rows of a
+ * segment get ids = -1. The plan may carry one shared-expert slot (num_shared_experts = 1): its rows follow the last rank's
+ * segment, are not messages and are skipped here, but give the caller row_of[:, world] for the locally computed shared
+ * row. The receiver runs b200moe_run directly on the message buffer through the *_stride fields. */
+int b200moe_ep_visits(const int32_t* topk_ids, int64_t num_tokens, int32_t top_k, int32_t experts_per_rank, int32_t world,
+                      int32_t* rank_slots, void* stream);
+int b200moe_ep_pack(b200moe_handle plan, const void* hidden_states, const void* hidden_states_scale, const int32_t* topk_ids,
+                    const float* topk_weights, int32_t hidden, int32_t top_k, int32_t experts_per_rank, int64_t row_bytes, void* out,
+                    void* stream);
 
 /* Route-map build for callers that must not allocate device memory, e.g. code running inside a memory pool
  * it does not own, under a framework allocator that forbids raw cudaMalloc, or in a latency-critical section

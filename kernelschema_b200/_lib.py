@@ -11,7 +11,7 @@ import os
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libb200moe.so")
 
-ABI_VERSION = 1
+ABI_VERSION = 2
 SF_ROW_MAJOR, SF_TILED = 0, 1
 
 
@@ -29,7 +29,8 @@ class Args(C.Structure):
                 ("gemm1_beta", C.c_void_p), ("gemm1_clamp_limit", C.c_void_p), ("output1_scale_scalar", C.c_void_p),
                 ("output1_scale_gate_scalar", C.c_void_p), ("output2_scale_scalar", C.c_void_p),
                 ("local_expert_offset", C.c_int32), ("direct_rows", C.c_int32), ("output", C.c_void_p),
-                ("output_stride", C.c_int64)]
+                ("output_stride", C.c_int64), ("hidden_states_stride", C.c_int64), ("hidden_states_scale_stride", C.c_int64),
+                ("topk_stride", C.c_int64)]
 
 
 class WorkspaceView(C.Structure):
@@ -57,6 +58,9 @@ SIGNATURES = {
     "b200moe_workspace_bytes": (C.c_int64, [C.POINTER(Config)]),
     "b200moe_workspace": (C.c_int, [C.c_void_p, C.POINTER(WorkspaceView)]),
     "b200moe_route_map": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p]),
+    "b200moe_ep_visits": (C.c_int, [C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
+    "b200moe_ep_pack": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32,
+                                  C.c_int64, C.c_void_p, C.c_void_p]),
     "b200moe_combine": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_void_p, C.c_int64,
                                   C.c_void_p]),
     "b200moe_route_map_noalloc": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32]

@@ -128,6 +128,13 @@ int check_args(const b200moe_layer* h, const b200moe_args* a) {
        (uintptr_t)a->gemm1_weights_scale | (uintptr_t)a->gemm2_weights_scale) & 15)
     return fail(730, "run: tensors must be 16-byte aligned");
   if (((uintptr_t)a->hidden_states_scale) & 3) return fail(731, "run: hidden_states_scale must be 4-byte aligned");
+  if (a->hidden_states_stride < 0 || a->hidden_states_stride % 16 || (a->hidden_states_stride && a->hidden_states_stride < h->cfg.hidden / 2))
+    return fail(735, "run: hidden_states_stride must be 0 or a multiple of 16 >= hidden/2 bytes");
+  if (a->hidden_states_scale_stride < 0 || a->hidden_states_scale_stride % 4 ||
+      (a->hidden_states_scale_stride && a->hidden_states_scale_stride < h->cfg.hidden / 16) ||
+      (a->hidden_states_scale_stride && a->hidden_states_scale_layout != 2))
+    return fail(736, "run: hidden_states_scale_stride must be 0 or a multiple of 4 >= hidden/16 bytes (row-major scales only)");
+  if (a->topk_stride < 0 || (a->topk_stride && a->topk_stride < h->cfg.top_k)) return fail(737, "run: topk_stride must be 0 or >= top_k");
   if (a->direct_rows && (h->cfg.top_k != 1 || h->cfg.num_shared_experts != 0))
     return fail(733, "run: direct_rows needs top_k == 1 and no shared experts");
   if (a->direct_rows && (((uintptr_t)a->output & 31) || a->output_stride % 16))
@@ -142,12 +149,12 @@ int run_impl(b200moe_layer* h, const b200moe_args* a, cudaStream_t st, cudaEvent
   int rc;
   auto mark = [&](int i) { if (ev) cudaEventRecord(ev[i], st); };
   mark(0);
-  rc = launch_route_map(a->topk_ids, a->topk_weights, T, c.top_k, c.num_shared_experts, c.num_experts, a->local_expert_offset,
-                        h->rm, st);
+  rc = launch_route_map(a->topk_ids, a->topk_weights, a->topk_stride, T, c.top_k, c.num_shared_experts, c.num_experts,
+                        a->local_expert_offset, h->rm, st);
   if (rc) return cuda_fail(rc, "route map");
   mark(1);
-  rc = launch_gather_rows(a->hidden_states, a->hidden_states_scale, a->hidden_states_scale_layout == 1, h->rm.tok_of_row,
-                          h->rm.tile_rows, h->rm.totals, c.hidden, h->row_capacity, h->a_q, h->a_sf, st);
+  rc = launch_gather_rows(a->hidden_states, a->hidden_states_scale, a->hidden_states_scale_layout == 1, a->hidden_states_stride,
+                          a->hidden_states_scale_stride, h->rm.tok_of_row, h->rm.tile_rows, h->rm.totals, c.hidden, h->row_capacity, h->a_q, h->a_sf, st);
   if (rc) return cuda_fail(rc, "permute");
   mark(2);
   if (h->b1_ptr != a->gemm1_weights || h->s1_ptr != a->gemm1_weights_scale) {
@@ -448,9 +455,30 @@ int b200moe_route_map(b200moe_handle h, const int32_t* ids, const float* weights
   if (!h) return fail(720, "route_map: null handle");
   if (T < 0 || T > h->cfg.max_tokens) return fail(722, "route_map: num_tokens=%d outside 0..max_tokens=%d", T, h->cfg.max_tokens);
   if (T && h->cfg.top_k > 0 && !ids) return fail(723, "route_map: topk_ids is null");
-  return cuda_fail(launch_route_map(ids, weights, T, h->cfg.top_k, h->cfg.num_shared_experts, h->cfg.num_experts, offset, h->rm,
+  return cuda_fail(launch_route_map(ids, weights, 0, T, h->cfg.top_k, h->cfg.num_shared_experts, h->cfg.num_experts, offset, h->rm,
                                     (cudaStream_t)stream),
                    "route map");
+}
+
+int b200moe_ep_visits(const int32_t* ids, int64_t T, int32_t top_k, int32_t experts_per_rank, int32_t world, int32_t* rank_slots,
+                      void* stream) {
+  if (T < 0 || top_k <= 0 || experts_per_rank <= 0 || world <= 0) return fail(790, "ep_visits: bad sizes");
+  if (T && (!ids || !rank_slots)) return fail(791, "ep_visits: null pointer");
+  return cuda_fail(launch_ep_visits(ids, T, top_k, experts_per_rank, world, rank_slots, (cudaStream_t)stream), "ep_visits");
+}
+
+int b200moe_ep_pack(b200moe_handle plan, const void* hidden_states, const void* hidden_states_scale, const int32_t* ids,
+                    const float* weights, int32_t hidden, int32_t top_k, int32_t experts_per_rank, int64_t row_bytes, void* out,
+                    void* stream) {
+  if (!plan) return fail(792, "ep_pack: null plan handle");
+  if (hidden <= 0 || hidden % 64 || top_k <= 0 || row_bytes % 16 || row_bytes < hidden / 2 + hidden / 16 + 8 * top_k)
+    return fail(793, "ep_pack: row_bytes must be a multiple of 16 and hold payload, scales, ids and weights");
+  if (!hidden_states || !hidden_states_scale || !ids || !weights || !out) return fail(794, "ep_pack: null pointer");
+  if (((uintptr_t)hidden_states | (uintptr_t)out) & 15) return fail(795, "ep_pack: payload and out must be 16-byte aligned");
+  return cuda_fail(launch_ep_pack(hidden_states, hidden_states_scale, ids, weights, plan->rm.tok_of_row, plan->rm.tile_expert,
+                                  plan->rm.tile_rows, plan->rm.totals, hidden, top_k, experts_per_rank, plan->cfg.num_experts, row_bytes,
+                                  plan->row_capacity, out, (cudaStream_t)stream),
+                   "ep_pack");
 }
 
 int b200moe_combine(const void* rows, const int32_t* row_of, const float* weight_of_row, int64_t T, int32_t slots, int32_t hidden,

@@ -10,7 +10,8 @@
 namespace b200 {
 
 __global__ void __launch_bounds__(256) k_gather_rows(const uint8_t* __restrict__ hid_q, const uint8_t* __restrict__ hid_sf,
-                                                     int hid_sf_tiled, const int32_t* __restrict__ tok_of_row,
+                                                     int hid_sf_tiled, int64_t q_stride, int64_t sf_stride,
+                                                     const int32_t* __restrict__ tok_of_row,
                                                      const int32_t* __restrict__ tile_rows,
                                                      const int32_t* __restrict__ totals, int H, uint8_t* __restrict__ a_q,
                                                      uint8_t* __restrict__ a_sf) {
@@ -29,7 +30,7 @@ __global__ void __launch_bounds__(256) k_gather_rows(const uint8_t* __restrict__
       for (int w = lane; w < words_per_row; w += 32) sf_dst[(size_t)w * 128] = 0u;
       continue;
     }
-    const uint4* src = reinterpret_cast<const uint4*>(hid_q + (size_t)tok * (H >> 1));
+    const uint4* src = reinterpret_cast<const uint4*>(hid_q + (size_t)tok * q_stride);
     uint4* dst = reinterpret_cast<uint4*>(a_q + (size_t)r * (H >> 1));
     for (int v = lane; v < vec_per_row; v += 32) dst[v] = __ldg(src + v);
     if (hid_sf_tiled) {
@@ -37,20 +38,92 @@ __global__ void __launch_bounds__(256) k_gather_rows(const uint8_t* __restrict__
                                                                  (size_t)(tok & 31) * 16 + (size_t)((tok >> 5) & 3) * 4);
       for (int w = lane; w < words_per_row; w += 32) sf_dst[(size_t)w * 128] = __ldg(sf_src + (size_t)w * 128);
     } else {
-      const uint32_t* sf_src = reinterpret_cast<const uint32_t*>(hid_sf + (size_t)tok * (H >> 4));
+      const uint32_t* sf_src = reinterpret_cast<const uint32_t*>(hid_sf + (size_t)tok * sf_stride);
       for (int w = lane; w < words_per_row; w += 32) sf_dst[(size_t)w * 128] = __ldg(sf_src + w);
     }
   }
 }
 
-int launch_gather_rows(const void* hid_q, const void* hid_sf, int hid_sf_tiled, const int32_t* tok_of_row, const int32_t* tile_rows,
-                       const int32_t* totals,
+int launch_gather_rows(const void* hid_q, const void* hid_sf, int hid_sf_tiled, int64_t q_stride, int64_t sf_stride,
+                       const int32_t* tok_of_row, const int32_t* tile_rows, const int32_t* totals,
                        int H, int64_t row_capacity, void* a_q, void* a_sf, cudaStream_t st) {
   if (row_capacity == 0) return 0;
   int64_t blocks = (row_capacity + 7) / 8;
   if (blocks > 148 * 8) blocks = 148 * 8;
-  k_gather_rows<<<(unsigned)blocks, 256, 0, st>>>((const uint8_t*)hid_q, (const uint8_t*)hid_sf, hid_sf_tiled, tok_of_row, tile_rows,
-                                                 totals, H, (uint8_t*)a_q, (uint8_t*)a_sf);
+  k_gather_rows<<<(unsigned)blocks, 256, 0, st>>>((const uint8_t*)hid_q, (const uint8_t*)hid_sf, hid_sf_tiled, q_stride > 0 ? q_stride : H / 2,
+                                                 sf_stride > 0 ? sf_stride : H / 16, tok_of_row, tile_rows, totals, H, (uint8_t*)a_q, (uint8_t*)a_sf);
+  return (int)cudaGetLastError();
+}
+
+// ----------------------------------------------------------------------------- expert-parallel dispatch packing
+// One message row per (token, destination rank) pair: [payload H/2 | scale bytes H/16 | K local expert ids (int32) |
+// K routing weights (fp32)], padded to a multiple of 16 bytes. The pairs come from a route map whose "experts" are
+// the destination ranks (segments are 128-row aligned; rows past a tile's count are padding and get ids = -1, so the
+// receiver ignores them). One warp per row.
+__global__ void __launch_bounds__(256) k_ep_pack(const uint8_t* __restrict__ hid_q, const uint8_t* __restrict__ hid_sf,
+                                                 const int32_t* __restrict__ ids, const float* __restrict__ weights,
+                                                 const int32_t* __restrict__ tok_of_row, const int32_t* __restrict__ tile_expert,
+                                                 const int32_t* __restrict__ tile_rows, const int32_t* __restrict__ totals, int H,
+                                                 int K, int experts_per_rank, int world, int64_t row_bytes, uint8_t* __restrict__ out) {
+  const int rows = totals[1];
+  const int lane = threadIdx.x & 31;
+  const int warps = (gridDim.x * blockDim.x) >> 5;
+  const int q_vecs = H >> 5, sf_words = H >> 6;
+  for (int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < rows; r += warps) {
+    const int dest = tile_expert[r >> 7];
+    if (dest >= world) break;  // rows of the plan's shared-expert slot follow the last rank's segment: not messages
+    uint8_t* dst = out + (size_t)r * row_bytes;
+    int32_t* id_dst = reinterpret_cast<int32_t*>(dst + (H >> 1) + (H >> 4));
+    float* w_dst = reinterpret_cast<float*>(id_dst + K);
+    const bool live = (r & 127) < tile_rows[r >> 7];
+    if (!live) {
+      if (lane < K) id_dst[lane] = -1;
+      continue;
+    }
+    const int tok = tok_of_row[r];
+    const uint4* src = reinterpret_cast<const uint4*>(hid_q + (size_t)tok * (H >> 1));
+    for (int v = lane; v < q_vecs; v += 32) reinterpret_cast<uint4*>(dst)[v] = __ldg(src + v);
+    const uint32_t* sf_src = reinterpret_cast<const uint32_t*>(hid_sf + (size_t)tok * (H >> 4));
+    for (int w = lane; w < sf_words; w += 32) reinterpret_cast<uint32_t*>(dst + (H >> 1))[w] = __ldg(sf_src + w);
+    if (lane < K) {
+      const int g = ids[(size_t)tok * K + lane];
+      const bool here = g >= 0 && g / experts_per_rank == dest;
+      id_dst[lane] = here ? g - dest * experts_per_rank : -1;
+      w_dst[lane] = weights[(size_t)tok * K + lane];
+    }
+  }
+}
+
+// rank_slots[t, r] = r when token t has at least one route to an expert of rank r, else -1.
+__global__ void k_ep_visits(const int32_t* __restrict__ ids, int64_t T, int K, int experts_per_rank, int world,
+                            int32_t* __restrict__ rank_slots) {
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= T * world) return;
+  const int64_t t = idx / world;
+  const int r = (int)(idx - t * world);
+  bool hit = false;
+  for (int k = 0; k < K; ++k) {
+    const int g = ids[t * K + k];
+    hit |= (g >= 0 && g / experts_per_rank == r);
+  }
+  rank_slots[idx] = hit ? r : -1;
+}
+
+int launch_ep_visits(const int32_t* ids, int64_t T, int K, int experts_per_rank, int world, int32_t* rank_slots, cudaStream_t st) {
+  const int64_t n = T * world;
+  if (n == 0) return 0;
+  k_ep_visits<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(ids, T, K, experts_per_rank, world, rank_slots);
+  return (int)cudaGetLastError();
+}
+
+int launch_ep_pack(const void* hid_q, const void* hid_sf, const int32_t* ids, const float* weights, const int32_t* tok_of_row,
+                   const int32_t* tile_expert, const int32_t* tile_rows, const int32_t* totals, int H, int K, int experts_per_rank,
+                   int world, int64_t row_bytes, int64_t row_capacity, void* out, cudaStream_t st) {
+  if (row_capacity == 0) return 0;
+  int64_t blocks = (row_capacity + 7) / 8;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  k_ep_pack<<<(unsigned)blocks, 256, 0, st>>>((const uint8_t*)hid_q, (const uint8_t*)hid_sf, ids, weights, tok_of_row, tile_expert,
+                                             tile_rows, totals, H, K, experts_per_rank, world, row_bytes, (uint8_t*)out);
   return (int)cudaGetLastError();
 }
 

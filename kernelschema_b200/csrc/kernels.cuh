@@ -62,12 +62,16 @@ int launch_route_topk(const float* logits, const float* bias, int64_t T, int E, 
                       cudaStream_t st);
 int launch_router_logits(const void* x, const void* w, int64_t T, int H, int E, float* logits, cudaStream_t st);
 int launch_router_logits_tc(const void* x, const void* w, int64_t T, int H, int E, float* logits, int32_t* status, cudaStream_t st);
-int launch_route_map(const int32_t* ids, const float* scores, int64_t T, int K, int S, int E, int expert_offset, RouteMapBuffers b,
-                     cudaStream_t st);
+int launch_route_map(const int32_t* ids, const float* scores, int64_t id_stride, int64_t T, int K, int S, int E, int expert_offset,
+                     RouteMapBuffers b, cudaStream_t st);
 int launch_route_map_static(const int32_t* ids, const float* scores, int64_t T, int K, int S, int E, int expert_offset,
                             RouteMapBuffers b, cudaStream_t st);
-int launch_gather_rows(const void* hid_q, const void* hid_sf, int hid_sf_tiled, const int32_t* tok_of_row, const int32_t* tile_rows,
-                       const int32_t* totals,
+int launch_ep_visits(const int32_t* ids, int64_t T, int K, int experts_per_rank, int world, int32_t* rank_slots, cudaStream_t st);
+int launch_ep_pack(const void* hid_q, const void* hid_sf, const int32_t* ids, const float* weights, const int32_t* tok_of_row,
+                   const int32_t* tile_expert, const int32_t* tile_rows, const int32_t* totals, int H, int K, int experts_per_rank,
+                   int world, int64_t row_bytes, int64_t row_capacity, void* out, cudaStream_t st);
+int launch_gather_rows(const void* hid_q, const void* hid_sf, int hid_sf_tiled, int64_t q_stride, int64_t sf_stride,
+                       const int32_t* tok_of_row, const int32_t* tile_rows, const int32_t* totals,
                        int H, int64_t row_capacity, void* a_q, void* a_sf, cudaStream_t st);
 int launch_finalize(const void* rout, const int32_t* row_of, const float* weight_of_row, int64_t T, int KK, int H, void* out,
                     int64_t out_stride, cudaStream_t st);

@@ -17,6 +17,7 @@ constexpr int kRouteWarps = 8;
 
 struct RouteView {
   const int32_t* ids;
+  int64_t id_stride;  // elements between the id rows of consecutive tokens (>= K)
   int64_t T;
   int K;            // routed slots per token
   int S;            // shared experts: extra always-selected slots
@@ -30,7 +31,7 @@ DEV int route_expert(const RouteView& r, int64_t f, int64_t total) {
   const int64_t t = f / kk;
   const int k = (int)(f - t * kk);
   if (k >= r.K) return r.E + (k - r.K);
-  const int e = r.ids[t * r.K + k] - r.expert_offset;
+  const int e = r.ids[t * r.id_stride + k] - r.expert_offset;
   return (e >= 0 && e < r.E) ? e : -1;
 }
 
@@ -194,7 +195,7 @@ __global__ void __launch_bounds__(256) k_route_scatter(RouteView r, const float*
         const int64_t t = f / kk;
         const int k = (int)(f - t * kk);
         tok_of_row[pos] = (int32_t)t;
-        weight_of_row[pos] = (k < r.K) ? (scores ? scores[t * r.K + k] : 1.0f) : 1.0f;
+        weight_of_row[pos] = (k < r.K) ? (scores ? scores[t * r.id_stride + k] : 1.0f) : 1.0f;
       }
     }
   }
@@ -290,18 +291,18 @@ __global__ void __launch_bounds__(256) k_route_single(RouteView r, const float* 
         const int64_t t = f / kk;
         const int k = (int)(f - t * kk);
         b.tok_of_row[pos] = (int32_t)t;
-        b.weight_of_row[pos] = (k < r.K) ? (scores ? scores[t * r.K + k] : 1.0f) : 1.0f;
+        b.weight_of_row[pos] = (k < r.K) ? (scores ? scores[t * r.id_stride + k] : 1.0f) : 1.0f;
       }
     }
   }
 }
 
-int launch_route_map(const int32_t* ids, const float* scores, int64_t T, int K, int S, int E, int expert_offset, RouteMapBuffers b,
-                     cudaStream_t st) {
+int launch_route_map(const int32_t* ids, const float* scores, int64_t id_stride, int64_t T, int K, int S, int E, int expert_offset,
+                     RouteMapBuffers b, cudaStream_t st) {
   const int etot = E + S;
   const int64_t total = T * (K + S);
   const int nblk = (int)((total + kRouteChunk - 1) / kRouteChunk);
-  RouteView r{ids, T, K, S, E, expert_offset};
+  RouteView r{ids, id_stride > 0 ? id_stride : K, T, K, S, E, expert_offset};
   if (nblk == 1) {
     k_route_single<<<1, 256, sizeof(int) * kRouteWarps * (size_t)etot, st>>>(r, scores, etot, b);
     return (int)cudaGetLastError();
@@ -346,7 +347,7 @@ int launch_route_map_static(const int32_t* ids, const float* scores, int64_t T, 
     g_route_scratch_ptr[dev] = (int32_t*)p;
   }
   b.block_hist = g_route_scratch_ptr[dev];
-  return launch_route_map(ids, scores, T, K, S, E, expert_offset, b, st);
+  return launch_route_map(ids, scores, 0, T, K, S, E, expert_offset, b, st);
 }
 
 }  // namespace b200

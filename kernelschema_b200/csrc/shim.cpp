@@ -38,7 +38,8 @@ PYBIND11_MODULE(_b200moe_shim, m) {
   m.def("run", [](uintptr_t h, int num_tokens, uintptr_t ids, uintptr_t weights, uintptr_t hidden_states, uintptr_t hidden_scale,
                   int scale_layout, int activation_type, uintptr_t w1, uintptr_t s1, uintptr_t w2, uintptr_t s2, uintptr_t alpha,
                   uintptr_t beta, uintptr_t limit, uintptr_t scale_up, uintptr_t scale_gate, uintptr_t scale_out, int expert_offset,
-                  int direct_rows, uintptr_t output, int64_t output_stride, uintptr_t stream) {
+                  int direct_rows, uintptr_t output, int64_t output_stride, uintptr_t stream, int64_t hidden_states_stride,
+                  int64_t hidden_states_scale_stride, int64_t topk_stride) {
     b200moe_args a{};
     a.struct_size = (int32_t)sizeof(a);
     a.num_tokens = num_tokens;
@@ -62,8 +63,16 @@ PYBIND11_MODULE(_b200moe_shim, m) {
     a.direct_rows = direct_rows;
     a.output = ptr<void>(output);
     a.output_stride = output_stride;
+    a.hidden_states_stride = hidden_states_stride;
+    a.hidden_states_scale_stride = hidden_states_scale_stride;
+    a.topk_stride = topk_stride;
     check(b200moe_run(ptr<b200moe_layer>(h), &a, ptr<void>(stream)), "b200moe_run");
-  });
+  }, py::arg("handle"), py::arg("num_tokens"), py::arg("ids"), py::arg("weights"), py::arg("hidden_states"), py::arg("hidden_scale"),
+     py::arg("scale_layout"), py::arg("activation_type"), py::arg("w1"), py::arg("s1"), py::arg("w2"), py::arg("s2"), py::arg("alpha"),
+     py::arg("beta"), py::arg("limit"), py::arg("scale_up"), py::arg("scale_gate"), py::arg("scale_out"), py::arg("expert_offset"),
+     py::arg("direct_rows"), py::arg("output"), py::arg("output_stride"), py::arg("stream"), py::arg("hidden_states_stride") = 0,
+     py::arg("hidden_states_scale_stride") = 0, py::arg("topk_stride") = 0);
+  m.def("handle_null", []() { return (uintptr_t)0; });
   m.def("status", [](uintptr_t h, uintptr_t stream) {
     int32_t code = 0;
     check(b200moe_status(ptr<b200moe_layer>(h), ptr<void>(stream), &code), "b200moe_status");

@@ -1,14 +1,21 @@
 """Expert-parallel wrapper: experts sharded contiguously over the ranks of one box, tokens data-parallel.
 
 Per step and rank:
-  1. plan: a token goes ONCE to every rank that owns at least one of its experts (not once per route);
-  2. dispatch all-to-all of the NVFP4 rows (payload, scale bytes) with the token's local expert ids and weights;
-  3. the receiving rank runs the ordinary layer on the tokens it got (top-k routing restricted to its experts,
-     ids of foreign experts = -1), i.e. it already applies the routing weights and sums over its own experts:
-     one bf16 partial row per (token, rank);
-  4. combine all-to-all of those partial rows back to the source, received in place;
-  5. the source adds the partial rows (and the shared experts' row, computed locally on a side stream under the
+  1. plan: a token goes ONCE to every rank that owns at least one of its experts (not once per route). The
+     (token, rank) pairs are ordered by rank, then token; every rank's segment is padded to a multiple of 128 rows;
+  2. pack: one message row per pair, `row_bytes(H, K)` bytes: NVFP4 payload | scale bytes | the token's K expert ids
+     relative to the destination rank (-1 for experts that live elsewhere, and for padding rows) | its K weights;
+  3. ONE dispatch all-to-all of the message rows;
+  4. the receiving rank runs the ordinary layer directly on the message buffer (row-strided views of its columns:
+     no unpacking copy), i.e. it already applies the routing weights and sums over its own experts: one bf16
+     partial row per (token, rank);
+  5. combine all-to-all of those partial rows back to the source, received in place;
+  6. the source adds the partial rows (and the shared experts' row, computed locally on a side stream under the
      exchange) in rank order with `b200moe_combine` and rounds once to bf16.
+On CUDA steps 1-2 are three launches of the library (`b200moe_ep_visits`, the route map of a "plan" layer whose
+experts are the ranks, `b200moe_ep_pack`); `plan_messages_torch` is the same plan in torch ops for the CPU tests and as
+the checker of the kernels. One host synchronisation per step: the segment sizes for the uneven all-to-all.
+
 A token that visits r ranks costs r rows in each direction instead of top_k: 5.25 instead of 8 on average at
 8 ranks with uniform top-8 routing, at most 2 at 2 ranks. The partial rows are rounded to bf16 before they travel, so
 the result differs from the single-GPU layer by one extra bf16 rounding per visited rank (well inside the
@@ -20,6 +27,21 @@ from __future__ import annotations
 
 import torch
 import torch.distributed as dist
+
+SEGMENT_ROWS = 128
+
+
+def row_bytes(hidden: int, top_k: int) -> int:
+    """Bytes of one dispatch message row (multiple of 16)."""
+    return (hidden // 2 + hidden // 16 + 8 * top_k + 15) // 16 * 16
+
+
+def message_views(msg: torch.Tensor, hidden: int, top_k: int):
+    """Column views (no copies) of a message buffer uint8 [n, row_bytes]: payload, scales, local ids, weights."""
+    q, sf = hidden // 2, hidden // 16
+    words = msg.view(torch.int32)
+    c0 = (q + sf) // 4
+    return msg[:, :q], msg[:, q:q + sf], words[:, c0:c0 + top_k], words[:, c0 + top_k:c0 + 2 * top_k].view(torch.float32)
 
 
 def build_dispatch(ids: torch.Tensor, experts_per_rank: int, world: int):
@@ -46,6 +68,35 @@ def build_dispatch(ids: torch.Tensor, experts_per_rank: int, world: int):
     return dict(tok=tok, dest=dest, send_counts=send_counts, local_ids=local_ids, pos_of_pair=pos.t().contiguous())
 
 
+def plan_messages_torch(ids, weights, hq, hs, experts_per_rank: int, world: int, shared_slot: bool = False):
+    """The dispatch plan and message buffer of one rank in torch ops (any device). Returns (msg uint8 [n_send,
+    row_bytes], seg_rows list[int] per destination rank, row_of int32 [T, world (+1)]); with ``shared_slot`` the last
+    column of row_of points at row n_send + t, where the caller puts the shared experts' row of token t."""
+    t, k = ids.shape
+    h = hq.shape[1] * 2
+    plan = build_dispatch(ids, experts_per_rank, world)
+    counts = plan["send_counts"]
+    padded = (counts + SEGMENT_ROWS - 1) // SEGMENT_ROWS * SEGMENT_ROWS
+    seg_start = torch.cumsum(padded, 0) - padded
+    first_pair = torch.cumsum(counts, 0) - counts
+    dest, tok = plan["dest"], plan["tok"]
+    position = seg_start[dest] + torch.arange(tok.numel(), device=ids.device) - first_pair[dest]
+    seg_rows = [int(v) for v in padded.tolist()]
+    n_send = sum(seg_rows)
+    msg = torch.zeros((n_send, row_bytes(h, k)), dtype=torch.uint8, device=ids.device)
+    m_q, m_sf, m_ids, m_w = message_views(msg, h, k)
+    m_ids.fill_(-1)
+    m_q[position] = hq.view(torch.uint8)[tok]
+    m_sf[position] = hs.view(torch.uint8)[tok]
+    m_ids[position] = plan["local_ids"]
+    m_w[position] = weights[tok].to(torch.float32)
+    row_of = torch.full((t, world + int(shared_slot)), -1, dtype=torch.int32, device=ids.device)
+    row_of[tok, dest] = position.to(torch.int32)
+    if shared_slot:
+        row_of[:, world] = n_send + torch.arange(t, dtype=torch.int32, device=ids.device)
+    return msg, seg_rows, row_of
+
+
 def exchange(send: torch.Tensor, send_counts: list[int], recv_counts: list[int], group=None) -> torch.Tensor:
     """Uneven all-to-all of rows: send is [sum(send_counts), ...] in destination order."""
     out = send.new_empty((sum(recv_counts),) + tuple(send.shape[1:]))
@@ -53,12 +104,39 @@ def exchange(send: torch.Tensor, send_counts: list[int], recv_counts: list[int],
     return out
 
 
+class CudaPlanner:
+    """`plan_messages_torch` in three launches of the library: `b200moe_ep_visits`, the route map of a "plan" layer
+    whose experts are the ranks (plus one shared slot), `b200moe_ep_pack`. Buffers are allocated once."""
+
+    def __init__(self, hidden, top_k, experts_per_rank, world, max_tokens, shared_slot, device):
+        from .ops import MoELayer
+        self.h, self.k, self.e_local, self.world = hidden, top_k, experts_per_rank, world
+        # the plan layer's GEMM operands are never used, so it gets the smallest legal sizes
+        self.layer = MoELayer(256, 256, world, world, max_tokens, num_shared_experts=1 if shared_slot else 0)
+        self.ws = self.layer.workspace()
+        self.slots = torch.empty((max_tokens, world), dtype=torch.int32, device=device)
+        self.msg = torch.empty((self.ws["row_capacity"], row_bytes(hidden, top_k)), dtype=torch.uint8, device=device)
+
+    def plan(self, ids, weights, hq, hs):
+        """Returns (msg buffer, segment rows per rank as a device tensor, row_of [T, world (+1)], row weights (all 1) for
+        `b200moe_combine`); the first sum(segment rows) rows of msg are the messages."""
+        from .ops import ep_pack, ep_visits
+        t = ids.shape[0]
+        slots = self.slots[:t]
+        ep_visits(ids, self.e_local, self.world, slots)
+        self.layer.route_map(slots, None)
+        ep_pack(self.layer, hq, hs, ids, weights, self.e_local, self.msg)
+        seg_start = self.ws["seg_start"]
+        return self.msg, seg_start[1:self.world + 1] - seg_start[:self.world], self.ws["row_of"][:t], self.ws["weight_of_row"]
+
+
 class ExpertParallelMoE:
     """Layer instance on one rank. `expert_rows`, `shared_rows` and `combine_rows` are the compute hooks; by default
-    they run libb200moe on the current CUDA device."""
+    they run libb200moe on the current CUDA device. `planner` is "cuda" (library kernels; default on a GPU) or
+    "torch" (`plan_messages_torch`; the only choice on CPU)."""
 
     def __init__(self, hidden, intermediate, num_experts, top_k, tokens_per_rank, num_shared_experts=0, group=None,
-                 expert_rows=None, combine_rows=None, shared_rows=None, recv_capacity=None):
+                 expert_rows=None, combine_rows=None, shared_rows=None, recv_capacity=None, planner=None):
         self.group = group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
@@ -67,15 +145,18 @@ class ExpertParallelMoE:
         self.h, self.i, self.k, self.s = hidden, intermediate, top_k, num_shared_experts
         self.e_local = num_experts // self.world
         self.t = tokens_per_rank
-        self.recv_capacity = recv_capacity or self.world * tokens_per_rank      # every token of every rank, at worst
+        seg = lambda n: (n + SEGMENT_ROWS - 1) // SEGMENT_ROWS * SEGMENT_ROWS
+        # every token of every rank, at worst (each source's segment padded to 128 rows)
+        self.recv_capacity = recv_capacity or self.world * seg(tokens_per_rank)
         self._expert_rows = expert_rows or self._cuda_expert_rows
         self._combine_rows = combine_rows or self._cuda_combine_rows
         self._shared_rows = shared_rows or self._cuda_shared_rows
-        self._routed = self._shared = None
+        self.planner = planner
+        self._routed = self._shared = self._plan = None
         self.profile = False
-        # quantise/route launches are the caller's; here: (route map 3 + permute + FC1 + FC2 + combine) for the received
-        # tokens, the same for the shared experts, and the final combine
-        self.launches_per_step = 7 * (2 if num_shared_experts else 1) + 1
+        # quantise/route launches are the caller's; here: plan (visits + route map + pack), then (route map + permute +
+        # FC1 + FC2 + combine) for the received tokens, the same for the shared experts, and the final combine
+        self.launches_per_step = 3 + 5 * (2 if num_shared_experts else 1) + 1
 
     # ------------------------------------------------------------------ CUDA hooks
     def _cuda_expert_rows(self, rows_q, rows_sf, local_ids, weights, w1q, w1s, w2q, w2s, out_rows, kw):
@@ -108,7 +189,7 @@ class ExpertParallelMoE:
 
     def status(self) -> int:
         code = 0
-        for layer in (self._routed, self._shared):
+        for layer in (self._routed, self._shared, self._plan.layer if self._plan else None):
             if layer is not None:
                 code = code or layer.status()
         return code
@@ -129,15 +210,23 @@ class ExpertParallelMoE:
                 marks.append((name, ev))
 
         mark("start")
-        plan = build_dispatch(ids, self.e_local, self.world)
-        send_counts_t = plan["send_counts"]
-        recv_counts_t = torch.empty_like(send_counts_t)
-        dist.all_to_all_single(recv_counts_t, send_counts_t, group=self.group)
-        send_counts = send_counts_t.tolist()      # host copies: split sizes of the uneven all-to-all
-        recv_counts = recv_counts_t.tolist()
+        planner = self.planner or ("cuda" if dev.type == "cuda" else "torch")
+        if planner == "cuda":
+            if self._plan is None or self._plan.layer.cfg.max_tokens < t:
+                self._plan = CudaPlanner(self.h, self.k, self.e_local, self.world, max(t, self.t), bool(self.s), dev)
+            msg, seg_rows_t, row_of, w_rows = self._plan.plan(ids, weights, hq, hs)
+            seg_rows_t = seg_rows_t.to(torch.int64)
+        else:
+            msg, seg_rows, row_of = plan_messages_torch(ids, weights, hq, hs, self.e_local, self.world, bool(self.s))
+            seg_rows_t = torch.tensor(seg_rows, dtype=torch.int64, device=dev)
+            w_rows = None
+        recv_rows_t = torch.empty_like(seg_rows_t)
+        dist.all_to_all_single(recv_rows_t, seg_rows_t, group=self.group)
+        sizes = torch.cat([seg_rows_t, recv_rows_t]).tolist()      # the step's one host copy: split sizes
+        send_counts, recv_counts = sizes[:self.world], sizes[self.world:]
         n_send, n_recv = sum(send_counts), sum(recv_counts)
         if n_recv > self.recv_capacity:
-            raise RuntimeError(f"rank {self.rank} received {n_recv} tokens, capacity is {self.recv_capacity}")
+            raise RuntimeError(f"rank {self.rank} received {n_recv} rows, capacity is {self.recv_capacity}")
         mark("plan+counts")
         shared_slot = 1 if self.s else 0
         rows_all = torch.empty((n_send + t * shared_slot, self.h), dtype=torch.bfloat16, device=dev)
@@ -151,26 +240,21 @@ class ExpertParallelMoE:
                     self._shared_rows(hq, hs, w1q, w1s, w2q, w2s, rows_all[n_send:], kw)
             else:
                 self._shared_rows(hq, hs, w1q, w1s, w2q, w2s, rows_all[n_send:], kw)
-        tok = plan["tok"]
-        rows_q = exchange(hq.index_select(0, tok), send_counts, recv_counts, self.group)
-        rows_sf = exchange(hs.index_select(0, tok), send_counts, recv_counts, self.group)
-        ids_recv = exchange(plan["local_ids"], send_counts, recv_counts, self.group)
-        w_recv = exchange(weights.index_select(0, tok), send_counts, recv_counts, self.group)
+        got = exchange(msg[:n_send], send_counts, recv_counts, self.group)
         mark("dispatch")
-        # one partial row per token received: routing-weighted sum over this rank's experts, rounded to bf16
+        # one partial row per row received: routing-weighted sum over this rank's experts, rounded to bf16
         res = torch.empty((n_recv, self.h), dtype=torch.bfloat16, device=dev)
         if n_recv:
+            rows_q, rows_sf, ids_recv, w_recv = message_views(got, self.h, self.k)
             self._expert_rows(rows_q, rows_sf, ids_recv, w_recv, w1q, w1s, w2q, w2s, res, kw)
         mark("experts")
         # partial rows return to their sources (received in place), the shared experts' rows come after them
         dist.all_to_all_single(rows_all[:n_send], res, output_split_sizes=send_counts, input_split_sizes=recv_counts,
                                group=self.group)
         mark("combine_a2a")
-        row_of = torch.full((t, self.world + shared_slot), -1, dtype=torch.int32, device=dev)
-        row_of[:, :self.world] = plan["pos_of_pair"]
-        w_rows = torch.ones(rows_all.shape[0], dtype=torch.float32, device=dev)
+        if w_rows is None:
+            w_rows = torch.ones(rows_all.shape[0], dtype=torch.float32, device=dev)
         if self.s:
-            row_of[:, self.world] = n_send + torch.arange(t, dtype=torch.int32, device=dev)
             if side is not None:
                 torch.cuda.current_stream(dev).wait_stream(side)
             mark("shared")

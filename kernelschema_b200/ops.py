@@ -123,6 +123,25 @@ def combine(rows: torch.Tensor, row_of: torch.Tensor, weight_of_row: torch.Tenso
     return out
 
 
+def ep_visits(ids: torch.Tensor, experts_per_rank: int, world: int, out: torch.Tensor | None = None) -> torch.Tensor:
+    """int32 [T, world]: column r holds r where the token has a route to an expert of rank r, else -1."""
+    _need_cuda(ids)
+    t, k = ids.shape
+    if out is None:
+        out = torch.empty((t, world), dtype=torch.int32, device=ids.device)
+    _lib.check(_lib.load().b200moe_ep_visits(_ptr(ids), t, k, experts_per_rank, world, _ptr(out), _stream()), "b200moe_ep_visits")
+    return out
+
+
+def ep_pack(plan: "MoELayer", hidden_states, hidden_states_scale, ids, weights, experts_per_rank: int, out: torch.Tensor):
+    """Fill the dispatch message rows (uint8 [rows, row_bytes]) of the (token, rank) pairs of ``plan``'s route map."""
+    _need_cuda(hidden_states, hidden_states_scale, ids, weights, out)
+    h = hidden_states.shape[1] * 2
+    _lib.check(_lib.load().b200moe_ep_pack(plan._h, _ptr(hidden_states), _ptr(hidden_states_scale), _ptr(ids), _ptr(weights), h,
+                                           ids.shape[1], experts_per_rank, out.shape[1], _ptr(out), _stream()), "b200moe_ep_pack")
+    return out
+
+
 class MoELayer:
     """One layer instance: owns the library workspace for a geometry (b200moe_create / b200moe_destroy)."""
 
@@ -168,12 +187,19 @@ class MoELayer:
     def run(self, ids, weights, hidden_states, hidden_states_scale, w1, s1, w2, s2, out, *, alpha=None, beta=None, limit=None,
             scale_up=None, scale_gate=None, scale_out=None, activation_type=3, expert_offset=0, scale_layout=2, direct_rows=False):
         """Asynchronous forward on the current stream; writes ``out`` (bf16 [T, H]) in place. The hot call goes through
-        the pybind11 shim (one positional C++ call, no ctypes struct marshalling)."""
+        the pybind11 shim (one positional C++ call, no ctypes struct marshalling). ids/weights, the payload and row-major
+        scales may be row-strided views (e.g. columns of a packed message buffer); their strides are passed on."""
         _need_cuda(hidden_states, hidden_states_scale, w1, s1, w2, s2, out)
         p = lambda t: 0 if t is None else t.data_ptr()
+        if ids is not None and weights is not None and ids.stride(0) != weights.stride(0):
+            raise ValueError("topk_ids and topk_weights must have the same row stride")
         _shim().run(self._h.value, hidden_states.shape[0], p(ids), p(weights), p(hidden_states), p(hidden_states_scale),
                     scale_layout, activation_type, p(w1), p(s1), p(w2), p(s2), p(alpha), p(beta), p(limit), p(scale_up),
-                    p(scale_gate), p(scale_out), expert_offset, int(direct_rows), p(out), out.stride(0), _stream())
+                    p(scale_gate), p(scale_out), expert_offset, int(direct_rows), p(out), out.stride(0), _stream(),
+                    hidden_states.stride(0) * hidden_states.element_size() if hidden_states.dim() == 2 else 0,
+                    hidden_states_scale.stride(0) * hidden_states_scale.element_size()
+                    if (scale_layout == 2 and hidden_states_scale.dim() == 2) else 0,
+                    0 if ids is None else ids.stride(0))
         return out
 
     def run_profiled(self, ids, weights, hidden_states, hidden_states_scale, w1, s1, w2, s2, out, **kw):

@@ -34,7 +34,7 @@ def test_header_and_binding_agree(lib):
 def test_struct_sizes_match_header(lib):
     from kernelschema_b200 import _lib
     assert C.sizeof(_lib.Config) == 16 * 4
-    assert C.sizeof(_lib.Args) == 8 + 8 * 4 + 8 + 8 * 10 + 8 + 16
+    assert C.sizeof(_lib.Args) == 8 + 8 * 4 + 8 + 8 * 10 + 8 + 16 + 24
     assert C.sizeof(_lib.WorkspaceView) == 14 * 8 + 16 + 24
 
 

@@ -109,3 +109,24 @@ def test_build_dispatch_plan():
     assert plan["tok"].tolist() == [0, 2, 3, 0, 1]
     assert plan["local_ids"].tolist() == [[-1, 0], [1, 1], [-1, 0], [1, -1], [-1, 0]]
     assert plan["pos_of_pair"].tolist() == [[0, 3], [-1, 4], [1, -1], [2, -1]]
+
+
+def test_plan_messages_torch_layout():
+    from kernelschema_b200.ep import message_views, plan_messages_torch, row_bytes
+    h, k = 256, 2
+    ids = torch.tensor([[3, 0], [-1, 2], [1, 1], [9, 0]], dtype=torch.int32)
+    w = torch.arange(8, dtype=torch.float32).reshape(4, 2)
+    hq = torch.arange(4 * h // 2, dtype=torch.int64).reshape(4, h // 2).to(torch.uint8)
+    hs = (torch.arange(4 * h // 16, dtype=torch.int64).reshape(4, h // 16) + 100).to(torch.uint8)
+    msg, seg_rows, row_of = plan_messages_torch(ids, w, hq, hs, experts_per_rank=2, world=2, shared_slot=True)
+    assert row_bytes(h, k) == 160 and msg.shape == (256, 160)
+    assert seg_rows == [128, 128]                      # 3 and 2 pairs, each segment padded to 128 rows
+    assert row_of.tolist() == [[0, 128, 256], [-1, 129, 257], [1, -1, 258], [2, -1, 259]]
+    m_q, m_sf, m_ids, m_w = message_views(msg, h, k)
+    assert torch.equal(m_q[[0, 1, 2, 128, 129]], hq[[0, 2, 3, 0, 1]])
+    assert torch.equal(m_sf[[0, 1, 2, 128, 129]], hs[[0, 2, 3, 0, 1]])
+    assert m_ids[[0, 1, 2, 128, 129]].tolist() == [[-1, 0], [1, 1], [-1, 0], [1, -1], [-1, 0]]
+    assert torch.equal(m_w[[0, 1, 2, 128, 129]], w[[0, 2, 3, 0, 1]])
+    live = torch.zeros(256, dtype=torch.bool)
+    live[[0, 1, 2, 128, 129]] = True
+    assert (m_ids[~live] == -1).all()                  # padding rows carry no routes

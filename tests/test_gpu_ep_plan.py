@@ -1,0 +1,69 @@
+"""The expert-parallel dispatch plan on ONE GPU: the library's three-launch planner against the torch-op plan of
+kernelschema_b200/ep.py, and the layer run on row-strided views of a message buffer against the same run on contiguous
+copies."""
+import numpy as np
+import pytest
+import torch
+
+from helpers import make_moe_case
+
+pytestmark = pytest.mark.gpu
+
+
+def _dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+@pytest.mark.parametrize("t,h,e,k,world,shared", [(96, 512, 8, 4, 2, True), (300, 256, 16, 3, 4, False),
+                                                   (4096, 1024, 64, 8, 8, True), (1, 256, 8, 2, 8, False)])
+def test_cuda_planner_matches_torch_plan(t, h, e, k, world, shared):
+    from kernelschema_b200.ep import CudaPlanner, message_views, plan_messages_torch
+    p = make_moe_case(5, t, h, 256, e, k, routing="zipf", masked=True)
+    ids, w = _dev(p["topk_ids"][0].astype(np.int32)), _dev(p["topk_ids"][1].astype(np.float32))
+    hq, hs = _dev(p["hidden_states"]), _dev(p["hidden_states_scale"])
+    ref_msg, ref_seg, ref_row_of = plan_messages_torch(ids, w, hq, hs, e // world, world, shared)
+    planner = CudaPlanner(h, k, e // world, world, t, shared, ids.device)
+    for _ in range(2):       # buffers are reused between steps
+        msg, seg, row_of, w_rows = planner.plan(ids, w, hq, hs)
+        torch.cuda.synchronize()
+        assert planner.layer.status() == 0
+        assert seg.tolist() == ref_seg
+        assert torch.equal(row_of, ref_row_of)
+        n = sum(ref_seg)
+        got = message_views(msg[:n], h, k)
+        want = message_views(ref_msg, h, k)
+        live = (want[2] >= 0).any(dim=1)
+        # every live pair row is byte-identical; padding rows (and rows of tokens whose routes are all masked: there are
+        # none, such a token visits no rank) only promise ids = -1
+        used_bytes = h // 2 + h // 16 + 8 * k     # the tail that rounds a row up to 16 bytes is never written or read
+        assert torch.equal(msg[:n][live][:, :used_bytes], ref_msg[live][:, :used_bytes])
+        assert torch.equal(got[2], want[2])
+        used = row_of[row_of >= 0].long()
+        assert (w_rows[used] == 1).all()
+
+
+def test_layer_runs_on_strided_message_views():
+    from kernelschema_b200.ep import message_views, plan_messages_torch
+    from kernelschema_b200.ops import MoELayer
+    t, h, i, e, k = 200, 512, 256, 4, 2
+    p = make_moe_case(9, t, h, i, e, k, global_scales=True, masked=True)
+    ids, w = _dev(p["topk_ids"][0].astype(np.int32)), _dev(p["topk_ids"][1].astype(np.float32))
+    hq, hs = _dev(p["hidden_states"]), _dev(p["hidden_states_scale"])
+    msg, seg, _ = plan_messages_torch(ids, w, hq, hs, e, 1)          # one rank owns every expert
+    m_q, m_sf, m_ids, m_w = message_views(msg, h, k)
+    wt = [_dev(p[n]) for n in ("gemm1_weights", "gemm1_weights_scale", "gemm2_weights", "gemm2_weights_scale")]
+    kw = dict(scale_up=_dev(p["output1_scale_scalar"]), scale_gate=_dev(p["output1_scale_gate_scalar"]),
+              scale_out=_dev(p["output2_scale_scalar"]))
+    layer = MoELayer(h, i, e, k, msg.shape[0])
+    out_strided = torch.empty((msg.shape[0], h), dtype=torch.bfloat16, device="cuda")
+    layer.run(m_ids, m_w, m_q, m_sf, *wt, out_strided, **kw)
+    out_packed = torch.empty_like(out_strided)
+    layer.run(m_ids.contiguous(), m_w.contiguous(), m_q.contiguous(), m_sf.contiguous(), *wt, out_packed, **kw)
+    torch.cuda.synchronize()
+    assert layer.status() == 0
+    assert torch.equal(out_strided, out_packed)
+    assert out_strided.float().abs().sum() > 0
+    # bad strides are refused before any launch
+    odd = torch.zeros((msg.shape[0], h // 2 + 8), dtype=torch.uint8, device="cuda")[:, :h // 2]     # row stride not % 16
+    with pytest.raises((RuntimeError, ValueError), match="stride"):
+        layer.run(m_ids, m_w, odd, m_sf, *wt, out_strided, **kw)
