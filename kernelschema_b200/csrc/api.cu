@@ -10,6 +10,16 @@
 
 using namespace b200;
 
+namespace b200 {
+bool pdl_enabled() {
+  static const bool on = [] {
+    const char* v = getenv("B200MOE_PDL");
+    return !(v && v[0] == '0');
+  }();
+  return on;
+}
+}  // namespace b200
+
 static thread_local char g_err[512] = "";
 
 static int fail(int code, const char* fmt, ...) {
@@ -180,6 +190,7 @@ int run_impl(b200moe_layer* h, const b200moe_args* a, cudaStream_t st, cudaEvent
   g.tile_rows = h->rm.tile_rows;
   g.n_tiles_ptr = h->rm.totals;
   g.status = h->status;
+  if (const char* dbg = getenv("B200MOE_DBG")) g.dbg = atoi(dbg);   // timing experiments only
   // FC1: [rows, H] x [2I, H]^T -> activation -> NVFP4 [rows, I]
   g.N = 2 * c.intermediate;
   g.K = c.hidden;
@@ -364,11 +375,6 @@ int b200moe_create(const b200moe_config* cfg, b200moe_handle* out) {
   h->row_capacity = p.row_capacity;
   h->tile_capacity = p.tile_capacity;
   h->bn = cfg->tile_n ? cfg->tile_n : ((2 * cfg->intermediate) % 256 == 0 && cfg->hidden % 256 == 0 ? 256 : 128);
-  h->n_clusters = 0;
-  if ((2 * cfg->intermediate) % (h->bn == 512 ? 256 : h->bn) || cfg->hidden % (h->bn == 512 ? 256 : h->bn)) {
-    delete h;
-    return fail(718, "create: tile_n=%d does not divide 2*intermediate and hidden", h->bn);
-  }
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e == cudaSuccess) e = cudaDeviceGetAttribute(&h->sm_count, cudaDevAttrMultiProcessorCount, dev);

@@ -12,6 +12,8 @@ __global__ void __launch_bounds__(128) k_finalize(const __nv_bfloat16* __restric
                                                   const float* __restrict__ weight_of_row, int64_t T, int KK, int H,
                                                   __nv_bfloat16* __restrict__ out, int64_t out_stride) {
   const int vecs = H >> 3;
+  pdl_trigger();
+  pdl_wait();
   for (int64_t t = blockIdx.x; t < T; t += gridDim.x) {
     for (int v = blockIdx.y * blockDim.x + threadIdx.x; v < vecs; v += gridDim.y * blockDim.x) {
       float acc[8];
@@ -48,9 +50,8 @@ int launch_finalize(const void* rout, const int32_t* row_of, const float* weight
   // few tokens: spread each token's row over several blocks so that the whole GPU pulls on HBM
   const int chunks = (H / 8 + 127) / 128;
   const int by = blocks >= 148 * 4 ? 1 : (int)(chunks < (148 * 4 + blocks - 1) / blocks ? chunks : (148 * 4 + blocks - 1) / blocks);
-  k_finalize<<<dim3((unsigned)blocks, (unsigned)by), 128, 0, st>>>((const __nv_bfloat16*)rout, row_of, weight_of_row, T, KK, H, (__nv_bfloat16*)out,
-                                              out_stride);
-  return (int)cudaGetLastError();
+  return (int)launch_chain(k_finalize, dim3((unsigned)blocks, (unsigned)by), dim3(128), 0, st, (const __nv_bfloat16*)rout, row_of,
+                           weight_of_row, T, KK, H, (__nv_bfloat16*)out, out_stride);
 }
 
 }  // namespace b200

@@ -16,6 +16,8 @@ __global__ void __launch_bounds__(256) k_gather_rows(const uint8_t* __restrict__
                                                      const int32_t* __restrict__ totals, int H, uint8_t* __restrict__ a_q,
                                                      uint8_t* __restrict__ a_sf) {
   // one warp per permuted row, 16 bytes per lane and step
+  pdl_trigger();
+  pdl_wait();
   const int rows = totals[1];
   const int lane = threadIdx.x & 31;
   const int vec_per_row = H >> 5;      // 16-byte vectors of payload per row (H/2 bytes)
@@ -50,9 +52,9 @@ int launch_gather_rows(const void* hid_q, const void* hid_sf, int hid_sf_tiled, 
   if (row_capacity == 0) return 0;
   int64_t blocks = (row_capacity + 7) / 8;
   if (blocks > 148 * 8) blocks = 148 * 8;
-  k_gather_rows<<<(unsigned)blocks, 256, 0, st>>>((const uint8_t*)hid_q, (const uint8_t*)hid_sf, hid_sf_tiled, q_stride > 0 ? q_stride : H / 2,
-                                                 sf_stride > 0 ? sf_stride : H / 16, tok_of_row, tile_rows, totals, H, (uint8_t*)a_q, (uint8_t*)a_sf);
-  return (int)cudaGetLastError();
+  return (int)launch_chain(k_gather_rows, dim3((unsigned)blocks), dim3(256), 0, st, (const uint8_t*)hid_q, (const uint8_t*)hid_sf,
+                           hid_sf_tiled, q_stride > 0 ? q_stride : (int64_t)(H / 2), sf_stride > 0 ? sf_stride : (int64_t)(H / 16),
+                           tok_of_row, tile_rows, totals, H, (uint8_t*)a_q, (uint8_t*)a_sf);
 }
 
 // ----------------------------------------------------------------------------- expert-parallel dispatch packing

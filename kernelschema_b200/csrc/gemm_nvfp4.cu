@@ -52,16 +52,24 @@ DEV float tanh_fast(float x) {
   return y;
 }
 
-// Epilogue of 128 accumulator columns [col0, col0 + 128) of one tile for the calling warp's 32 TMEM lanes.
-// All 128 values are pulled into registers first and `release` is called right after the last TMEM read, so
-// the accumulator buffer is free again after a few hundred cycles and the arithmetic, the requantisation and the
-// global stores overlap the next tile's mainloop.
-template <int MODE, class Release>
-DEV void epilogue_cols128(const GemmParams& p, uint32_t taddr, int e, size_t row, bool live, int col0, Release release) {
+// Epilogue of EC (64 or 128) accumulator columns [col0, col0 + EC) of one tile for the calling warp's 32 TMEM lanes.
+// The values are pulled into registers first and `release` is called right after the last TMEM read, so the
+// accumulator buffer is free again after a few hundred cycles and the arithmetic, the requantisation and the global
+// stores overlap the next tile's mainloop. EC = 64 (16 epilogue warps on a 256-column tile) keeps four warps on every
+// scheduler: the activation + requantisation chain is latency-bound with two, which shows when the k-loop of a tile is
+// short (K <= 2048: 8 stages, about 4 us); with a long k-loop the eight-warp form (EC = 128) hides it and draws less power.
+template <int MODE, int EC, class Release>
+DEV void epilogue_cols(const GemmParams& p, uint32_t taddr, int e, size_t row, bool live, int col0, Release release) {
+  constexpr int NCB = EC / 32;
   if (p.dbg & 8) live = false;
-  float v[4][32];
+  // a warp whose 32 rows are all padding (decode: a few routes per expert) neither reads the accumulator nor computes
+  if (!__any_sync(0xFFFFFFFFu, live)) {
+    release();
+    return;
+  }
+  float v[NCB][32];
 #pragma unroll
-  for (int cb = 0; cb < 4; ++cb) tmem_ld32(taddr + cb * 32, v[cb]);
+  for (int cb = 0; cb < NCB; ++cb) tmem_ld32(taddr + cb * 32, v[cb]);
   tmem_ld_wait();
   release();
   if (MODE == kGemmFc1) {
@@ -71,10 +79,10 @@ DEV void epilogue_cols128(const GemmParams& p, uint32_t taddr, int e, size_t row
     const float beta = p.beta ? p.beta[e] : 0.0f;
     const bool clamp = p.limit != nullptr;
     const float limit = clamp ? p.limit[e] : 0.f;
-    uint2 packed[4];
+    uint2 packed[NCB];
     uint32_t sfword = 0;
 #pragma unroll
-    for (int cb = 0; cb < 4; ++cb) {
+    for (int cb = 0; cb < NCB; ++cb) {
       float act[16];
       float amax = 0.f;
 #pragma unroll
@@ -111,14 +119,21 @@ DEV void epilogue_cols128(const GemmParams& p, uint32_t taddr, int e, size_t row
     }
     if (live) {
       const int half_i = p.N >> 2;                     // bytes of one row of packed activations (I / 2)
-      const int i0 = col0 >> 1;                        // first intermediate channel of these 128 columns (multiple of 64)
-      asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p.act_q + row * half_i + (i0 >> 1)), "r"(packed[0].x),
-                   "r"(packed[0].y), "r"(packed[1].x), "r"(packed[1].y), "r"(packed[2].x), "r"(packed[2].y), "r"(packed[3].x),
-                   "r"(packed[3].y)
-                   : "memory");
+      const int i0 = col0 >> 1;                        // first intermediate channel of these columns (multiple of EC / 2)
       // scale bytes of 64 channels = one 4-byte word of the 128x4-tiled layout [row/128][I/64][32][16]
       const size_t off = ((row >> 7) * (size_t)(p.N >> 7) + (size_t)(i0 >> 6)) * kSfChunk + (row & 31) * 16 + ((row >> 5) & 3) * 4;
-      *reinterpret_cast<uint32_t*>(p.act_sf + off) = sfword;
+      if constexpr (NCB == 4) {
+        asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p.act_q + row * half_i + (i0 >> 1)), "r"(packed[0].x),
+                     "r"(packed[0].y), "r"(packed[1].x), "r"(packed[1].y), "r"(packed[2].x), "r"(packed[2].y), "r"(packed[3].x),
+                     "r"(packed[3].y)
+                     : "memory");
+        *reinterpret_cast<uint32_t*>(p.act_sf + off) = sfword;
+      } else {
+        asm volatile("st.global.v4.b32 [%0], {%1,%2,%3,%4};" ::"l"(p.act_q + row * half_i + (i0 >> 1)), "r"(packed[0].x),
+                     "r"(packed[0].y), "r"(packed[1].x), "r"(packed[1].y)
+                     : "memory");
+        *reinterpret_cast<uint16_t*>(p.act_sf + off + ((i0 >> 5) & 1) * 2) = (uint16_t)sfword;
+      }
     }
   } else {
     if (!live) return;
@@ -126,7 +141,7 @@ DEV void epilogue_cols128(const GemmParams& p, uint32_t taddr, int e, size_t row
     const size_t orow = (MODE == kGemmFc2 && p.out_row_index) ? (size_t)p.out_row_index[row] : row;
     __nv_bfloat16* dst_row = p.out + orow * p.out_stride + col0;
 #pragma unroll
-    for (int cb = 0; cb < 4; ++cb) {
+    for (int cb = 0; cb < NCB; ++cb) {
       uint32_t o[16];
 #pragma unroll
       for (int j = 0; j < 16; ++j) {
@@ -154,15 +169,15 @@ DEV void epilogue_cols128(const GemmParams& p, uint32_t taddr, int e, size_t row
 }
 
 // Warp roles: 0 = TMA producer, 1 = TMEM owner + MMA issuer, 2 = scale-factor copier (shared memory -> TMEM),
-// 3 .. 3 + BN/32 - 1 = epilogue; epilogue warp w owns TMEM lane quadrant w & 3 and the 128-column group (w - 3) / 4.
-template <int BN>
-constexpr int gemm_threads() { return 32 * (3 + BN / 32); }
+// 3 .. 3 + 4 * BN/EC - 1 = epilogue; epilogue warp w owns TMEM lane quadrant w & 3 and the EC-column group (w - 3) / 4.
+template <int BN, int EC>
+constexpr int gemm_threads() { return 32 * (3 + 4 * BN / EC); }
 
-template <int MODE, int BN>
-__global__ void __launch_bounds__(gemm_threads<BN>(), 1)
+template <int MODE, int BN, int EC>
+__global__ void __launch_bounds__(gemm_threads<BN, EC>(), 1)
 k_gemm_nvfp4(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, const GemmParams p) {
   using C = GemmCfg<BN>;
-  constexpr int kEpiWarps = BN / 32;
+  constexpr int kEpiWarps = 4 * BN / EC;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t s_a = smem_base;
@@ -200,6 +215,8 @@ k_gemm_nvfp4(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
   tc_fence_after();
   uint32_t tmem;
   asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem) : "r"(s_tmem_slot));
+  // everything above touches no global memory: it overlaps the previous kernel of the stream
+  pdl_wait();
 
   const int n_mtiles = p.n_tiles_ptr ? *p.n_tiles_ptr : p.n_tiles_static;
   const int n_ntiles = p.N / BN;
@@ -212,10 +229,21 @@ k_gemm_nvfp4(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
     if (lane == 0) {
       uint32_t s = 0, ph = 1;
       bool ok = true;
+      // the tile-table entries of an item are fetched one item ahead, so their latency hides behind a whole k-loop
+      int mt_n = 0, e_n = 0, row0_n = 0;
+      if (blockIdx.x < total_items) {
+        mt_n = (int)(blockIdx.x / n_ntiles);
+        e_n = p.tile_expert ? p.tile_expert[mt_n] : 0;
+        row0_n = p.tile_row0 ? p.tile_row0[mt_n] : mt_n * kBM;
+      }
       for (long long item = blockIdx.x; ok && item < total_items; item += gridDim.x) {
-        const int mt = (int)(item / n_ntiles), nt = (int)(item % n_ntiles);
-        const int e = p.tile_expert ? p.tile_expert[mt] : 0;
-        const int row0 = p.tile_row0 ? p.tile_row0[mt] : mt * kBM;
+        const int nt = (int)(item - (long long)mt_n * n_ntiles);
+        const int e = e_n, row0 = row0_n;
+        if (item + gridDim.x < total_items) {
+          mt_n = (int)((item + gridDim.x) / n_ntiles);
+          e_n = p.tile_expert ? p.tile_expert[mt_n] : 0;
+          row0_n = p.tile_row0 ? p.tile_row0[mt_n] : mt_n * kBM;
+        }
         const int brow0 = e * p.N + nt * BN;
         const uint8_t* sfa_src = p.sfa + (size_t)(row0 >> 7) * chunks_per_row * kSfChunk;
         const uint8_t* sfb_src = p.sfb + (size_t)(brow0 >> 7) * chunks_per_row * kSfChunk;
@@ -237,6 +265,8 @@ k_gemm_nvfp4(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
           if (++s == C::kStages) { s = 0; ph ^= 1; }
         }
       }
+      // this CTA has asked for its last bytes: the next kernel of the stream may start its prologue under our tail
+      pdl_trigger();
     }
   } else if (warp == 2) {
     // ------------------------------------------------------------------ scale-factor copier: shared memory -> TMEM
@@ -305,7 +335,7 @@ k_gemm_nvfp4(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
   } else {
     // ------------------------------------------------------------------ epilogue
     const int quad = warp & 3;
-    const int group = (warp - 3) >> 2;               // which 128 accumulator columns
+    const int group = (warp - 3) >> 2;               // which EC accumulator columns
     const int r_in_tile = quad * 32 + lane;
     uint32_t it = 0;
     for (long long item = blockIdx.x; item < total_items; item += gridDim.x, ++it) {
@@ -319,8 +349,8 @@ k_gemm_nvfp4(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
       okw = __shfl_sync(0xFFFFFFFFu, okw, 0);
       if (!okw) { if (lane == 0) report(p.status, 104); break; }
       tc_fence_after();
-      const uint32_t taddr = tmem + ((uint32_t)(quad * 32) << 16) + buf * BN + group * 128;
-      epilogue_cols128<MODE>(p, taddr, e, (size_t)row0 + r_in_tile, r_in_tile < rows, nt * BN + group * 128, [&]() {
+      const uint32_t taddr = tmem + ((uint32_t)(quad * 32) << 16) + buf * BN + group * EC;
+      epilogue_cols<MODE, EC>(p, taddr, e, (size_t)row0 + r_in_tile, r_in_tile < rows, nt * BN + group * EC, [&]() {
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_acc_empty + 8 * buf);
@@ -341,7 +371,7 @@ k_gemm_nvfp4(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
 // single-CTA tile. Work item = (pair of consecutive 128-row m-tiles of one expert, 256 weight rows).
 // Barriers: `full` lives in the leader (2 producer arrivals + both CTAs' TMA bytes); `empty` and `acc_full` exist
 // in both CTAs and are signalled by the leader's tcgen05.commit to both; `acc_empty` lives in the leader and
-// collects the 8 epilogue warps of the pair.
+// collects the 32 epilogue warps of the pair.
 struct PairCfg {
   static constexpr int kStages = 5;
   static constexpr int kABytes = 128 * 128;
@@ -354,7 +384,7 @@ struct PairCfg {
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
 };
 
-constexpr int kPairThreads = 32 * 11;    // TMA, MMA, scale-factor copier, 8 epilogue warps
+constexpr int kPairThreads = 32 * 19;    // TMA, MMA, scale-factor copier, 16 epilogue warps
 
 template <int MODE>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
@@ -373,7 +403,7 @@ k_gemm_nvfp4_pair(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   const uint32_t bar_sf = bar_full + 8 * C::kStages;          // leader: scale factors copied into both CTAs' TMEM
   const uint32_t bar_empty = bar_sf + 8 * C::kStages;         // both CTAs: MMAs of the stage retired
   const uint32_t bar_acc_full = bar_empty + 8 * C::kStages;   // both CTAs
-  const uint32_t bar_acc_empty = bar_acc_full + 8;            // leader: 16 epilogue warps of the pair
+  const uint32_t bar_acc_empty = bar_acc_full + 8;            // leader: 32 epilogue warps of the pair
   const uint32_t s_tmem_slot = bar_acc_empty + 8;
 
   const int warp = threadIdx.x >> 5;
@@ -388,7 +418,7 @@ k_gemm_nvfp4_pair(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       mbar_init(bar_empty + 8 * s, 1);
     }
     mbar_init(bar_acc_full, 1);
-    mbar_init(bar_acc_empty, 16);
+    mbar_init(bar_acc_empty, 32);
     mbar_init_fence();
   }
   if (warp == 1) tmem_alloc_pair<512>(s_tmem_slot);
@@ -398,6 +428,7 @@ k_gemm_nvfp4_pair(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   tc_fence_after();
   uint32_t tmem;
   asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem) : "r"(s_tmem_slot));
+  pdl_wait();
 
   const int n_pairs = p.n_tiles_ptr ? *p.n_tiles_ptr : p.n_tiles_static;
   const int n_ntiles = p.N / BN;
@@ -435,6 +466,7 @@ k_gemm_nvfp4_pair(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
           if (++s == C::kStages) { s = 0; ph ^= 1; }
         }
       }
+      pdl_trigger();
     }
   } else if (warp == 2) {
     // ------------------------------------------------------------------ scale-factor copier (leader; acts on both CTAs)
@@ -512,8 +544,8 @@ k_gemm_nvfp4_pair(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       okw = __shfl_sync(0xFFFFFFFFu, okw, 0);
       if (!okw) { if (lane == 0) report(p.status, 204); break; }
       tc_fence_after();
-      const uint32_t taddr = tmem + ((uint32_t)(quad * 32) << 16) + group * 128;
-      epilogue_cols128<MODE>(p, taddr, e, (size_t)row0 + r_in_tile, r_in_tile < rows, nt * BN + group * 128, [&]() {
+      const uint32_t taddr = tmem + ((uint32_t)(quad * 32) << 16) + group * 64;
+      epilogue_cols<MODE, 64>(p, taddr, e, (size_t)row0 + r_in_tile, r_in_tile < rows, nt * BN + group * 64, [&]() {
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive_remote(acc_empty_leader);
@@ -584,8 +616,7 @@ static int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUten
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  kern<<<grid, kPairThreads, PairCfg::kSmemBytes, st>>>(ta, tb, tsa, tsb, p);
-  return (int)cudaGetLastError();
+  return (int)launch_chain(kern, dim3(grid), dim3(kPairThreads), PairCfg::kSmemBytes, st, ta, tb, tsa, tsb, p);
 }
 
 // grid = 2 CTAs per work-item stream, at most one pair per two SMs
@@ -599,34 +630,43 @@ int launch_gemm_nvfp4_pair(int mode, const CUtensorMap& ta, const CUtensorMap& t
   return launch_pair<kGemmDense>(ta, tb, tsa, tsb, p, grid, st);
 }
 
-template <int MODE, int BN>
+template <int MODE, int BN, int EC>
 static int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid, cudaStream_t st) {
-  auto kern = k_gemm_nvfp4<MODE, BN>;
+  auto kern = k_gemm_nvfp4<MODE, BN, EC>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmCfg<BN>::kSmemBytes);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  kern<<<grid, gemm_threads<BN>(), GemmCfg<BN>::kSmemBytes, st>>>(ta, tb, p);
-  return (int)cudaGetLastError();
+  return (int)launch_chain(kern, dim3(grid), dim3(gemm_threads<BN, EC>()), GemmCfg<BN>::kSmemBytes, st, ta, tb, p);
+}
+
+// Epilogue columns per warp: 64 when a tile's k-loop is too short to hide the eight-warp epilogue (see epilogue_cols).
+static int epilogue_cols_for(int k) {
+  static const int forced = [] {
+    const char* v = getenv("B200MOE_EPI_COLS");      // timing experiments only
+    return v ? atoi(v) : 0;
+  }();
+  if (forced == 64 || forced == 128) return forced;
+  return k >= 4096 ? 128 : 64;
+}
+
+template <int MODE>
+static int launch_mode(int bn, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid, cudaStream_t st) {
+  const int ec = epilogue_cols_for(p.K);
+  if (bn == 128) return ec == 64 ? launch_one<MODE, 128, 64>(ta, tb, p, grid, st) : launch_one<MODE, 128, 128>(ta, tb, p, grid, st);
+  if (bn == 256) return ec == 64 ? launch_one<MODE, 256, 64>(ta, tb, p, grid, st) : launch_one<MODE, 256, 128>(ta, tb, p, grid, st);
+  return 703;
 }
 
 int launch_gemm_nvfp4(int mode, int bn, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid,
                       cudaStream_t st) {
   if (grid <= 0) return 0;
   if (p.K % kStageK != 0 || p.N % bn != 0) return 702;
-  if (bn == 128) {
-    if (mode == kGemmFc1) return launch_one<kGemmFc1, 128>(ta, tb, p, grid, st);
-    if (mode == kGemmFc2) return launch_one<kGemmFc2, 128>(ta, tb, p, grid, st);
-    return launch_one<kGemmDense, 128>(ta, tb, p, grid, st);
-  }
-  if (bn == 256) {
-    if (mode == kGemmFc1) return launch_one<kGemmFc1, 256>(ta, tb, p, grid, st);
-    if (mode == kGemmFc2) return launch_one<kGemmFc2, 256>(ta, tb, p, grid, st);
-    return launch_one<kGemmDense, 256>(ta, tb, p, grid, st);
-  }
-  return 703;
+  if (mode == kGemmFc1) return launch_mode<kGemmFc1>(bn, ta, tb, p, grid, st);
+  if (mode == kGemmFc2) return launch_mode<kGemmFc2>(bn, ta, tb, p, grid, st);
+  return launch_mode<kGemmDense>(bn, ta, tb, p, grid, st);
 }
 
 }  // namespace b200

@@ -9,6 +9,25 @@ namespace b200 {
 
 enum { kGemmDense = 0, kGemmFc1 = 1, kGemmFc2 = 2 };
 
+// True unless the environment says B200MOE_PDL=0 (read once): launches carry the programmatic-stream-serialization
+// attribute, so consecutive kernels of the layer overlap launch latency and prologue (see pdl_wait in ptx.cuh).
+bool pdl_enabled();
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_chain(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
 // Device buffers produced by the route-map build.
 struct RouteMapBuffers {
   int32_t* block_hist;     // [nblk, E'] scratch

@@ -13,6 +13,14 @@ namespace b200 {
 constexpr uint32_t kSpinLimit = 1u << 24;   // polls of try_wait before a wait is declared dead (~ a few seconds)
 
 DEV uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+// Programmatic dependent launch: `pdl_trigger` lets the next kernel of the stream start its prologue while this grid is
+// still running; `pdl_wait` blocks until every earlier grid of the stream has finished and its writes are visible.
+// Every kernel of the layer chain issues both before it touches global memory, so the only overlap is launch latency
+// and prologue (barrier init, TMEM allocation, tensor-map prefetch). Both are no-ops in a kernel launched without the
+// attribute.
+DEV void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+DEV void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 DEV uint32_t lane_id() { return threadIdx.x & 31; }
 
 // ----------------------------------------------------------------------------- mbarrier

@@ -27,6 +27,8 @@ __global__ void __launch_bounds__(256) k_quantize_nvfp4(const __nv_bfloat16* __r
                                                         uint8_t* __restrict__ scales, int sf_layout) {
   // One block walks rows, its threads walk the 16-element blocks of a row: no integer division anywhere.
   const int blocks_per_row = (int)(cols >> 4);
+  pdl_trigger();
+  pdl_wait();
   for (int64_t row = blockIdx.x; row < rows; row += gridDim.x)
   for (int blk = threadIdx.x; blk < blocks_per_row; blk += blockDim.x) {
     const uint4* src = reinterpret_cast<const uint4*>(x + row * row_stride + blk * 16);
@@ -115,13 +117,10 @@ int launch_quantize_nvfp4(const void* x, int64_t rows, int64_t cols, int64_t row
   int exp2 = 0;
   const bool pow2 = frexpf(gs, &exp2) == 0.5f && exp2 > -100 && exp2 < 100;     // gs = 2^(exp2-1): exact pre-scaling
   if (pow2)
-    k_quantize_nvfp4<false><<<(unsigned)blocks, threads, 0, st>>>((const __nv_bfloat16*)x, rows, cols, row_stride, gs,
-                                                                 ldexpf(1.0f, 1 - exp2), (uint8_t*)payload, (uint8_t*)scales,
-                                                                 sf_layout);
-  else
-    k_quantize_nvfp4<true><<<(unsigned)blocks, threads, 0, st>>>((const __nv_bfloat16*)x, rows, cols, row_stride, gs, 1.0f,
-                                                                (uint8_t*)payload, (uint8_t*)scales, sf_layout);
-  return (int)cudaGetLastError();
+    return (int)launch_chain(k_quantize_nvfp4<false>, dim3((unsigned)blocks), dim3(threads), 0, st, (const __nv_bfloat16*)x, rows, cols,
+                             row_stride, gs, ldexpf(1.0f, 1 - exp2), (uint8_t*)payload, (uint8_t*)scales, sf_layout);
+  return (int)launch_chain(k_quantize_nvfp4<true>, dim3((unsigned)blocks), dim3(threads), 0, st, (const __nv_bfloat16*)x, rows, cols,
+                           row_stride, gs, 1.0f, (uint8_t*)payload, (uint8_t*)scales, sf_layout);
 }
 
 int launch_sf_to_tiles(const void* src, int64_t rows, int64_t blocks_per_row, void* dst, cudaStream_t st) {

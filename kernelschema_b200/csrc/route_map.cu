@@ -35,24 +35,51 @@ DEV int route_expert(const RouteView& r, int64_t f, int64_t total) {
   return (e >= 0 && e < r.E) ? e : -1;
 }
 
+// Lanes of the warp whose expert equals this lane's: one ballot per bit of the expert id instead of __match_any_sync,
+// whose cost grows with the number of distinct values in the warp (close to 32 here). `bits` covers ids below the
+// expert count; the extra round on bit `bits` separates the invalid id -1 from the expert made of all ones.
+DEV unsigned same_expert_lanes(int e, int bits) {
+  unsigned m = 0xFFFFFFFFu;
+  for (int b = 0; b <= bits; ++b) {
+    const bool set = (e >> b) & 1;
+    const unsigned bal = __ballot_sync(0xFFFFFFFFu, set);
+    m &= set ? bal : ~bal;
+  }
+  return m;
+}
+DEV int expert_bits(int etot) { return etot > 1 ? 32 - __clz(etot - 1) : 0; }
+
 constexpr int kRouteSteps = kRouteChunk / kRouteWarps / 32;   // routes per lane in a chunk
+constexpr int kRoutesPerWarp = kRouteSteps * 32;
 
 // Expert of each of this lane's routes in the block's chunk: all loads are issued before any is used.
 DEV void load_chunk(const RouteView& r, int64_t total, int64_t chunk_base, int (&e)[kRouteSteps]) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int64_t base = chunk_base + warp * (kRouteChunk / kRouteWarps);
+  const int64_t base = chunk_base + warp * kRoutesPerWarp;
 #pragma unroll
   for (int step = 0; step < kRouteSteps; ++step) e[step] = route_expert(r, base + step * 32 + lane, total);
+}
+
+// The same for a build whose routes all fit 32-bit indices (the one-block kernel): no 64-bit divisions.
+DEV int route_expert32(const RouteView& r, int f, int total) {
+  if (f >= total) return -1;
+  const int kk = r.K + r.S;
+  const int t = f / kk;
+  const int k = f - t * kk;
+  if (k >= r.K) return r.E + (k - r.K);
+  const int e = r.ids[(int64_t)t * r.id_stride + k] - r.expert_offset;
+  return (e >= 0 && e < r.E) ? e : -1;
 }
 
 // Per-warp histograms of this block's chunk into hist[warp][e]; each warp owns its row, so no atomics.
 DEV void chunk_histogram(const int (&e)[kRouteSteps], int etot, int* hist) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int i = threadIdx.x; i < kRouteWarps * etot; i += blockDim.x) hist[i] = 0;
+  const int bits = expert_bits(etot);
+  for (int i = threadIdx.x; i < (int)(blockDim.x >> 5) * etot; i += blockDim.x) hist[i] = 0;
   __syncthreads();
 #pragma unroll
   for (int step = 0; step < kRouteSteps; ++step) {
-    const unsigned m = __match_any_sync(0xFFFFFFFFu, e[step]);
+    const unsigned m = same_expert_lanes(e[step], bits);
     if (e[step] >= 0 && lane == (__ffs(m) - 1)) hist[warp * etot + e[step]] += __popc(m);
     __syncwarp();
   }
@@ -61,6 +88,8 @@ DEV void chunk_histogram(const int (&e)[kRouteSteps], int etot, int* hist) {
 
 __global__ void __launch_bounds__(256) k_route_hist(RouteView r, int etot, int32_t* __restrict__ block_hist) {
   extern __shared__ int hist[];
+  pdl_trigger();
+  pdl_wait();
   const int64_t total = r.T * (r.K + r.S);
   int ex[kRouteSteps];
   load_chunk(r, total, (int64_t)blockIdx.x * kRouteChunk, ex);
@@ -84,6 +113,8 @@ __global__ void __launch_bounds__(1024) k_route_scan(int etot, int nblk, int32_t
   __shared__ int warp_pad[32], warp_tiles[32], warp_cnt[32], warp_pairs[32];
   __shared__ int carry[4];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  pdl_trigger();
+  pdl_wait();
   if (threadIdx.x < 4) carry[threadIdx.x] = 0;
   __syncthreads();
   for (int e0 = 0; e0 < etot; e0 += blockDim.x) {
@@ -162,6 +193,8 @@ __global__ void __launch_bounds__(256) k_route_scatter(RouteView r, const float*
                                                        int32_t* __restrict__ row_of, int32_t* __restrict__ tok_of_row,
                                                        float* __restrict__ weight_of_row) {
   extern __shared__ int hist[];
+  pdl_trigger();
+  pdl_wait();
   const int kk = r.K + r.S;
   const int64_t total = r.T * kk;
   int ex[kRouteSteps];
@@ -179,48 +212,97 @@ __global__ void __launch_bounds__(256) k_route_scatter(RouteView r, const float*
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t base = (int64_t)blockIdx.x * kRouteChunk + warp * (kRouteChunk / kRouteWarps);
+  float wt[kRouteSteps];      // all loads before any store
+  int32_t tk[kRouteSteps];
 #pragma unroll
   for (int step = 0; step < kRouteSteps; ++step) {
     const int64_t f = base + step * 32 + lane;
+    const int64_t t = f / kk;
+    const int k = (int)(f - t * kk);
+    tk[step] = (int32_t)t;
+    wt[step] = (scores && ex[step] >= 0 && k < r.K) ? scores[t * r.id_stride + k] : 1.0f;
+  }
+  int pos[kRouteSteps];
+#pragma unroll
+  for (int step = 0; step < kRouteSteps; ++step) {
     const int e = ex[step];
-    const unsigned m = __match_any_sync(0xFFFFFFFFu, e);
-    int pos = -1;
-    if (e >= 0) pos = hist[warp * etot + e] + __popc(m & ((1u << lane) - 1u));
+    const unsigned m = same_expert_lanes(e, expert_bits(etot));
+    pos[step] = -1;
+    if (e >= 0) pos[step] = hist[warp * etot + e] + __popc(m & ((1u << lane) - 1u));
     __syncwarp();
     if (e >= 0 && lane == (__ffs(m) - 1)) hist[warp * etot + e] += __popc(m);
     __syncwarp();
+  }
+#pragma unroll
+  for (int step = 0; step < kRouteSteps; ++step) {
+    const int64_t f = base + step * 32 + lane;
     if (f < total) {
-      row_of[f] = pos;
-      if (pos >= 0) {
-        const int64_t t = f / kk;
-        const int k = (int)(f - t * kk);
-        tok_of_row[pos] = (int32_t)t;
-        weight_of_row[pos] = (k < r.K) ? (scores ? scores[t * r.id_stride + k] : 1.0f) : 1.0f;
+      row_of[f] = pos[step];
+      if (pos[step] >= 0) {
+        tok_of_row[pos[step]] = tk[step];
+        weight_of_row[pos[step]] = wt[step];
       }
     }
   }
 }
 
-// Whole build in one block when all routes fit one chunk (decode sizes): histogram, scan, tile list, stable scatter,
-// in one launch instead of three.
-__global__ void __launch_bounds__(256) k_route_single(RouteView r, const float* __restrict__ scores, int etot, RouteMapBuffers b) {
-  extern __shared__ int hist[];                    // [kRouteWarps][etot], then the running bases
+// Whole build in ONE launch for decode-to-medium sizes (up to kFusedMaxBlocks x 2048 routes). Block c scatters chunk c,
+// and instead of exchanging histograms with the other blocks it reads ALL expert ids itself (a few tens of KB): that
+// gives it every expert's total (segment starts, tile list) and the count in the chunks before its own (its base inside
+// the segment). The counts of foreign chunks are accumulated with shared-memory atomics; a count does not depend on the
+// order of the additions, so every output stays reproducible. Block 0 also writes the per-expert tables.
+constexpr int kFusedMaxBlocks = 8;
+
+__global__ void __launch_bounds__(256) k_route_fused(RouteView r, const float* __restrict__ scores, int etot, RouteMapBuffers b) {
+  extern __shared__ int hist[];                    // own chunk [kRouteWarps][etot] | all chunks [etot] | chunks before [etot]
   __shared__ int warp_pad[8], warp_tiles[8], warp_pairs[8], warp_cnt[8];
   __shared__ int carry[4];
+  int* others = hist + kRouteWarps * etot;         // routes of expert e in the other chunks
+  int* before = others + etot;                     // ... in the chunks before this block's
   const int kk = r.K + r.S;
-  const int64_t total = r.T * kk;
+  const int total = (int)(r.T * kk);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const bool writer = blockIdx.x == 0;
+  pdl_trigger();
+  pdl_wait();
+  for (int i = threadIdx.x; i < 2 * etot; i += blockDim.x) others[i] = 0;
+  __syncthreads();
   int ex[kRouteSteps];
-  load_chunk(r, total, 0, ex);
-  chunk_histogram(ex, etot, hist);
+  float wt[kRouteSteps];                           // routing weight of each own route: fetched with the ids, before any store
+#pragma unroll
+  for (int step = 0; step < kRouteSteps; ++step) {
+    const int f = (int)blockIdx.x * kRouteChunk + warp * kRoutesPerWarp + step * 32 + lane;
+    ex[step] = route_expert32(r, f, total);
+    wt[step] = 1.0f;
+    if (scores && ex[step] >= 0 && ex[step] < r.E) {
+      const int t = f / kk;
+      wt[step] = scores[(int64_t)t * r.id_stride + (f - t * kk)];
+    }
+  }
+  for (int c = 0; c < (int)gridDim.x; ++c) {
+    if (c == (int)blockIdx.x) continue;
+    int eo[kRouteSteps];
+#pragma unroll
+    for (int step = 0; step < kRouteSteps; ++step)
+      eo[step] = route_expert32(r, c * kRouteChunk + warp * kRoutesPerWarp + step * 32 + lane, total);
+#pragma unroll
+    for (int step = 0; step < kRouteSteps; ++step)
+      if (eo[step] >= 0) {
+        atomicAdd(&others[eo[step]], 1);
+        if (c < (int)blockIdx.x) atomicAdd(&before[eo[step]], 1);
+      }
+  }
+  chunk_histogram(ex, etot, hist);                 // own chunk, per warp; its barriers also publish others/before
   if (threadIdx.x < 4) carry[threadIdx.x] = 0;
   __syncthreads();
   for (int e0 = 0; e0 < etot; e0 += blockDim.x) {
     const int e = e0 + threadIdx.x;
     int cnt = 0;
-    if (e < etot)
+    if (e < etot) {
+      cnt = others[e];
 #pragma unroll
       for (int w = 0; w < kRouteWarps; ++w) cnt += hist[w * etot + e];
+    }
     const int ntile = (cnt + 127) >> 7, pad = ntile << 7, npair = (ntile + 1) >> 1;
     int ip = pad, it = ntile, ic = cnt, iq = npair;
 #pragma unroll
@@ -235,20 +317,22 @@ __global__ void __launch_bounds__(256) k_route_single(RouteView r, const float* 
     for (int w = 0; w < warp; ++w) { bp += warp_pad[w]; bt += warp_tiles[w]; bq += warp_pairs[w]; }
     const int start = bp + ip - pad, tile0 = bt + it - ntile, pair0 = bq + iq - npair;
     if (e < etot) {
-      b.counts[e] = cnt;
-      b.seg_start[e] = start;
-      for (int j = 0; j < ntile; ++j) {
-        b.tile_expert[tile0 + j] = e;
-        b.tile_row0[tile0 + j] = start + (j << 7);
-        b.tile_rows[tile0 + j] = min(128, cnt - (j << 7));
-      }
-      if (b.pair_expert)
-        for (int j = 0; j < npair; ++j) {
-          b.pair_expert[pair0 + j] = e;
-          b.pair_row0[pair0 + j] = start + (j << 8);
-          b.pair_rows[pair0 + j] = min(256, cnt - (j << 8));
+      if (writer) {
+        b.counts[e] = cnt;
+        b.seg_start[e] = start;
+        for (int j = 0; j < ntile; ++j) {
+          b.tile_expert[tile0 + j] = e;
+          b.tile_row0[tile0 + j] = start + (j << 7);
+          b.tile_rows[tile0 + j] = min(128, cnt - (j << 7));
         }
-      int run = start;                               // per-warp bases of this expert, in place of the counts
+        if (b.pair_expert)
+          for (int j = 0; j < npair; ++j) {
+            b.pair_expert[pair0 + j] = e;
+            b.pair_row0[pair0 + j] = start + (j << 8);
+            b.pair_rows[pair0 + j] = min(256, cnt - (j << 8));
+          }
+      }
+      int run = start + before[e];                   // per-warp bases of this expert, in place of the counts
 #pragma unroll
       for (int w = 0; w < kRouteWarps; ++w) {
         const int c = hist[w * etot + e];
@@ -259,7 +343,7 @@ __global__ void __launch_bounds__(256) k_route_single(RouteView r, const float* 
     __syncthreads();
     if (threadIdx.x == blockDim.x - 1) {
       int tc = 0;
-      for (int w = 0; w < (int)(blockDim.x >> 5); ++w) tc += warp_cnt[w];
+      for (int w = 0; w < kRouteWarps; ++w) tc += warp_cnt[w];
       carry[0] = bp + ip;
       carry[1] = bt + it;
       carry[2] += tc;
@@ -267,31 +351,32 @@ __global__ void __launch_bounds__(256) k_route_single(RouteView r, const float* 
     }
     __syncthreads();
   }
-  if (threadIdx.x == 0) {
+  if (writer && threadIdx.x == 0) {
     b.seg_start[etot] = carry[0];
     b.totals[0] = carry[1];
     b.totals[1] = carry[0];
     b.totals[2] = carry[2];
     b.totals[3] = carry[3];
   }
-  const int64_t base = (int64_t)warp * (kRouteChunk / kRouteWarps);
+  int pos[kRouteSteps];
 #pragma unroll
   for (int step = 0; step < kRouteSteps; ++step) {
-    const int64_t f = base + step * 32 + lane;
     const int e = ex[step];
-    const unsigned m = __match_any_sync(0xFFFFFFFFu, e);
-    int pos = -1;
-    if (e >= 0) pos = hist[warp * etot + e] + __popc(m & ((1u << lane) - 1u));
+    const unsigned m = same_expert_lanes(e, expert_bits(etot));
+    pos[step] = -1;
+    if (e >= 0) pos[step] = hist[warp * etot + e] + __popc(m & ((1u << lane) - 1u));
     __syncwarp();
     if (e >= 0 && lane == (__ffs(m) - 1)) hist[warp * etot + e] += __popc(m);
     __syncwarp();
+  }
+#pragma unroll
+  for (int step = 0; step < kRouteSteps; ++step) {
+    const int f = (int)blockIdx.x * kRouteChunk + warp * kRoutesPerWarp + step * 32 + lane;
     if (f < total) {
-      b.row_of[f] = pos;
-      if (pos >= 0) {
-        const int64_t t = f / kk;
-        const int k = (int)(f - t * kk);
-        b.tok_of_row[pos] = (int32_t)t;
-        b.weight_of_row[pos] = (k < r.K) ? (scores ? scores[t * r.id_stride + k] : 1.0f) : 1.0f;
+      b.row_of[f] = pos[step];
+      if (pos[step] >= 0) {
+        b.tok_of_row[pos[step]] = f / kk;
+        b.weight_of_row[pos[step]] = wt[step];
       }
     }
   }
@@ -303,18 +388,18 @@ int launch_route_map(const int32_t* ids, const float* scores, int64_t id_stride,
   const int64_t total = T * (K + S);
   const int nblk = (int)((total + kRouteChunk - 1) / kRouteChunk);
   RouteView r{ids, id_stride > 0 ? id_stride : K, T, K, S, E, expert_offset};
-  if (nblk == 1) {
-    k_route_single<<<1, 256, sizeof(int) * kRouteWarps * (size_t)etot, st>>>(r, scores, etot, b);
-    return (int)cudaGetLastError();
-  }
+  if (nblk >= 1 && nblk <= kFusedMaxBlocks)
+    return (int)launch_chain(k_route_fused, dim3(nblk), dim3(256), sizeof(int) * (kRouteWarps + 2) * (size_t)etot, st, r, scores, etot, b);
   const size_t smem = sizeof(int) * kRouteWarps * (size_t)etot;
-  if (nblk > 0) k_route_hist<<<nblk, 256, smem, st>>>(r, etot, b.block_hist);
-  k_route_scan<<<1, 1024, 0, st>>>(etot, nblk, b.block_hist, b.counts, b.seg_start, b.tile_expert, b.tile_row0, b.tile_rows,
-                                   b.totals, b.pair_expert, b.pair_row0, b.pair_rows);
-  if (nblk > 0)
-    k_route_scatter<<<nblk, 256, smem, st>>>(r, scores, etot, b.block_hist, b.seg_start, b.row_of, b.tok_of_row,
-                                            b.weight_of_row);
-  return (int)cudaGetLastError();
+  cudaError_t err = cudaSuccess;
+  if (nblk > 0) err = launch_chain(k_route_hist, dim3(nblk), dim3(256), smem, st, r, etot, b.block_hist);
+  if (err == cudaSuccess)
+    err = launch_chain(k_route_scan, dim3(1), dim3(1024), 0, st, etot, nblk, b.block_hist, b.counts, b.seg_start, b.tile_expert,
+                       b.tile_row0, b.tile_rows, b.totals, b.pair_expert, b.pair_row0, b.pair_rows);
+  if (err == cudaSuccess && nblk > 0)
+    err = launch_chain(k_route_scatter, dim3(nblk), dim3(256), smem, st, r, scores, etot, (const int32_t*)b.block_hist,
+                       (const int32_t*)b.seg_start, b.row_of, b.tok_of_row, b.weight_of_row);
+  return (int)err;
 }
 
 // ----------------------------------------------------------------------------- allocation-free variant

@@ -16,6 +16,8 @@ __global__ void __launch_bounds__(256) k_route_topk(const float* __restrict__ lo
                                                     int E, int K, int32_t* __restrict__ ids, float* __restrict__ weights) {
   const int lane = threadIdx.x & 31;
   const int64_t tok = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  pdl_trigger();
+  pdl_wait();
   if (tok >= T) return;
   float v[PL];
 #pragma unroll
@@ -133,6 +135,8 @@ k_router_logits_tc(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
   tc_fence_after();
   uint32_t tmem;
   asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem) : "r"(s_slot));
+  pdl_trigger();
+  pdl_wait();
   const int n_tiles = (T + 127) >> 7;
   const int nk = H >> 6;
   const uint32_t stage_bytes = kLgABytes + (uint32_t)e_pad * 128;
@@ -226,8 +230,8 @@ int launch_router_logits_tc(const void* x, const void* w, int64_t T, int H, int 
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int n_tiles = (int)((T + 127) / 128);
-  k_router_logits_tc<<<n_tiles < sms ? n_tiles : sms, 192, kLgSmem, st>>>(tx, tw, (int)T, H, E, e_pad, logits, status);
-  return (int)cudaGetLastError();
+  return (int)launch_chain(k_router_logits_tc, dim3(n_tiles < sms ? n_tiles : sms), dim3(192), kLgSmem, st, tx, tw, (int)T, H, E, e_pad,
+                           logits, status);
 }
 
 int launch_route_topk(const float* logits, const float* bias, int64_t T, int E, int K, int32_t* ids, float* weights,
@@ -235,13 +239,14 @@ int launch_route_topk(const float* logits, const float* bias, int64_t T, int E, 
   if (T == 0) return 0;
   const unsigned blocks = (unsigned)((T * 32 + 255) / 256);
   const int per_lane = (E + 31) / 32;
-  if (per_lane <= 1) k_route_topk<1><<<blocks, 256, 0, st>>>(logits, bias, T, E, K, ids, weights);
-  else if (per_lane <= 2) k_route_topk<2><<<blocks, 256, 0, st>>>(logits, bias, T, E, K, ids, weights);
-  else if (per_lane <= 4) k_route_topk<4><<<blocks, 256, 0, st>>>(logits, bias, T, E, K, ids, weights);
-  else if (per_lane <= 8) k_route_topk<8><<<blocks, 256, 0, st>>>(logits, bias, T, E, K, ids, weights);
-  else if (per_lane <= 16) k_route_topk<16><<<blocks, 256, 0, st>>>(logits, bias, T, E, K, ids, weights);
-  else k_route_topk<32><<<blocks, 256, 0, st>>>(logits, bias, T, E, K, ids, weights);
-  return (int)cudaGetLastError();
+  cudaError_t err;
+  if (per_lane <= 1) err = launch_chain(k_route_topk<1>, dim3(blocks), dim3(256), 0, st, logits, bias, T, E, K, ids, weights);
+  else if (per_lane <= 2) err = launch_chain(k_route_topk<2>, dim3(blocks), dim3(256), 0, st, logits, bias, T, E, K, ids, weights);
+  else if (per_lane <= 4) err = launch_chain(k_route_topk<4>, dim3(blocks), dim3(256), 0, st, logits, bias, T, E, K, ids, weights);
+  else if (per_lane <= 8) err = launch_chain(k_route_topk<8>, dim3(blocks), dim3(256), 0, st, logits, bias, T, E, K, ids, weights);
+  else if (per_lane <= 16) err = launch_chain(k_route_topk<16>, dim3(blocks), dim3(256), 0, st, logits, bias, T, E, K, ids, weights);
+  else err = launch_chain(k_route_topk<32>, dim3(blocks), dim3(256), 0, st, logits, bias, T, E, K, ids, weights);
+  return (int)err;
 }
 
 int launch_router_logits(const void* x, const void* w, int64_t T, int H, int E, float* logits, cudaStream_t st) {
