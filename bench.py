@@ -326,6 +326,20 @@ def run_gpu(args, wl):
     ms = timed(resident, args.steps, args.warmup)
     clocks = sampler.stop() if rank == 0 else None
     ms_e2e = timed(end_to_end, args.steps, max(1, args.warmup), finish=e2e_finish)
+    # Decode sizes: the same resident step replayed from a CUDA graph (one host call per step instead of ~10 launches;
+    # the programmatic-dependent-launch edges between the kernels survive the capture).
+    graph_ms = None
+    if world == 1 and (args.graph or t <= 2048):
+        side = torch.cuda.Stream(device)
+        side.wait_stream(torch.cuda.current_stream(device))
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                step(x_dev)
+        torch.cuda.current_stream(device).wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            step(x_dev)
+        graph_ms = timed(graph.replay, args.steps, args.warmup) / args.steps
     status = owner.status()
 
     valid = (state["ids"] >= 0).sum().to(torch.float64)
@@ -393,6 +407,8 @@ def run_gpu(args, wl):
                 e2e=dict(value=tflops_e2e, unit="TFLOP/s", h2d_bytes_per_step=x_host.numel() * 2, d2h_bytes_per_step=out_host.numel() * 2,
                          ms_per_step=ms_e2e / args.steps),
                 gpu_launches=launches * args.steps, device_status=status, clocks=clocks)
+    if graph_ms is not None:
+        line["graph_replay"] = dict(ms_per_step=graph_ms, tokens_per_s=t / (graph_ms * 1e-3))
     if ep_stage:
         line["stage_ms"] = ep_stage
     if stage:
@@ -493,6 +509,52 @@ def run_dense(args):
                           frac_of_nominal_fp4=tf / FP4_NOMINAL_TFLOPS)))
 
 
+def run_dense_w4a16(args):
+    """Dense GEMM with bf16 activations and NVFP4 weights (A not quantised): the second catalogue operator's contract.
+    Also times torch.matmul (cuBLAS bf16) on weights expanded to bf16 beforehand, as the library alternative."""
+    import torch
+    import kernelschema_b200 as ks
+    m, n, k = (int(v) for v in args.dense.split(","))
+    a = torch.randn(m, k, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(n, k, device="cuda") * k ** -0.5).to(torch.bfloat16)
+    bq, bsf = ks.nvfp4_quantize(w, 1.0)
+    bsf = bsf.view(torch.uint8)
+    alpha = torch.ones(1, dtype=torch.float32, device="cuda")
+    out = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+
+    def timed(fn):
+        for _ in range(max(3, args.warmup)):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / args.steps
+
+    ms = timed(lambda: ks.mm_bf16_nvfp4(a, bq, bsf, alpha, out=out, status=status))
+    # library alternative: the same product by cuBLAS on pre-expanded bf16 weights (reads 3.6x the weight bytes)
+    lut = torch.tensor([0, .5, 1, 1.5, 2, 3, 4, 6, -0., -.5, -1, -1.5, -2, -3, -4, -6], device="cuda")
+    codes = torch.stack((bq & 15, bq >> 4), -1).long().reshape(n, k)
+    w_dec = (lut[codes] * bsf.view(torch.float8_e4m3fn).float().repeat_interleave(16, -1)).to(torch.bfloat16)
+    ref = torch.empty_like(out)
+    ms_lib = timed(lambda: torch.matmul(a, w_dec.t(), out=ref))
+    agree = float(((out.float() - ref.float()).norm() / ref.float().norm()).item())
+    tf = 2.0 * m * n * k / (ms * 1e-3) / 1e12
+    pk = peaks()
+    print(json.dumps(dict(metric="bf16_nvfp4_dense_gemm_tflops", value=tf, unit="TFLOP/s", n_gpus=1, steps=args.steps, warmup=args.warmup,
+                          ms_per_step=ms, higher_is_better=True, dtype="bf16 x nvfp4 (weights expanded to bf16 exactly, fp32 accumulate)",
+                          data="synthetic", config=dict(workload=f"dense_bf16_nvfp4_gemm_{m}x{n}x{k}"),
+                          device_status=int(status.item()),
+                          roofline=dict(bound="tensor", achieved=tf, peak=pk["bf16"], unit="TFLOP/s", frac=tf / pk["bf16"],
+                                        peak_source=f"bf16_tflops (burst) of {pk['source']} MEASURED_PEAKS"),
+                          cublas_bf16=dict(ms_per_step=ms_lib, tflops=2.0 * m * n * k / (ms_lib * 1e-3) / 1e12, rel_l2_between=agree),
+                          hbm_algorithmic_gbs=(m * k * 2 + n * k * 9 / 16 + m * n * 2) / (ms * 1e-3) / 1e9)))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -502,11 +564,13 @@ def main():
     ap.add_argument("--workload", default="dsv3", choices=sorted(WORKLOADS))
     ap.add_argument("--zipf", type=float, default=None, help="override the workload's Zipf exponent of the router bias (0 = uniform)")
     ap.add_argument("--tokens", type=int, default=None, help="override the workload's tokens per GPU (e.g. 64 or 256 for decode)")
+    ap.add_argument("--graph", action="store_true", help="also time the step replayed from a CUDA graph (always done up to 2048 tokens)")
     ap.add_argument("--dense", default=None, metavar="M,N,K", help="time the dense NVFP4 GEMM of this shape instead of the layer")
+    ap.add_argument("--a-bf16", action="store_true", help="with --dense: keep A in bf16 (the bf16 x NVFP4 operator) instead of quantising it")
     ap.add_argument("--tile-n", type=int, default=0, help="GEMM tile for --dense (0 = default, 128, 256, 512 = CTA pair)")
     args = ap.parse_args()
     if args.dense:
-        return run_dense(args)
+        return run_dense_w4a16(args) if args.a_bf16 else run_dense(args)
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     wl = dict(WORKLOADS[args.workload])
     if args.tokens is not None:

@@ -132,6 +132,15 @@ int b200moe_router_logits(const void* x, const void* gate_weight, int64_t num_to
 int b200moe_gemm_nvfp4(const void* a_q, const void* a_sf_tiled, const void* b_q, const void* b_sf_tiled, float alpha, void* out,
                        int64_t m, int64_t n, int64_t k, int64_t out_stride, int32_t tile_n, int32_t* status, void* stream);
 
+/* Dense GEMM with bf16 activations and NVFP4 weights: out[M,N] = bf16(alpha * A @ decode(B)^T), A NOT quantised. The
+ * contract of DG/problem/reference.py:10-15 as the operator publishes it (production entry flashinfer.mm_bf16_fp4,
+ * DG/problem/solution.py:11-12): a bf16 [M, K] (a_stride elements between rows), b_q uint8 [N, K/2], b_descale E4M3
+ * [N, K/16] row-major (not tiled), alpha a device fp32 scalar or NULL (= 1). K % 256 == 0, N % 128 == 0; out 32-byte
+ * aligned with out_stride % 16 == 0. The weights are expanded to bf16 exactly (E2M1 x E4M3 has 6 significant bits), so
+ * the result differs from the fp32 reference only by the order of the fp32 additions. */
+int b200moe_gemm_bf16_nvfp4(const void* a, int64_t a_stride, const void* b_q, const void* b_descale, const float* alpha, void* out,
+                            int64_t m, int64_t n, int64_t k, int64_t out_stride, int32_t* status, void* stream);
+
 /* Layer life cycle. Replaces moe_init / moe_run of NV/candidate/nvfp4_moe.cu:6618, :9496 (bound there through
  * ctypes, NV/candidate/solution.py:96-102). create allocates the workspace on the current device. */
 int b200moe_create(const b200moe_config* cfg, b200moe_handle* out);

@@ -579,11 +579,11 @@ static EncodeTiledFn encode_fn() {
 }
 
 // 2-D byte tensor [rows, row_bytes] -> boxes of 128 bytes x box_rows rows, 128-byte swizzle.
-int make_operand_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_rows) {
+int make_operand_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_rows, uint64_t pitch_bytes) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return 701;
   cuuint64_t dims[2] = {row_bytes, rows};
-  cuuint64_t strides[1] = {row_bytes};
+  cuuint64_t strides[1] = {pitch_bytes ? pitch_bytes : row_bytes};
   cuuint32_t box[2] = {128, box_rows};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,

@@ -114,6 +114,30 @@ def mm_nvfp4(a_q, a_sf_tiled, b_q, b_sf_tiled, alpha: float = 1.0, out: torch.Te
     return out
 
 
+def mm_bf16_nvfp4(a: torch.Tensor, b: torch.Tensor, b_descale: torch.Tensor, alpha: torch.Tensor | None = None,
+                  out: torch.Tensor | None = None, status: torch.Tensor | None = None) -> torch.Tensor:
+    """out[M, N] = bf16(alpha * a @ decode(b)^T): bf16 activations [M, K] (not quantised), NVFP4 weights uint8 [N, K/2] with
+    row-major E4M3 scales [N, K/16], alpha a 1-element fp32 device tensor or None (the dense operator's contract,
+    gemm/dense/bf16_nvfp4_gemm/problem/reference.py:10-15)."""
+    _need_cuda(a, b, b_descale, out, alpha)
+    if a.dtype != torch.bfloat16 or a.dim() != 2 or a.stride(1) != 1:
+        raise ValueError("a must be a bf16 matrix with unit column stride")
+    m, k = a.shape
+    n = b.shape[0]
+    if b.shape[1] * 2 != k or b_descale.shape != (n, k // 16) or not b.is_contiguous() or not b_descale.is_contiguous():
+        raise ValueError(f"b must be contiguous [N, K/2] and b_descale contiguous [N, K/16]; got {tuple(b.shape)}, {tuple(b_descale.shape)}")
+    if alpha is not None and (alpha.dtype != torch.float32 or alpha.numel() != 1):
+        raise ValueError("alpha must be one fp32 value")
+    if out is None:
+        out = torch.empty((m, n), dtype=torch.bfloat16, device=a.device)
+    if out.dtype != torch.bfloat16 or out.shape != (m, n) or out.stride(1) != 1:
+        raise ValueError("out must be bf16 [M, N] with unit column stride")
+    _lib.check(_lib.load().b200moe_gemm_bf16_nvfp4(a.data_ptr(), a.stride(0), b.data_ptr(), b_descale.data_ptr(), _ptr(alpha),
+                                                   out.data_ptr(), m, n, k, out.stride(0), _ptr(status), _stream()),
+               "b200moe_gemm_bf16_nvfp4")
+    return out
+
+
 def combine(rows: torch.Tensor, row_of: torch.Tensor, weight_of_row: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     """out[t] = bf16(sum_s rows[row_of[t, s]] * weight_of_row[row_of[t, s]]) (reference.py:91-92), slots ascending."""
     _need_cuda(rows, row_of, weight_of_row, out)

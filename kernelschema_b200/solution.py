@@ -95,3 +95,23 @@ class Model(torch.nn.Module):
                   activation_type=int(activation_type), expert_offset=int(local_expert_offset or 0))
         self._last_inputs = keep   # keep converted temporaries alive until the stream has consumed them
         return [output]
+
+
+class DenseModel(torch.nn.Module):
+    """Drop-in ``Model`` for the reference operator ``bf16_nvfp4_gemm`` (gemm/dense/bf16_nvfp4_gemm/problem/reference.py:18-25;
+    production entry ``flashinfer.mm_bf16_fp4``, problem/solution.py:11-12): same positional/keyword ``forward``; writes
+    ``out`` in place and returns it. ``a`` stays bf16 (it is not quantised); ``b`` uint8 [N, K/2] with row-major E4M3
+    ``b_descale`` [N, K/16]; ``alpha`` a one-element fp32 tensor or None. ``backend`` and ``enable_pdl`` are accepted and
+    ignored (there is one backend; launches always carry the programmatic-dependent-launch attribute)."""
+
+    def forward(self, a, b, b_descale, alpha=None, *, backend=None, out_dtype=None, out=None, block_size=16, enable_pdl=True):
+        from .ops import mm_bf16_nvfp4
+        if block_size != 16:
+            raise ValueError("NVFP4 uses blocks of 16 elements")
+        if out_dtype not in (None, torch.bfloat16):
+            raise ValueError("only bfloat16 output is supported")
+        if b_descale.dtype != torch.uint8:
+            b_descale = b_descale.view(torch.uint8)
+        if b.dtype != torch.uint8:
+            b = b.view(torch.uint8)
+        return mm_bf16_nvfp4(a, b, b_descale, alpha, out=out)
