@@ -1,7 +1,7 @@
 """Generate the golden fixtures under tests/golden/ from the reference's own Python code.
 
-Run once, in a container that has the reference checkout (default
-``/root/reference``, override with ``KERNELSCHEMA_REFERENCE``):
+Run once, in a container that has the reference checkout (its location is
+taken from ``KERNELSCHEMA_REFERENCE``):
 
     python tests/golden/make_golden.py
 

@@ -124,7 +124,8 @@ def test_w4a16_matches_reference_output_bits():
 
 
 @pytest.mark.parametrize("m,n,k,outliers", [(1, 128, 256, False), (100, 256, 512, False), (129, 384, 768, True), (256, 128, 2048, False),
-                                            (300, 1536, 1024, False), (1000, 512, 256, True)])
+                                            (300, 1536, 1024, False), (1000, 512, 256, True), (300, 384, 512, False),
+                                            (513, 768, 1024, False)])
 def test_w4a16_matches_oracle(m, n, k, outliers):
     import kernelschema_b200 as ks
     a, bq, bsf = _w4a16_case(m, n, k, 100 + m, outliers)
