@@ -137,9 +137,15 @@ int b200moe_gemm_nvfp4(const void* a_q, const void* a_sf_tiled, const void* b_q,
  * DG/problem/solution.py:11-12): a bf16 [M, K] (a_stride elements between rows), b_q uint8 [N, K/2], b_descale E4M3
  * [N, K/16] row-major (not tiled), alpha a device fp32 scalar or NULL (= 1). K % 256 == 0, N % 128 == 0; out 32-byte
  * aligned with out_stride % 16 == 0. The weights are expanded to bf16 exactly (E2M1 x E4M3 has 6 significant bits), so
- * the result differs from the fp32 reference only by the order of the fp32 additions. */
+ * the result differs from the fp32 reference only by the order of the fp32 additions.
+ * workspace (optional, 16-byte aligned device memory of at least b200moe_gemm_bf16_nvfp4_workspace_bytes(m, n, k) bytes;
+ * that function returns 0 when none is useful): for M <= 128 it lets several CTAs share the reduction of one output
+ * tile (fp32 partial sums added in a fixed order: results stay reproducible). Without it every tile is reduced by one
+ * CTA, which leaves most of the device idle at small M. */
+int64_t b200moe_gemm_bf16_nvfp4_workspace_bytes(int64_t m, int64_t n, int64_t k);
 int b200moe_gemm_bf16_nvfp4(const void* a, int64_t a_stride, const void* b_q, const void* b_descale, const float* alpha, void* out,
-                            int64_t m, int64_t n, int64_t k, int64_t out_stride, int32_t* status, void* stream);
+                            int64_t m, int64_t n, int64_t k, int64_t out_stride, void* workspace, int64_t workspace_bytes,
+                            int32_t* status, void* stream);
 
 /* Layer life cycle. Replaces moe_init / moe_run of NV/candidate/nvfp4_moe.cu:6618, :9496 (bound there through
  * ctypes, NV/candidate/solution.py:96-102). create allocates the workspace on the current device. */

@@ -58,8 +58,9 @@ SIGNATURES = {
     "b200moe_workspace_bytes": (C.c_int64, [C.POINTER(Config)]),
     "b200moe_workspace": (C.c_int, [C.c_void_p, C.POINTER(WorkspaceView)]),
     "b200moe_route_map": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p]),
+    "b200moe_gemm_bf16_nvfp4_workspace_bytes": (C.c_int64, [C.c_int64, C.c_int64, C.c_int64]),
     "b200moe_gemm_bf16_nvfp4": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64,
-                                          C.c_int64, C.c_int64, C.c_void_p, C.c_void_p]),
+                                          C.c_int64, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p]),
     "b200moe_ep_visits": (C.c_int, [C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
     "b200moe_ep_pack": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32,
                                   C.c_int64, C.c_void_p, C.c_void_p]),

@@ -356,8 +356,14 @@ int b200moe_gemm_nvfp4(const void* a_q, const void* a_sf, const void* b_q, const
   return cuda_fail(launch_gemm_nvfp4(kGemmDense, bn, ta, tb, g, grid, (cudaStream_t)stream), "gemm");
 }
 
+int64_t b200moe_gemm_bf16_nvfp4_workspace_bytes(int64_t m, int64_t n, int64_t k) {
+  if (m <= 0 || n <= 0 || k <= 0 || k % 256 || n % 128) return 0;
+  return gemm_w4a16_workspace_bytes(m, n, k);
+}
+
 int b200moe_gemm_bf16_nvfp4(const void* a, int64_t a_stride, const void* b_q, const void* b_descale, const float* alpha, void* out,
-                            int64_t m, int64_t n, int64_t k, int64_t out_stride, int32_t* status, void* stream) {
+                            int64_t m, int64_t n, int64_t k, int64_t out_stride, void* workspace, int64_t workspace_bytes,
+                            int32_t* status, void* stream) {
   if (m < 0 || n <= 0 || k <= 0 || k % 256 || n % 128)
     return fail(765, "gemm_bf16_nvfp4: M=%lld N=%lld K=%lld need K %% 256 == 0 and N %% 128 == 0", (long long)m, (long long)n, (long long)k);
   if (m == 0) return 0;
@@ -367,7 +373,9 @@ int b200moe_gemm_bf16_nvfp4(const void* a, int64_t a_stride, const void* b_q, co
   if (a_stride < k || a_stride % 8) return fail(768, "gemm_bf16_nvfp4: a_stride must be >= K and a multiple of 8 elements");
   if (out_stride < n || out_stride % 16 || ((uintptr_t)out & 31))
     return fail(769, "gemm_bf16_nvfp4: out must be 32-byte aligned, out_stride >= N and a multiple of 16");
-  return cuda_fail(launch_gemm_w4a16(a, a_stride, b_q, b_descale, alpha, m, n, k, out, out_stride, status, (cudaStream_t)stream),
+  if (workspace && ((uintptr_t)workspace & 15)) return fail(769, "gemm_bf16_nvfp4: workspace must be 16-byte aligned");
+  return cuda_fail(launch_gemm_w4a16(a, a_stride, b_q, b_descale, alpha, m, n, k, out, out_stride, workspace,
+                                     workspace ? workspace_bytes : 0, status, (cudaStream_t)stream),
                    "gemm_bf16_nvfp4");
 }
 

@@ -48,6 +48,11 @@ struct W4A16Params {
   int64_t out_stride;
   int M, N, K;
   int32_t* status;
+  // split-K (small M only): `splits` CTAs share one output tile, each reduces `groups_per_split` k-groups of 256 and
+  // writes fp32 partial sums to partial[split][M][N]; k_w4a16_reduce adds them in split order. splits == 1: no workspace.
+  int splits;
+  int groups_per_split;
+  float* partial;
 };
 
 DEV void fence_async_proxy() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
@@ -102,9 +107,24 @@ DEV void decode_half_stage(const uint32_t* w, uint32_t sf2, uint32_t dst, uint32
 // BN accumulator columns of the calling warp's 32 lanes -> alpha * x as bf16 at out[row, col0 ...], 64 columns at a
 // time; `release` is called right after the last TMEM read. A warp without live rows only releases.
 template <int BN, class Release>
-DEV void store_cols(const W4A16Params& p, uint32_t taddr, int row, bool live, int col0, float alpha, Release release) {
+DEV void store_cols(const W4A16Params& p, uint32_t taddr, int row, bool live, int col0, float alpha, int split, Release release) {
   if (!__any_sync(0xFFFFFFFFu, live)) {
     release();
+    return;
+  }
+  if (BN == 128 && p.splits > 1) {                   // fp32 partial sums of this split; alpha and the rounding come in the reduce
+    float* dst = p.partial + ((size_t)split * p.M + row) * p.N + col0;
+#pragma unroll
+    for (int pass = 0; pass < BN / 32; ++pass) {
+      float v[32];
+      tmem_ld32(taddr + pass * 32, v);
+      tmem_ld_wait();
+      if (pass == BN / 32 - 1) release();
+      if (live) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) reinterpret_cast<float4*>(dst + pass * 32)[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+      }
+    }
     return;
   }
   __nv_bfloat16* dst_row = p.out + (size_t)row * p.out_stride + col0;
@@ -174,8 +194,13 @@ k_gemm_w4a16(const __grid_constant__ CUtensorMap tm_a, const W4A16Params p) {
 
   const int n_mt = (p.M + 255) >> 8;        // 256-row tiles of A
   const int n_nt = p.N / BN;                // BN-row tiles of the weights
-  const int nk = p.K >> 6;                  // k-steps of 64
-  const int total_items = n_mt * n_nt;      // n fastest: the CTAs of a wave share A's rows and sweep the weights (L2-resident)
+  const int groups = p.K >> 8;              // k-groups of 256 weights = one 128-byte line per weight row
+  // item = (tile, split), split fastest; tile = (mt, nt), n fastest: the CTAs of a wave share A's rows and sweep the
+  // weights (L2-resident). A split covers k-groups [g0, g1).
+  const int total_items = n_mt * n_nt * p.splits;
+  auto item_tile = [&](int item) { return item / p.splits; };
+  auto item_g0 = [&](int item) { return (item % p.splits) * p.groups_per_split; };
+  auto item_g1 = [&](int item) { return min(groups, (item % p.splits + 1) * p.groups_per_split); };
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer of A
@@ -183,8 +208,8 @@ k_gemm_w4a16(const __grid_constant__ CUtensorMap tm_a, const W4A16Params p) {
       uint32_t s = 0, ph = 1;
       bool ok = true;
       for (int item = blockIdx.x; ok && item < total_items; item += gridDim.x) {
-        const int mt = item / n_nt;
-        for (int ks = 0; ks < nk; ++ks) {
+        const int mt = item_tile(item) / n_nt;
+        for (int ks = 4 * item_g0(item); ks < 4 * item_g1(item); ++ks) {
           if (!mbar_wait(bar_empty + 8 * s, ph)) { if (p.status) atomicCAS(p.status, 0, 121); ok = false; break; }
           mbar_expect_tx(bar_full_a + 8 * s, C::kABytes);
           tma_load_2d(s_a + s * C::kABytes, &tm_a, bar_full_a + 8 * s, ks * 128, mt * 256);
@@ -200,8 +225,9 @@ k_gemm_w4a16(const __grid_constant__ CUtensorMap tm_a, const W4A16Params p) {
       uint32_t s = 0, ph = 0, it = 0;
       bool ok = true;
       for (int item = blockIdx.x; ok && item < total_items; item += gridDim.x, ++it) {
-        const int mt = item / n_nt;
+        const int mt = item_tile(item) / n_nt;
         const bool second = p.M - mt * 256 > 128;          // rows 128..255 of the tile hold real rows
+        const int nk = 4 * (item_g1(item) - item_g0(item));
         const uint32_t buf = it % C::kAccBufs;
         if (!mbar_wait(bar_acc_empty + 8 * buf, ((it / C::kAccBufs) & 1) ^ 1)) { if (p.status) atomicCAS(p.status, 0, 122); break; }
         tc_fence_after();
@@ -228,7 +254,6 @@ k_gemm_w4a16(const __grid_constant__ CUtensorMap tm_a, const W4A16Params p) {
   } else if (warp < C::kEpiWarp0) {
     // ------------------------------------------------------------------ weight decoders: thread = weight row of the tile
     const int r = threadIdx.x - 64;                         // 0 .. BN-1
-    const int groups = p.K >> 8;                            // k-groups of 256 weights = one 128-byte line per row
     const uint32_t row_off = (uint32_t)r * 128u;
     const uint32_t sw = (uint32_t)(r & 7);
     uint32_t s = 0, ph = 1;
@@ -236,16 +261,17 @@ k_gemm_w4a16(const __grid_constant__ CUtensorMap tm_a, const W4A16Params p) {
     uint4 nxt[8];
     uint4 nxt_sf;
     auto fetch = [&](int item, int g) {
-      const int nt = item % n_nt;
+      const int nt = item_tile(item) % n_nt;
       const size_t row = (size_t)nt * BN + r;
       const uint4* q = reinterpret_cast<const uint4*>(p.b_q + row * (size_t)(p.K >> 1)) + (size_t)g * 8;
 #pragma unroll
       for (int i = 0; i < 8; ++i) nxt[i] = __ldg(q + i);
       nxt_sf = __ldg(reinterpret_cast<const uint4*>(p.b_sf + row * (size_t)(p.K >> 4)) + g);
     };
-    if ((int)blockIdx.x < total_items) fetch(blockIdx.x, 0);
+    if ((int)blockIdx.x < total_items) fetch(blockIdx.x, item_g0(blockIdx.x));
     for (int item = blockIdx.x; ok && item < total_items; item += gridDim.x) {
-      for (int g = 0; ok && g < groups; ++g) {
+      const int g1 = item_g1(item);
+      for (int g = item_g0(item); ok && g < g1; ++g) {
         uint32_t cur[32];
         uint32_t cur_sf[4];
 #pragma unroll
@@ -254,8 +280,8 @@ k_gemm_w4a16(const __grid_constant__ CUtensorMap tm_a, const W4A16Params p) {
         }
         cur_sf[0] = nxt_sf.x; cur_sf[1] = nxt_sf.y; cur_sf[2] = nxt_sf.z; cur_sf[3] = nxt_sf.w;
         // next line: the following k-group of this item, or the first of this CTA's next item
-        if (g + 1 < groups) fetch(item, g + 1);
-        else if (item + (int)gridDim.x < total_items) fetch(item + gridDim.x, 0);
+        if (g + 1 < g1) fetch(item, g + 1);
+        else if (item + (int)gridDim.x < total_items) fetch(item + gridDim.x, item_g0(item + gridDim.x));
 #pragma unroll
         for (int q = 0; q < 4; ++q) {                       // the four 64-wide k-steps of the group
           int okw = 1;
@@ -279,7 +305,8 @@ k_gemm_w4a16(const __grid_constant__ CUtensorMap tm_a, const W4A16Params p) {
     const float alpha = p.alpha ? *p.alpha : 1.0f;
     uint32_t it = 0;
     for (int item = blockIdx.x; item < total_items; item += gridDim.x, ++it) {
-      const int mt = item / n_nt, nt = item % n_nt;
+      const int tile = item_tile(item);
+      const int mt = tile / n_nt, nt = tile % n_nt;
       const uint32_t buf = it % C::kAccBufs;
       int okw = 1;
       if (lane == 0) okw = mbar_wait(bar_acc_full + 8 * buf, (it / C::kAccBufs) & 1) ? 1 : 0;
@@ -289,7 +316,7 @@ k_gemm_w4a16(const __grid_constant__ CUtensorMap tm_a, const W4A16Params p) {
       const int row = mt * 256 + half * 128 + quad * 32 + lane;
       const bool live = row < p.M;
       const uint32_t taddr = tmem + ((uint32_t)(quad * 32) << 16) + buf * 2 * BN + half * BN;
-      store_cols<BN>(p, taddr, row, live, nt * BN, alpha, [&]() {
+      store_cols<BN>(p, taddr, row, live, nt * BN, alpha, item % p.splits, [&]() {
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_acc_empty + 8 * buf);
@@ -304,7 +331,46 @@ k_gemm_w4a16(const __grid_constant__ CUtensorMap tm_a, const W4A16Params p) {
   }
 }
 
+// out[m, n] = bf16(alpha * sum over splits of partial[s][m][n]), splits added in ascending order (reproducible).
+__global__ void __launch_bounds__(256) k_w4a16_reduce(const float* __restrict__ partial, const float* __restrict__ alpha_ptr, int splits,
+                                                      int64_t M, int64_t N, __nv_bfloat16* __restrict__ out, int64_t out_stride) {
+  pdl_trigger();
+  pdl_wait();
+  const float alpha = alpha_ptr ? *alpha_ptr : 1.0f;
+  const int64_t quads = M * N / 4;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < quads; i += (int64_t)gridDim.x * blockDim.x) {
+    float4 acc = reinterpret_cast<const float4*>(partial)[i];
+    for (int s = 1; s < splits; ++s) {
+      const float4 v = reinterpret_cast<const float4*>(partial + (size_t)s * M * N)[i];
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    const int64_t m = (i * 4) / N, n = (i * 4) % N;
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x * alpha, acc.y * alpha), hi = __floats2bfloat162_rn(acc.z * alpha, acc.w * alpha);
+    uint2 o;
+    o.x = *reinterpret_cast<const uint32_t*>(&lo);
+    o.y = *reinterpret_cast<const uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(out + m * out_stride + n) = o;
+  }
+}
+
 }  // namespace
+
+// Split-K plan for small M: enough CTAs per output tile to occupy the device; 1 = no split (no workspace needed).
+static int w4a16_splits(int64_t m, int64_t n, int64_t k, int sms) {
+  if (m > 128) return 1;
+  const int64_t tiles = n / 128, groups = k / 256;
+  int64_t s = sms / tiles;
+  if (s > 8) s = 8;
+  if (s > groups) s = groups;
+  return s < 2 ? 1 : (int)s;
+}
+
+int64_t gemm_w4a16_workspace_bytes(int64_t m, int64_t n, int64_t k) {
+  int dev = 0, sms = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) sms = 148;
+  const int s = w4a16_splits(m, n, k, sms);
+  return s > 1 ? (int64_t)s * m * n * 4 : 0;
+}
 
 template <int BN>
 static int launch_w4a16(const CUtensorMap& ta, const W4A16Params& p, int sms, cudaStream_t st) {
@@ -315,12 +381,13 @@ static int launch_w4a16(const CUtensorMap& ta, const W4A16Params& p, int sms, cu
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  const int64_t items = (int64_t)((p.M + 255) / 256) * (p.N / BN);
+  const int64_t items = (int64_t)((p.M + 255) / 256) * (p.N / BN) * p.splits;
   return (int)launch_chain(kern, dim3((unsigned)(items < sms ? items : sms)), dim3(WCfg<BN>::kThreads), WCfg<BN>::kSmem, st, ta, p);
 }
 
 int launch_gemm_w4a16(const void* a, int64_t a_stride, const void* b_q, const void* b_sf, const float* alpha, int64_t m, int64_t n,
-                      int64_t k, void* out, int64_t out_stride, int32_t* status, cudaStream_t st) {
+                      int64_t k, void* out, int64_t out_stride, void* workspace, int64_t workspace_bytes, int32_t* status,
+                      cudaStream_t st) {
   if (m == 0) return 0;
   static const int forced = [] {
     const char* v = getenv("B200MOE_W4A16_TILE_N");      // timing experiments only
@@ -344,7 +411,21 @@ int launch_gemm_w4a16(const void* a, int64_t a_stride, const void* b_q, const vo
   p.N = (int)n;
   p.K = (int)k;
   p.status = status;
-  return bn == 256 ? launch_w4a16<256>(ta, p, sms, st) : launch_w4a16<128>(ta, p, sms, st);
+  p.splits = 1;
+  p.groups_per_split = (int)(k / 256);
+  p.partial = nullptr;
+  const int want = w4a16_splits(m, n, k, sms);
+  if (bn == 128 && want > 1 && workspace && workspace_bytes >= (int64_t)want * m * n * 4) {
+    p.groups_per_split = (int)((k / 256 + want - 1) / want);
+    p.splits = (int)((k / 256 + p.groups_per_split - 1) / p.groups_per_split);      // no empty split
+    p.partial = (float*)workspace;
+  }
+  rc = bn == 256 ? launch_w4a16<256>(ta, p, sms, st) : launch_w4a16<128>(ta, p, sms, st);
+  if (rc || p.splits == 1) return rc;
+  const int64_t quads = m * n / 4;
+  const int64_t blocks = (quads + 255) / 256;
+  return (int)launch_chain(k_w4a16_reduce, dim3((unsigned)(blocks < 148 * 8 ? blocks : 148 * 8)), dim3(256), 0, st, (const float*)p.partial,
+                           alpha, p.splits, m, n, (__nv_bfloat16*)out, out_stride);
 }
 
 }  // namespace b200

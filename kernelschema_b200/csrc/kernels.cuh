@@ -97,7 +97,9 @@ int launch_finalize(const void* rout, const int32_t* row_of, const float* weight
 int make_operand_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_rows,
                      uint64_t pitch_bytes = 0);   // pitch 0 = rows are contiguous
 int launch_gemm_w4a16(const void* a, int64_t a_stride, const void* b_q, const void* b_sf, const float* alpha, int64_t m, int64_t n,
-                      int64_t k, void* out, int64_t out_stride, int32_t* status, cudaStream_t st);
+                      int64_t k, void* out, int64_t out_stride, void* workspace, int64_t workspace_bytes, int32_t* status,
+                      cudaStream_t st);
+int64_t gemm_w4a16_workspace_bytes(int64_t m, int64_t n, int64_t k);
 int make_sf_map(CUtensorMap* map, const void* base, uint64_t n_chunks);
 int launch_gemm_nvfp4_pair(int mode, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tsa, const CUtensorMap& tsb,
                            const GemmParams& p, int n_clusters, cudaStream_t st);

@@ -114,8 +114,11 @@ def mm_nvfp4(a_q, a_sf_tiled, b_q, b_sf_tiled, alpha: float = 1.0, out: torch.Te
     return out
 
 
+_W4A16_WORKSPACE: dict = {}     # device index -> fp32 split-K scratch, grown on demand (small M only)
+
+
 def mm_bf16_nvfp4(a: torch.Tensor, b: torch.Tensor, b_descale: torch.Tensor, alpha: torch.Tensor | None = None,
-                  out: torch.Tensor | None = None, status: torch.Tensor | None = None) -> torch.Tensor:
+                  out: torch.Tensor | None = None, status: torch.Tensor | None = None, split_k: bool = True) -> torch.Tensor:
     """out[M, N] = bf16(alpha * a @ decode(b)^T): bf16 activations [M, K] (not quantised), NVFP4 weights uint8 [N, K/2] with
     row-major E4M3 scales [N, K/16], alpha a 1-element fp32 device tensor or None (the dense operator's contract,
     gemm/dense/bf16_nvfp4_gemm/problem/reference.py:10-15)."""
@@ -132,8 +135,18 @@ def mm_bf16_nvfp4(a: torch.Tensor, b: torch.Tensor, b_descale: torch.Tensor, alp
         out = torch.empty((m, n), dtype=torch.bfloat16, device=a.device)
     if out.dtype != torch.bfloat16 or out.shape != (m, n) or out.stride(1) != 1:
         raise ValueError("out must be bf16 [M, N] with unit column stride")
-    _lib.check(_lib.load().b200moe_gemm_bf16_nvfp4(a.data_ptr(), a.stride(0), b.data_ptr(), b_descale.data_ptr(), _ptr(alpha),
-                                                   out.data_ptr(), m, n, k, out.stride(0), _ptr(status), _stream()),
+    lib = _lib.load()
+    ws = None
+    need = int(lib.b200moe_gemm_bf16_nvfp4_workspace_bytes(m, n, k)) if split_k else 0
+    if need:
+        # one scratch buffer per device, reused by later calls on the same stream order (calls on different streams
+        # that may overlap should pass split_k=False or run on one stream)
+        dev = a.device.index
+        ws = _W4A16_WORKSPACE.get(dev)
+        if ws is None or ws.numel() < need:
+            ws = _W4A16_WORKSPACE[dev] = torch.empty(need, dtype=torch.uint8, device=a.device)
+    _lib.check(lib.b200moe_gemm_bf16_nvfp4(a.data_ptr(), a.stride(0), b.data_ptr(), b_descale.data_ptr(), _ptr(alpha), out.data_ptr(),
+                                           m, n, k, out.stride(0), _ptr(ws), need, _ptr(status), _stream()),
                "b200moe_gemm_bf16_nvfp4")
     return out
 

@@ -175,3 +175,23 @@ def test_w4a16_rejects_bad_shapes():
     a = torch.zeros((8, 128), dtype=torch.bfloat16, device="cuda")
     with pytest.raises((ValueError, RuntimeError)):
         ks.mm_bf16_nvfp4(a, torch.zeros((128, 64), dtype=torch.uint8, device="cuda"), torch.zeros((128, 8), dtype=torch.uint8, device="cuda"))
+
+
+@pytest.mark.parametrize("m,n,k", [(16, 4096, 3072), (128, 1024, 2048), (1, 256, 1024), (100, 7168, 2048)])
+def test_w4a16_split_k_small_m(m, n, k):
+    """Small M: several CTAs share one output tile through fp32 partial sums added in a fixed order. Same result as the
+    one-CTA-per-tile form up to the order of the fp32 additions, and identical from run to run."""
+    import kernelschema_b200 as ks
+    a, bq, bsf = _w4a16_case(m, n, k, 300 + m)
+    args = (_bf16_dev(a), torch.from_numpy(bq).cuda(), torch.from_numpy(bsf).cuda(), torch.tensor([1.25], dtype=torch.float32, device="cuda"))
+    y_split = ks.mm_bf16_nvfp4(*args, split_k=True)
+    y_again = ks.mm_bf16_nvfp4(*args, split_k=True)
+    y_plain = ks.mm_bf16_nvfp4(*args, split_k=False)
+    torch.cuda.synchronize()
+    assert torch.equal(y_split, y_again)
+    ref = o.dense_expected(a, bq, bsf, 1.25)
+    for y in (y_split, y_plain):
+        got = y.float().cpu().numpy()
+        r = compare_outputs(got, ref)
+        assert r["rel_l2"] <= 1e-3 and r["max_abs"] <= 2e-2 * r["rms"], r
+        assert (np.abs(got - ref) <= 0.01 + 0.05 * np.abs(ref)).all()
