@@ -53,7 +53,7 @@ def peaks():
 
 # --------------------------------------------------------------------------------------------- clocks
 class ClockSampler:
-    """Samples SM clock, power and throttle reasons through NVML (read-only) every 50 ms while the timed region runs."""
+    """Samples SM clock, power and throttle reasons through NVML (read-only) every 5 ms while the timed region runs."""
 
     def __init__(self, index: int):
         self.index = index
@@ -100,7 +100,7 @@ class ClockSampler:
                         self.reasons.add(n)
             except Exception:
                 pass
-            self._stop.wait(0.05)
+            self._stop.wait(0.005)
 
     def stop(self):
         if self._thread is None:
@@ -558,7 +558,7 @@ def run_dense_w4a16(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference", "reference-gpu"])
     ap.add_argument("--workload", default="dsv3", choices=sorted(WORKLOADS))

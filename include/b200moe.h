@@ -40,7 +40,8 @@ typedef struct {
   int32_t num_shared_experts; /* S experts every token also visits with weight 1; stored after the routed ones */
   int32_t max_tokens;         /* largest T a run may pass */
   int32_t tile_n;             /* GEMM tile: 0 = default; 128 or 256 = one CTA per 128 x tile_n tile; 512 = CTA pair per 256 x 256 tile */
-  int32_t reserved[8];
+  int32_t sm_margin;          /* SMs the persistent GEMM grids leave free (0 = use all): room for a collective that runs beside them */
+  int32_t reserved[7];
 } b200moe_config;
 
 /* One forward call. Field names follow the reference operator's forward() arguments

@@ -79,6 +79,7 @@ int check_cfg(const b200moe_config* c) {
     return fail(713, "config: num_experts + num_shared_experts must be in 1..1024");
   if (c->top_k < 0 || c->top_k > 32 || c->top_k + c->num_shared_experts <= 0) return fail(714, "config: top_k out of range");
   if (c->max_tokens <= 0) return fail(715, "config: max_tokens must be positive");
+  if (c->sm_margin < 0 || c->sm_margin > 64) return fail(708, "config: sm_margin must be in 0..64");
   if (c->tile_n != 0 && c->tile_n != 128 && c->tile_n != 256 && c->tile_n != 512)
     return fail(716, "config: tile_n must be 0, 128, 256 or 512");
   return 0;
@@ -406,6 +407,7 @@ int b200moe_create(const b200moe_config* cfg, b200moe_handle* out) {
     delete h;
     return cuda_fail((int)e, "create: workspace allocation");
   }
+  if (h->sm_count > 2 * cfg->sm_margin) h->sm_count -= cfg->sm_margin;   // persistent GEMM grids stay off `sm_margin` SMs
   h->bytes = p.total;
   uint8_t* b = (uint8_t*)h->base;
   h->rm.block_hist = (int32_t*)(b + p.off_block_hist);

@@ -136,7 +136,8 @@ class ExpertParallelMoE:
     "torch" (`plan_messages_torch`; the only choice on CPU)."""
 
     def __init__(self, hidden, intermediate, num_experts, top_k, tokens_per_rank, num_shared_experts=0, group=None,
-                 expert_rows=None, combine_rows=None, shared_rows=None, recv_capacity=None, planner=None):
+                 expert_rows=None, combine_rows=None, shared_rows=None, recv_capacity=None, planner=None, micro_batches=None,
+                 sm_margin=None):
         self.group = group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
@@ -152,7 +153,17 @@ class ExpertParallelMoE:
         self._combine_rows = combine_rows or self._cuda_combine_rows
         self._shared_rows = shared_rows or self._cuda_shared_rows
         self.planner = planner
+        # Optional: two micro-batches (token halves) pipeline the exchanges under the expert GEMMs (dispatch of the second
+        # half beside the experts of the first, the return of the first beside the experts of the second); the persistent
+        # GEMM grids then stay off `sm_margin` SMs so that the collective's kernels find room next to them. Measured on
+        # B200s it does not pay (2 ranks: 3.78 against 3.22 ms; 8 ranks: 5.37 against 5.16 ms per step): every half re-reads
+        # this rank's expert weights and the GEMMs lose the SMs they leave free. Off unless asked for.
+        import os
+        env = os.environ.get("B200MOE_EP_MICRO_BATCHES")
+        self.micro_batches = int(env) if env else (micro_batches or 1)
+        self.sm_margin = (sm_margin if sm_margin is not None else 16) if self.micro_batches > 1 else 0
         self._routed = self._shared = self._plan = None
+        self._plans = {}
         self.profile = False
         # quantise/route launches are the caller's; here: plan (visits + route map + pack), then (route map + permute +
         # FC1 + FC2 + combine) for the received tokens, the same for the shared experts, and the final combine
@@ -165,7 +176,7 @@ class ExpertParallelMoE:
         if self._routed is None or self._routed.cfg.max_tokens < n:
             if self._routed is not None:
                 self._routed.close()
-            self._routed = MoELayer(self.h, self.i, self.e_local, self.k, max(n, self.recv_capacity))
+            self._routed = MoELayer(self.h, self.i, self.e_local, self.k, max(n, self.recv_capacity), sm_margin=self.sm_margin)
         e = self.e_local
         self._routed.run(local_ids, weights, rows_q, rows_sf, w1q[:e], w1s[:e], w2q[:e], w2s[:e], out_rows,
                          **{k: (None if v is None else v[:e]) for k, v in kw.items()})
@@ -173,7 +184,7 @@ class ExpertParallelMoE:
     def _cuda_shared_rows(self, hq, hs, w1q, w1s, w2q, w2s, out_rows, kw):
         from .ops import MoELayer
         if self._shared is None:
-            self._shared = MoELayer(self.h, self.i, 0, 0, self.t, num_shared_experts=self.s)
+            self._shared = MoELayer(self.h, self.i, 0, 0, self.t, num_shared_experts=self.s, sm_margin=self.sm_margin)
         e = self.e_local
         self._shared.run(None, None, hq, hs, w1q[e:], w1s[e:], w2q[e:], w2s[e:], out_rows,
                          **{k: (None if v is None else v[e:]) for k, v in kw.items()})
@@ -189,7 +200,7 @@ class ExpertParallelMoE:
 
     def status(self) -> int:
         code = 0
-        for layer in (self._routed, self._shared, self._plan.layer if self._plan else None):
+        for layer in [self._routed, self._shared, self._plan.layer if self._plan else None] + [p.layer for p in self._plans.values()]:
             if layer is not None:
                 code = code or layer.status()
         return code
@@ -201,6 +212,8 @@ class ExpertParallelMoE:
         scale_gate, scale_out) for the same experts. Returns bf16 [T, H]."""
         dev = hq.device
         t = hq.shape[0]
+        if self.micro_batches > 1 and dev.type == "cuda" and t >= 2 * SEGMENT_ROWS:
+            return self._forward_pipelined(ids, weights, hq, hs, w1q, w1s, w2q, w2s, out, kw)
         marks = []
 
         def mark(name):
@@ -262,6 +275,91 @@ class ExpertParallelMoE:
             out = torch.empty((t, self.h), dtype=torch.bfloat16, device=dev)
         self._combine_rows(rows_all, row_of, w_rows, out)
         mark("combine")
+        if marks:
+            self._pending_marks = marks
+        return out
+
+    def _forward_pipelined(self, ids, weights, hq, hs, w1q, w1s, w2q, w2s, out, kw):
+        """The same steps on two token halves, interleaved on a compute stream (the caller's) and a communication
+        stream: plan(A), plan(B) | dispatch(A), dispatch(B) | experts(A) beside dispatch(B) | return(A) beside
+        experts(B) | return(B) | the two final combines. Every rank issues its collectives in the same order."""
+        dev = hq.device
+        t = hq.shape[0]
+        main = torch.cuda.current_stream(dev)
+        if getattr(self, "_comm", None) is None:
+            self._comm = torch.cuda.Stream(device=dev)
+        comm = self._comm
+        marks = []
+
+        def mark(name):
+            if self.profile:
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record()
+                marks.append((name, ev))
+
+        mark("start")
+        t0 = (t // 2 + SEGMENT_ROWS - 1) // SEGMENT_ROWS * SEGMENT_ROWS
+        bounds = [(0, t0), (t0, t)]
+        if out is None:
+            out = torch.empty((t, self.h), dtype=torch.bfloat16, device=dev)
+        mbs = []
+        for i, (lo, hi) in enumerate(bounds):          # plans and the (tiny) size exchanges of both halves first
+            planner = self._plans.get(i)
+            if planner is None or planner.layer.cfg.max_tokens < hi - lo:
+                planner = self._plans[i] = CudaPlanner(self.h, self.k, self.e_local, self.world, max(hi - lo, t0), bool(self.s), dev)
+            msg, seg_rows_t, row_of, w_rows = planner.plan(ids[lo:hi], weights[lo:hi], hq[lo:hi], hs[lo:hi])
+            seg_rows_t = seg_rows_t.to(torch.int64)
+            recv_rows_t = torch.empty_like(seg_rows_t)
+            dist.all_to_all_single(recv_rows_t, seg_rows_t, group=self.group)
+            mbs.append(dict(lo=lo, hi=hi, msg=msg, sizes=torch.cat([seg_rows_t, recv_rows_t]), row_of=row_of, w_rows=w_rows))
+        for mb in mbs:
+            sizes = mb["sizes"].tolist()
+            mb["send"], mb["recv"] = sizes[:self.world], sizes[self.world:]
+            mb["n_send"], mb["n_recv"] = sum(mb["send"]), sum(mb["recv"])
+            if mb["n_recv"] > self.recv_capacity:
+                raise RuntimeError(f"rank {self.rank} received {mb['n_recv']} rows, capacity is {self.recv_capacity}")
+            mb["rows_all"] = torch.empty((mb["n_send"] + (mb["hi"] - mb["lo"]) * (1 if self.s else 0), self.h), dtype=torch.bfloat16,
+                                         device=dev)
+        mark("plan+counts")
+        side = None
+        if self.s:                                        # shared experts: own tokens only, on a third stream
+            side = self._side_stream(dev)
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                for mb in mbs:
+                    lo, hi = mb["lo"], mb["hi"]
+                    mb["rows_all"].record_stream(side)
+                    self._shared_rows(hq[lo:hi], hs[lo:hi], w1q, w1s, w2q, w2s, mb["rows_all"][mb["n_send"]:], kw)
+        comm.wait_stream(main)
+        with torch.cuda.stream(comm):
+            for mb in mbs:
+                mb["got"] = exchange(mb["msg"][:mb["n_send"]], mb["send"], mb["recv"], self.group)
+                mb["got"].record_stream(main)
+                mb["ev_dispatch"] = torch.cuda.Event()
+                mb["ev_dispatch"].record(comm)
+        for mb in mbs:
+            main.wait_event(mb["ev_dispatch"])
+            mb["res"] = torch.empty((mb["n_recv"], self.h), dtype=torch.bfloat16, device=dev)
+            if mb["n_recv"]:
+                rows_q, rows_sf, ids_recv, w_recv = message_views(mb["got"], self.h, self.k)
+                self._expert_rows(rows_q, rows_sf, ids_recv, w_recv, w1q, w1s, w2q, w2s, mb["res"], kw)
+            ev = torch.cuda.Event()
+            ev.record(main)
+            with torch.cuda.stream(comm):
+                comm.wait_event(ev)
+                mb["res"].record_stream(comm)
+                mb["rows_all"].record_stream(comm)
+                dist.all_to_all_single(mb["rows_all"][:mb["n_send"]], mb["res"], output_split_sizes=mb["send"],
+                                       input_split_sizes=mb["recv"], group=self.group)
+                mb["ev_return"] = torch.cuda.Event()
+                mb["ev_return"].record(comm)
+        mark("experts(+exchanges)")
+        if side is not None:
+            main.wait_stream(side)
+        for mb in mbs:
+            main.wait_event(mb["ev_return"])
+            self._combine_rows(mb["rows_all"], mb["row_of"], mb["w_rows"], out[mb["lo"]:mb["hi"]])
+        mark("return+combine")
         if marks:
             self._pending_marks = marks
         return out

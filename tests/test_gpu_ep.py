@@ -18,7 +18,8 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, results):
+def _worker(rank, world, port, results, tokens=T, micro_batches=1):
+    T = tokens
     import torch.distributed as dist
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
@@ -34,12 +35,17 @@ def _worker(rank, world, port, results):
         mine = slice(rank * T, (rank + 1) * T)
         own = list(range(rank * e_local, (rank + 1) * e_local)) + list(range(E, E + S))
         dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
-        ep = ExpertParallelMoE(H, I, E, K, T, num_shared_experts=S)
+        ep = ExpertParallelMoE(H, I, E, K, T, num_shared_experts=S, micro_batches=micro_batches)
+        assert ep.micro_batches == micro_batches
         ids, scores = p["topk_ids"]
         out = ep.forward(dev(ids[mine]), dev(scores[mine]), dev(p["hidden_states"][mine]), dev(p["hidden_states_scale"][mine]),
                          dev(p["gemm1_weights"][own]), dev(p["gemm1_weights_scale"][own]), dev(p["gemm2_weights"][own]),
                          dev(p["gemm2_weights_scale"][own]), scale_up=dev(p["output1_scale_scalar"][own]),
                          scale_gate=dev(p["output1_scale_gate_scalar"][own]), scale_out=dev(p["output2_scale_scalar"][own]))
+        out = ep.forward(dev(ids[mine]), dev(scores[mine]), dev(p["hidden_states"][mine]), dev(p["hidden_states_scale"][mine]),
+                         dev(p["gemm1_weights"][own]), dev(p["gemm1_weights_scale"][own]), dev(p["gemm2_weights"][own]),
+                         dev(p["gemm2_weights_scale"][own]), scale_up=dev(p["output1_scale_scalar"][own]),
+                         scale_gate=dev(p["output1_scale_gate_scalar"][own]), scale_out=dev(p["output2_scale_scalar"][own]))   # buffers reused
         torch.cuda.synchronize()
         assert ep.status() == 0
         r = assert_layer_parity(out.float().cpu().numpy(), o.moe_expected(p)[mine], f"rank {rank}", extra_bf16_roundings=world)
@@ -54,4 +60,14 @@ def test_expert_parallel_two_gpus():
     with mp.Manager() as mgr:
         results = mgr.dict()
         mp.spawn(_worker, args=(2, _free_port(), results), nprocs=2, join=True)
+        assert sorted(results.keys()) == [0, 1]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_expert_parallel_two_gpus_pipelined():
+    """Two token halves pipelined over a compute and a communication stream (optional form, off by default)."""
+    import torch.multiprocessing as mp
+    with mp.Manager() as mgr:
+        results = mgr.dict()
+        mp.spawn(_worker, args=(2, _free_port(), results, 384, 2), nprocs=2, join=True)
         assert sorted(results.keys()) == [0, 1]
