@@ -258,12 +258,14 @@ def run_gpu(args, wl):
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed(fn, steps, warmup, finish=None):
+    def timed(fn, steps, warmup, finish=None, on_start=None):
         for _ in range(warmup):
             fn()
         if finish:
             finish()
         barrier()
+        if on_start:
+            on_start()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for _ in range(steps):
@@ -321,9 +323,7 @@ def run_gpu(args, wl):
         cur.wait_stream(s_out)
 
     sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
-    ms = timed(resident, args.steps, args.warmup)
+    ms = timed(resident, args.steps, args.warmup, on_start=sampler.start if rank == 0 else None)   # clocks of the timed region only
     clocks = sampler.stop() if rank == 0 else None
     ms_e2e = timed(end_to_end, args.steps, max(1, args.warmup), finish=e2e_finish)
     # Decode sizes: the same resident step replayed from a CUDA graph (one host call per step instead of ~10 launches;
