@@ -304,7 +304,13 @@ int b200moe_router_logits(const void* x, const void* w, int64_t T, int32_t H, in
   if (T && (!x || !w || !logits)) return fail(753, "router_logits: null pointer");
   if (((uintptr_t)x | (uintptr_t)w) & 15) return fail(754, "router_logits: operands must be 16-byte aligned");
   // tensor-core path: whole gate matrix as one B tile (E <= 256), K in 64-element stages, 16-byte aligned rows
-  if (E <= 256 && H % 64 == 0 && E % 8 == 0)
+  static const int forced = [] {
+    const char* v = getenv("B200MOE_ROUTER_PATH");      // timing experiments only: 1 = tensor cores, 2 = SIMT, 3 = decode kernel
+    return v ? atoi(v) : 0;
+  }();
+  if ((forced == 0 || forced == 3) && T <= 16)      // decode sizes: stream the gate matrix over the whole device
+    return cuda_fail(launch_router_logits_small(x, w, T, H, E, logits, (cudaStream_t)stream), "router_logits");
+  if (forced != 2 && E <= 256 && H % 64 == 0 && E % 8 == 0)
     return cuda_fail(launch_router_logits_tc(x, w, T, H, E, logits, nullptr, (cudaStream_t)stream), "router_logits");
   return cuda_fail(launch_router_logits(x, w, T, H, E, logits, (cudaStream_t)stream), "router_logits");
 }

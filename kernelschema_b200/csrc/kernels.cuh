@@ -81,6 +81,7 @@ int launch_route_topk(const float* logits, const float* bias, int64_t T, int E, 
                       cudaStream_t st);
 int launch_router_logits(const void* x, const void* w, int64_t T, int H, int E, float* logits, cudaStream_t st);
 int launch_router_logits_tc(const void* x, const void* w, int64_t T, int H, int E, float* logits, int32_t* status, cudaStream_t st);
+int launch_router_logits_small(const void* x, const void* w, int64_t T, int H, int E, float* logits, cudaStream_t st);   // T <= 16
 int launch_route_map(const int32_t* ids, const float* scores, int64_t id_stride, int64_t T, int K, int S, int E, int expert_offset,
                      RouteMapBuffers b, cudaStream_t st);
 int launch_route_map_static(const int32_t* ids, const float* scores, int64_t T, int K, int S, int E, int expert_offset,

@@ -106,6 +106,74 @@ __global__ void __launch_bounds__(256) k_router_logits(const __nv_bfloat16* __re
   }
 }
 
+// ----------------------------------------------------------------------------- decode-size router logits (T <= 16)
+// With a handful of tokens the product is a stream over the gate matrix (E x H bf16, a few MB): one 128-token tensor-core
+// tile walks K serially in a single CTA (34 us at H = 7168, E = 256 against 6 us here at T = 1, 12 us at T = 8), so here the matrix is spread over the device instead: a block
+// = 2 experts x 4 quarters of H (one warp each), every warp reads its part of the weight row once and keeps one fp32
+// accumulator per token; the four partial sums of an expert are added in a fixed order (reproducible).
+template <int TT>
+__global__ void __launch_bounds__(256) k_router_logits_small(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                                                             int T, int H, int E, float* __restrict__ logits) {
+  __shared__ float part_sum[4][2][TT];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int el = warp >> 2, part = warp & 3;
+  const int e = blockIdx.x * 2 + el;
+  pdl_trigger();
+  pdl_wait();
+  float acc[TT];
+#pragma unroll
+  for (int t = 0; t < TT; ++t) acc[t] = 0.f;
+  if (e < E) {
+    const int vecs = H >> 3;
+    const uint4* wr = reinterpret_cast<const uint4*>(w + (int64_t)e * H);
+    const uint4* xr = reinterpret_cast<const uint4*>(x);
+    for (int c = part * 32 + lane; c < vecs; c += 128) {
+      const uint4 wv = __ldg(wr + c);
+      const uint32_t* ww = reinterpret_cast<const uint32_t*>(&wv);
+      float wf[8];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        wf[2 * i] = __uint_as_float(ww[i] << 16);
+        wf[2 * i + 1] = __uint_as_float(ww[i] & 0xFFFF0000u);
+      }
+#pragma unroll
+      for (int t = 0; t < TT; ++t) {
+        if (t < T) {
+          const uint4 xv = __ldg(xr + (int64_t)t * vecs + c);
+          const uint32_t* xw = reinterpret_cast<const uint32_t*>(&xv);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            acc[t] = fmaf(__uint_as_float(xw[i] << 16), wf[2 * i], acc[t]);
+            acc[t] = fmaf(__uint_as_float(xw[i] & 0xFFFF0000u), wf[2 * i + 1], acc[t]);
+          }
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int t = 0; t < TT; ++t) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) acc[t] += __shfl_xor_sync(0xFFFFFFFFu, acc[t], off);
+    if (lane == 0) part_sum[part][el][t] = acc[t];
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < 2 * TT; i += blockDim.x) {
+    const int ee = i / TT, t = i % TT;
+    const int eg = blockIdx.x * 2 + ee;
+    if (t < T && eg < E) logits[(int64_t)t * E + eg] = ((part_sum[0][ee][t] + part_sum[1][ee][t]) + part_sum[2][ee][t]) + part_sum[3][ee][t];
+  }
+}
+
+int launch_router_logits_small(const void* x, const void* w, int64_t T, int H, int E, float* logits, cudaStream_t st) {
+  if (T == 0) return 0;
+  const dim3 grid((unsigned)((E + 1) / 2));
+  if (T <= 8)
+    return (int)launch_chain(k_router_logits_small<8>, grid, dim3(256), 0, st, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (int)T, H, E,
+                             logits);
+  return (int)launch_chain(k_router_logits_small<16>, grid, dim3(256), 0, st, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (int)T, H, E,
+                           logits);
+}
+
 // ----------------------------------------------------------------------------- tensor-core router logits
 // Same product on the 5th-gen tensor cores: 128-token tiles, the whole gate matrix (E <= 256 rows) as the B tile,
 // K staged 64 bf16 (128 B rows, 128-byte swizzle) at a time by TMA, tcgen05.mma kind::f16 into double-buffered TMEM

@@ -89,9 +89,10 @@ def test_router_random_with_bias_and_ties(t, e, k):
     assert ulp.max() <= 1
 
 
-@pytest.mark.parametrize("t,h,e", [(300, 2048, 130), (300, 7168, 256), (1000, 2048, 128), (129, 1024, 8), (5, 256, 72)])
+@pytest.mark.parametrize("t,h,e", [(300, 2048, 130), (300, 7168, 256), (1000, 2048, 128), (129, 1024, 8), (5, 256, 72),
+                                   (1, 7168, 256), (8, 2048, 128), (9, 2048, 127), (16, 7168, 256), (17, 2048, 128)])
 def test_router_logits(t, h, e):
-    """e=130 takes the SIMT kernel, the others the tcgen05 bf16 kernel."""
+    """Up to 16 tokens take the decode kernel; above, e=130 takes the SIMT kernel, the others the tcgen05 bf16 kernel."""
     import kernelschema_b200 as ks
     x = torch.randn(t, h).to(torch.bfloat16)
     w = (torch.randn(e, h) * 0.02).to(torch.bfloat16)
