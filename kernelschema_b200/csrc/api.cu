@@ -164,8 +164,11 @@ int run_impl(b200moe_layer* h, const b200moe_args* a, cudaStream_t st, cudaEvent
                         a->local_expert_offset, h->rm, st);
   if (rc) return cuda_fail(rc, "route map");
   mark(1);
+  // rows this call can occupy at most (every routing of T tokens fits), not the layer's capacity: sizes the permute grid
+  int64_t call_rows = ((int64_t)T * h->kk / 128 + h->etot + 1) * 128;
+  if (call_rows > h->row_capacity) call_rows = h->row_capacity;
   rc = launch_gather_rows(a->hidden_states, a->hidden_states_scale, a->hidden_states_scale_layout == 1, a->hidden_states_stride,
-                          a->hidden_states_scale_stride, h->rm.tok_of_row, h->rm.tile_rows, h->rm.totals, c.hidden, h->row_capacity, h->a_q, h->a_sf, st);
+                          a->hidden_states_scale_stride, h->rm.tok_of_row, h->rm.tile_rows, h->rm.totals, c.hidden, call_rows, h->a_q, h->a_sf, st);
   if (rc) return cuda_fail(rc, "permute");
   mark(2);
   if (h->b1_ptr != a->gemm1_weights || h->s1_ptr != a->gemm1_weights_scale) {
