@@ -83,3 +83,14 @@ def test_pybind_shim_loads_and_maps_errors(lib):
         shim.create(100, 256, 4, 2, 0, 8, 0)
     with pytest.raises(ValueError):
         shim.run(0, 1, *([0] * 21))
+
+
+def test_dense_entry_refuses_bad_shapes_without_a_device(lib):
+    """Argument checks of the bf16 x NVFP4 GEMM entry run before any CUDA call."""
+    import ctypes as C
+    assert lib.b200moe_gemm_bf16_nvfp4(None, 128, None, None, None, None, 8, 128, 100, 128, None, 0, None, None) == 765   # K % 256
+    assert b"K % 256" in lib.b200moe_last_error()
+    assert lib.b200moe_gemm_bf16_nvfp4(None, 256, None, None, None, None, 8, 100, 256, 128, None, 0, None, None) == 765   # N % 128
+    assert lib.b200moe_gemm_bf16_nvfp4(None, 256, None, None, None, None, 8, 128, 256, 128, None, 0, None, None) == 766   # null pointers
+    assert lib.b200moe_gemm_bf16_nvfp4(None, 256, None, None, None, None, 0, 128, 256, 128, None, 0, None, None) == 0     # M = 0: nothing to do
+    assert lib.b200moe_gemm_bf16_nvfp4_workspace_bytes(8, 100, 256) == 0
