@@ -9,8 +9,14 @@ with pinned HOST buffers (host->device copy of the tokens and device->host copy 
 region). With --gpus N > 1 (launched under torchrun) experts are sharded over the ranks and tokens travel by
 NCCL all-to-all (weak scaling: every rank brings its own T tokens).
 
-`--impl reference` times the CPU restatement of the reference operator's fp32 dequantise-then-matmul path
-(oracle/) on the host cores, on a bounded sample of the same geometry.
+`--impl reference` times the reference operator's own fp32 dequantise-then-matmul path (`reference.py::Model.forward`
+of the staged problem files under oracle/_ref, built by oracle/build_ref.py; the numpy restatement in oracle/ when the
+staging is absent) on the host cores, on a bounded sample of the same geometry.
+
+Besides the headline workload the default run adds short sub-records (`sub`): the Qwen3-30B layer, the dense GEMM
+sizes, decode batches of the headline geometry, and an A/B against the reference's own Blackwell kernel run through
+its unmodified host; with N > 1 ranks: decode batches, a uniform-routing step and a parity record of the
+expert-parallel result against the single-GPU layer. `--no-sub` leaves them out.
 """
 from __future__ import annotations
 
@@ -34,11 +40,13 @@ WORKLOADS = {
     "qwen3": dict(h=2048, i=768, e=128, k=8, s=0, t=16384, zipf=0.0, label="qwen3_30b_a3b_moe_layer_T16384_E128_top8"),
     "c1": dict(h=1024, i=512, e=8, k=2, s=0, t=256, zipf=0.0, label="small_moe_layer_T256_E8_top2"),
 }
-ACT_GLOBAL_SCALE = 2.0 ** -9        # static (calibrated) activation global scale: amax 6 -> 6/(6*448) ~ 2^-8.8, as a power of two
+# static (calibrated) activation global scale amax / (6 * 448) for N(0, 1) activations whose block peaks reach ~5.7
+ACT_GLOBAL_SCALE = 5.7 / (6.0 * 448.0)
 FP4_NOMINAL_TFLOPS = 9000.0
-# dram__bytes_read.sum + dram__bytes_write.sum of one FC1 launch, from the ncu captures summarised under profiles/
-# (workload -> bytes); null for workloads that were not captured.
+# dram__bytes_read.sum + dram__bytes_write.sum of one FC1 launch, from the ncu captures summarised in
+# profiles/bench_dsv3_T8192_launch_list.md and profiles/layer_kernels_qwen3_T16384_ncu_full.md (workload -> bytes).
 FC1_DRAM_TRAFFIC = {"dsv3": 4966850048 + 79877632, "qwen3": 386940416 + 49309952}
+REF_DIR = os.path.join(ROOT, "oracle", "_ref")
 
 
 def peaks():
@@ -154,33 +162,50 @@ def build_layer(wl, rank, world, device, global_scales=True):
                 gate_w=gate_w, bias=bias, e_local=e_local)
 
 
-def make_step(wl, L, world, device):
-    """Returns step(x_bf16_device) -> out_bf16_device, the launch count per step, and the route statistics."""
+def make_step(wl, L, world, device, tokens=None):
+    """Returns step(x_bf16_device) -> (out_bf16_device, ids), the object that owns the library state, and the launch
+    count per step. Every buffer of the step is allocated here, once."""
     import torch
     import kernelschema_b200 as ks
-    h, i, k, s, t = wl["h"], wl["i"], wl["k"], wl["s"], wl["t"]
+    h, i, k, s = wl["h"], wl["i"], wl["k"], wl["s"]
+    t = tokens or wl["t"]
+    e = wl["e"]
+    hq = torch.empty((t, h // 2), dtype=torch.uint8, device=device)
+    hs = torch.empty((t, h // 16), dtype=torch.uint8, device=device)
+    logits = torch.empty((t, e), dtype=torch.float32, device=device)
+    ids = torch.empty((t, k), dtype=torch.int32, device=device)
+    w = torch.empty((t, k), dtype=torch.float32, device=device)
+    out_own = torch.empty((t, h), dtype=torch.bfloat16, device=device)
+
+    def front(x):
+        n = x.shape[0]
+        ks.nvfp4_quantize(x, ACT_GLOBAL_SCALE, out=(hq[:n], hs[:n]))
+        ks.route_topk(ks.router_logits(x, L["gate_w"], out=logits[:n]), k, L["bias"], out=(ids[:n], w[:n]))
+        return hq[:n], hs[:n], ids[:n], w[:n]
+
     if world == 1:
-        layer = ks.MoELayer(h, i, L["e_local"], k, t, num_shared_experts=s, tile_n=int(os.environ.get("B200MOE_TILE_N", "0")))
-        out = torch.empty((t, h), dtype=torch.bfloat16, device=device)
+        layer = ks.MoELayer(h, i, L["e_local"], k, t, num_shared_experts=s)
 
-        def step(x, out=out):
-            hq, hs = ks.nvfp4_quantize(x, ACT_GLOBAL_SCALE)
-            ids, w = ks.route_topk(ks.router_logits(x, L["gate_w"]), k, L["bias"])
-            layer.run(ids, w, hq, hs.view(torch.uint8), L["w1q"], L["w1s"], L["w2q"], L["w2s"], out, scale_up=L["scale_fc1"],
+        def step(x, out=None):
+            out = out_own[:x.shape[0]] if out is None else out
+            q, sf, ids_, w_ = front(x)
+            layer.run(ids_, w_, q, sf, L["w1q"], L["w1s"], L["w2q"], L["w2s"], out, scale_up=L["scale_fc1"],
                       scale_gate=L["scale_fc1"], scale_out=L["scale_fc2"])
-            return out, ids
+            return out, ids_
 
+        step.front = front
         return step, layer, 10
     from kernelschema_b200.ep import ExpertParallelMoE
-    ep = ExpertParallelMoE(h, i, wl["e"], k, t, num_shared_experts=s)
+    ep = ExpertParallelMoE(h, i, e, k, t, num_shared_experts=s)
 
     def step(x, out=None):
-        hq, hs = ks.nvfp4_quantize(x, ACT_GLOBAL_SCALE)
-        ids, w = ks.route_topk(ks.router_logits(x, L["gate_w"]), k, L["bias"])
-        out = ep.forward(ids, w, hq, hs.view(torch.uint8), L["w1q"], L["w1s"], L["w2q"], L["w2s"], out=out,
+        out = out_own[:x.shape[0]] if out is None else out
+        q, sf, ids_, w_ = front(x)
+        out = ep.forward(ids_, w_, q, sf, L["w1q"], L["w1s"], L["w2q"], L["w2s"], out=out,
                          scale_up=L["scale_fc1"], scale_gate=L["scale_fc1"], scale_out=L["scale_fc2"])
-        return out, ids
+        return out, ids_
 
+    step.front = front
     return step, ep, ep.launches_per_step + 3
 
 
@@ -189,29 +214,63 @@ def layer_flops(wl, valid_routes, tokens):
 
 
 # --------------------------------------------------------------------------------------------- CPU arm
-def cpu_sample_case(wl):
-    """Bounded sample of the workload for the host cores: same hidden / intermediate sizes, 8 routed experts
-    (+ the shared one), 256 tokens, top-2."""
-    sys.path.insert(0, os.path.join(ROOT, "tests"))
-    from helpers import make_moe_case
+def _staged(*parts):
+    return os.path.join(REF_DIR, *parts)
+
+
+def reference_staged():
+    return all(os.path.exists(_staged("problem", n)) for n in ("reference.py", "input.py"))
+
+
+def _load_module(name, path):
+    import importlib.util
+    spec = importlib.util.spec_from_file_location(name, path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def cpu_sample_shape(wl):
+    """Bounded sample of the workload for the host cores: same hidden / intermediate sizes, 8 routed experts, 256 tokens,
+    top-2 (the reference has no shared expert and reads no global scales, so the sample has neither)."""
     e, k, t = (8, 2, 256) if wl["e"] >= 8 else (wl["e"], wl["k"], wl["t"])
-    p = make_moe_case(0, t, wl["h"], wl["i"], e, k, shared=wl["s"], global_scales=True)
-    valid = int((p["topk_ids"][0] >= 0).sum())
-    flops = 6.0 * valid * wl["i"] * wl["h"] + 6.0 * t * wl["s"] * wl["i"] * wl["h"]
-    desc = f"H={wl['h']} I={wl['i']} experts={e}+{wl['s']} shared, T={t}, top-{k}: {flops / 1e9:.1f} GFLOP per pass"
-    return p, flops, t, desc
+    return dict(hidden=wl["h"], intermediate=wl["i"], local_experts=e, tokens=t, topk=k)
 
 
 def time_cpu(wl, steps, warmup):
-    from oracle import nvfp4_oracle as o
-    p, flops, t, desc = cpu_sample_case(wl)
+    """Times the reference's own CPU path on the sample: `reference.py::Model.forward` of the staged problem files with
+    inputs from its own generator (kind "reference"); the numpy restatement on the equivalent seeded case when the
+    staging is absent (kind "port")."""
+    shape = cpu_sample_shape(wl)
+    t = shape["tokens"]
+    if reference_staged():
+        import torch
+        ref = _load_module("staged_reference_cpu", _staged("problem", "reference.py"))
+        inp = _load_module("staged_input_cpu", _staged("problem", "input.py"))
+        torch.manual_seed(0)
+        kw = inp._make_inputs(**shape, device="cpu")
+        model = ref.Model()
+        fn = lambda: model(**kw)
+        valid = int((kw["topk_ids"][0] >= 0).sum())
+        kind, cores = "reference", torch.get_num_threads()
+    else:
+        sys.path.insert(0, os.path.join(ROOT, "tests"))
+        from helpers import make_moe_case
+        from oracle import nvfp4_oracle as o
+        p = make_moe_case(0, t, wl["h"], wl["i"], shape["local_experts"], shape["topk"])
+        fn = lambda: o.moe_expected(p)
+        valid = int((p["topk_ids"][0] >= 0).sum())
+        kind, cores = "port", os.cpu_count()
+    flops = 6.0 * valid * wl["i"] * wl["h"]
+    desc = (f"H={wl['h']} I={wl['i']} experts={shape['local_experts']} T={t} top-{shape['topk']}, no shared expert: "
+            f"{flops / 1e9:.1f} GFLOP per pass")
     for _ in range(warmup):
-        o.moe_expected(p)
+        fn()
     t0 = time.perf_counter()
     for _ in range(steps):
-        o.moe_expected(p)
+        fn()
     dt = (time.perf_counter() - t0) / steps
-    return dict(tflops=flops / dt / 1e12, tokens_per_s=t / dt, seconds=dt, sample=desc, cores=os.cpu_count())
+    return dict(tflops=flops / dt / 1e12, tokens_per_s=t / dt, seconds=dt, sample=desc, cores=cores, kind=kind)
 
 
 def run_reference(args, wl):
@@ -223,12 +282,230 @@ def run_reference(args, wl):
                 steps=args.steps, warmup=args.warmup, ms_per_step=r["seconds"] * 1e3, higher_is_better=True, scaling="weak",
                 vs_baseline=None, dtype="f32", data="synthetic", tokens_per_s=r["tokens_per_s"],
                 config=dict(workload=wl["label"], sample=r["sample"]),
-                cpu_baseline=dict(value=r["tflops"], unit="TFLOP/s", cores=r["cores"], kind="port", sample=r["sample"]),
+                cpu_baseline=dict(value=r["tflops"], unit="TFLOP/s", cores=r["cores"], kind=r["kind"], sample=r["sample"]),
                 e2e=dict(value=r["tflops"], unit="TFLOP/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0))
     print(json.dumps(line))
 
 
 # --------------------------------------------------------------------------------------------- GPU arm
+def _timed_loop(fn, steps, warmup):
+    """ms per call of `fn` with CUDA events on the current stream, after warm-up, synchronised on both sides."""
+    import torch
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
+def fp4_peaks(pk):
+    """The three FP4 tensor denominators: 4 x the measured bf16 figures (nominal FP4 : bf16 ratio) and the nominal 9 PFLOP/s."""
+    return dict(burst=4.0 * pk["bf16"], sustained=4.0 * pk["bf16_sustained"], nominal=FP4_NOMINAL_TFLOPS)
+
+
+def tensor_roofline(achieved, pk, clocks, **extra):
+    """`frac` uses the burst peak when the sampled SM clock stayed at >= 95 % of its maximum, the sustained one otherwise."""
+    f = fp4_peaks(pk)
+    sm, mx = (clocks or {}).get("sm_mhz"), (clocks or {}).get("sm_max_mhz")
+    which = "burst" if (sm and mx and sm >= 0.95 * mx) else "sustained"
+    return dict(bound="tensor", achieved=achieved, peak=f[which], unit="TFLOP/s", frac=achieved / f[which],
+                frac_burst=achieved / f["burst"], frac_sustained=achieved / f["sustained"], frac_nominal=achieved / f["nominal"],
+                peak_burst=f["burst"], peak_sustained=f["sustained"], peak_nominal=f["nominal"],
+                peak_source=f"4 x bf16_tflops ({which}) of {pk['source']} MEASURED_PEAKS: FP4 : bf16 nominal ratio; chosen by the sampled SM clock",
+                **extra)
+
+
+def sub_layer_record(name, tokens, args, device, pk, L=None, zipf=None, steps=10):
+    """Short resident-input timing of another workload (or of the headline geometry at another batch) for `sub`."""
+    import torch
+    import kernelschema_b200 as ks
+    wl = dict(WORKLOADS[name])
+    if tokens:
+        wl["t"] = tokens
+    if zipf is not None:
+        wl["zipf"] = zipf
+    own_L = L is None
+    if own_L:
+        L = build_layer(wl, 0, 1, device)
+    step, layer, _ = make_step(wl, L, 1, device)
+    t, h = wl["t"], wl["h"]
+    x = torch.randn((t, h), device=device, generator=torch.Generator(device=device).manual_seed(4242)).to(torch.bfloat16)
+    state = {}
+
+    def fn():
+        state["out"], state["ids"] = step(x)
+
+    ms = _timed_loop(fn, steps, 3)
+    valid = float((state["ids"] >= 0).sum())
+    flops = layer_flops(wl, valid, t)
+    counts = layer.workspace()["counts"].cpu()
+    touched = int((counts > 0).sum())
+    weight_bytes = touched * 3 * wl["i"] * h * 9 / 16
+    act_bytes = t * h * 2 * 2 + t * h * 9 / 16
+    rec = dict(workload=wl["label"], tokens=t, ms_per_step=ms, tflops=flops / (ms * 1e-3) / 1e12, tokens_per_s=t / (ms * 1e-3),
+               frac_of_nominal_fp4=flops / (ms * 1e-3) / 1e12 / FP4_NOMINAL_TFLOPS, experts_touched=touched,
+               hbm_algorithmic_gbs=(weight_bytes + act_bytes) / (ms * 1e-3) / 1e9, device_status=layer.status())
+    rec["hbm_frac_of_measured"] = rec["hbm_algorithmic_gbs"] / pk["hbm_gbs"]
+    if t <= 2048:        # decode sizes: also the step replayed from a CUDA graph
+        side = torch.cuda.Stream(device)
+        side.wait_stream(torch.cuda.current_stream(device))
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                step(x)
+        torch.cuda.current_stream(device).wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            step(x)
+        gms = _timed_loop(graph.replay, steps, 3)
+        rec["graph_replay_ms_per_step"] = gms
+        rec["graph_replay_hbm_frac_of_measured"] = (weight_bytes + act_bytes) / (gms * 1e-3) / 1e9 / pk["hbm_gbs"]
+    layer.close()
+    return rec
+
+
+def sub_dense_records(pk, steps=10):
+    """The dense NVFP4 GEMM sizes of the benchmark (A quantised on the device with a global scale, B pre-quantised)."""
+    import torch
+    import kernelschema_b200 as ks
+    out = []
+    for m, n, k in ((2048, 2048, 2048), (4096, 4096, 4096), (8192, 8192, 8192), (16384, 7168, 2048)):
+        a = torch.randn(m, k, device="cuda").to(torch.bfloat16)
+        b = (torch.randn(n, k, device="cuda") * 0.02).to(torch.bfloat16)
+        gs_a, gs_b = float(a.float().abs().max()) / 2688.0, float(b.float().abs().max()) / 2688.0
+        bq, bsf = ks.nvfp4_quantize(b, gs_b, tiled_scales=True)
+        aq = torch.empty((m, k // 2), dtype=torch.uint8, device="cuda")
+        asf = torch.zeros(((m + 127) // 128, k // 64, 32, 16), dtype=torch.uint8, device="cuda")
+        y = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+        status = torch.zeros(4, dtype=torch.int32, device="cuda")
+        ms_q = _timed_loop(lambda: ks.nvfp4_quantize(a, gs_a, tiled_scales=True, out=(aq, asf)), steps, 3)
+        ms = _timed_loop(lambda: ks.mm_nvfp4(aq, asf, bq, bsf, alpha=gs_a * gs_b, out=y, status=status), steps, 3)
+        tf = 2.0 * m * n * k / (ms * 1e-3) / 1e12
+        f = fp4_peaks(pk)
+        out.append(dict(shape=[m, n, k], ms_gemm=ms, ms_quantise_a=ms_q, tflops=tf, frac_burst=tf / f["burst"],
+                        frac_sustained=tf / f["sustained"], frac_nominal=tf / f["nominal"],
+                        quantiser_gbs=m * k * 2.5625 / (ms_q * 1e-3) / 1e9, quantiser_hbm_frac_of_measured=m * k * 2.5625 / (ms_q * 1e-3) / 1e9 / pk["hbm_gbs"],
+                        device_status=int(status[0])))
+    return out
+
+
+def sub_reference_kernel(steps=10):
+    """The reference's own Blackwell kernel through its UNMODIFIED host (candidate/solution.py::Model: its selector, its graph
+    replay), staged under oracle/_ref by oracle/build_ref.py, against this library's drop-in Model on the same device
+    inputs, made by the reference's own generator: its fixed shapes 0, 1, 2 (T = 1, 32, 128), 6 (Qwen3-30B, T = 8192) and
+    the routed part of the DeepSeek-V3 layer (H 7168, I 2048, E 256, top-8, T = 8192, skewed routing)."""
+    import torch
+    need = [_staged("candidate", "solution.py"), _staged("candidate", "nvfp4_moe.cu"), _staged("problem", "input.py"),
+            _staged("problem", "shape_cases.json")]
+    if not all(os.path.exists(p) for p in need):
+        return dict(unavailable="oracle/_ref staging absent: python oracle/build_ref.py needs the reference checkout")
+    os.environ["TORCH_EXTENSIONS_DIR"] = _staged("cache")      # where build_ref.py left the kernel prebuilt under the host's own cache name
+    try:
+        inp = _load_module("staged_input_gpu", _staged("problem", "input.py"))
+        cand = _load_module("staged_candidate", _staged("candidate", "solution.py"))
+        from kernelschema_b200.solution import Model as Mine
+        with open(_staged("problem", "shape_cases.json")) as f:
+            cases = json.load(f)
+    except Exception as exc:
+        return dict(unavailable=f"reference host does not load here: {exc!r}"[:400])
+    todo = [(f"shape_{i}", cases[str(i)]["input_kwargs"]) for i in (0, 1, 2, 6)]
+    todo.append(("dsv3_routed_T8192", dict(tokens=8192, hidden=7168, intermediate=2048, local_experts=256, topk=8, routing="skewed")))
+    ref_model, my_model = cand.Model(), Mine()
+    rows = {}
+    for name, kw_shape in todo:
+        try:
+            torch.manual_seed(2026101501)
+            kw = inp._make_inputs(**kw_shape)
+            out_ref = kw["output"]
+            out_mine = inp.guarded(tuple(out_ref.shape), out_ref.dtype, out_ref.device)
+            kw_mine = dict(kw, output=out_mine)
+            t, h = out_ref.shape
+            flops = 6.0 * float((kw["topk_ids"][0] >= 0).sum()) * kw["intermediate_size"] * h
+            rec = dict(tokens=t, hidden=h, intermediate=kw["intermediate_size"], experts=kw["num_experts"], gflop=flops / 1e9)
+            try:
+                ms_ref = _timed_loop(lambda: ref_model(**kw), steps, 4)          # its 2nd identical call captures its graph
+                rec["reference_kernel_ms"] = ms_ref
+            except Exception as exc:
+                rec["reference_kernel_error"] = repr(exc)[:300]
+                ms_ref = None
+            ms_mine = _timed_loop(lambda: my_model(**kw_mine), steps, 4)
+            rec["this_library_ms"] = ms_mine
+            g = torch.cuda.CUDAGraph()
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                my_model(**kw_mine)
+            torch.cuda.current_stream().wait_stream(side)
+            with torch.cuda.graph(g):
+                my_model(**kw_mine)
+            rec["this_library_graph_replay_ms"] = _timed_loop(g.replay, steps, 3)
+            if ms_ref:
+                rec["speedup_over_reference_kernel"] = ms_ref / ms_mine
+                d = out_ref.float() - out_mine.float()
+                rec["rel_l2_between"] = float(d.norm() / out_ref.float().norm().clamp_min(1e-30))
+                rec["bf16_identical_fraction"] = float((d == 0).float().mean())
+                rec["output_rms"] = [float(out_ref.float().pow(2).mean().sqrt()), float(out_mine.float().pow(2).mean().sqrt())]
+            rows[name] = rec
+            del kw, kw_mine
+            torch.cuda.empty_cache()
+        except Exception as exc:
+            rows[name] = dict(error=repr(exc)[:300])
+    return dict(host="candidate/solution.py::Model of the reference, unmodified (own selector, graph replay on)", cases=rows)
+
+
+def ep_parity_record(wl, L, step, device, world, rank):
+    """Expert-parallel result of this rank's tokens against the single-GPU layer holding ALL experts (gathered over the
+    ranks), by the rules of the parity tests; the expert-parallel path rounds one bf16 partial row per visited rank."""
+    import torch
+    import torch.distributed as dist
+    import kernelschema_b200 as ks
+    t, h, k, s = wl["t"], wl["h"], wl["k"], wl["s"]
+    e_local = L["e_local"]
+    x = torch.randn((t, h), device=device, generator=torch.Generator(device=device).manual_seed(9000 + rank)).to(torch.bfloat16)
+    out_ep, _ = step(x)
+    out_ep = out_ep.clone()
+
+    def gather(name, per_expert=True):
+        mine = L[name][:e_local].contiguous()
+        parts = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(parts, mine)
+        return torch.cat(parts + [L[name][e_local:]], 0).contiguous()
+
+    w1q, w1s, w2q, w2s = gather("w1q"), gather("w1s"), gather("w2q"), gather("w2s")
+    sc1, sc2 = gather("scale_fc1"), gather("scale_fc2")
+    layer = ks.MoELayer(h, wl["i"], wl["e"], k, t, num_shared_experts=s)
+    q, sf, ids, w = step.front(x)
+    ref = torch.empty((t, h), dtype=torch.bfloat16, device=device)
+    layer.run(ids, w, q, sf, w1q, w1s, w2q, w2s, ref, scale_up=sc1, scale_gate=sc1, scale_out=sc2)
+    torch.cuda.synchronize()
+    status = layer.status()
+    layer.close()
+    got, exp = out_ep.float(), ref.float()
+    diff = (got - exp).abs()
+    rms = float(exp.pow(2).mean().sqrt())
+    peak = float(exp.abs().max())
+    import math
+    slack = world * 2.0 ** (math.floor(math.log2(max(peak, 1e-30))) - 7)       # one bf16 step of the largest output per visited rank
+    rec = dict(rel_l2=float((got - exp).norm() / exp.norm().clamp_min(1e-30)), max_abs_over_rms=float(diff.max()) / max(rms, 1e-30),
+               mismatch=float((diff > 0.01 + 0.05 * got.abs()).float().mean()), single_gpu_status=status)
+    ok = (rec["mismatch"] <= 1e-3 and rec["rel_l2"] <= 1e-2 and float(diff.max()) <= 2e-2 * rms + slack and status == 0
+          and bool(torch.isfinite(got).all()))
+    flag = torch.tensor([0 if ok else 1], device=device)
+    worst = torch.tensor([rec["rel_l2"], rec["max_abs_over_rms"], rec["mismatch"]], device=device)
+    dist.all_reduce(flag)
+    dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+    rec = dict(rel_l2=float(worst[0]), max_abs_over_rms=float(worst[1]), mismatch=float(worst[2]), ranks_failed=int(flag.item()),
+               passed=int(flag.item()) == 0, against="single-GPU layer with all experts, this rank's tokens; worst over ranks",
+               rule="mismatch <= 1e-3, rel_l2 <= 1e-2, max_abs <= 2e-2 rms + world bf16 steps of the largest output")
+    del w1q, w1s, w2q, w2s
+    torch.cuda.empty_cache()
+    return rec
+
+
 def run_gpu(args, wl):
     import torch
     import torch.distributed as dist
@@ -244,6 +521,7 @@ def run_gpu(args, wl):
         dist.init_process_group("nccl", device_id=device)
     if wl["e"] % world:
         raise SystemExit("experts must divide evenly over the ranks")
+    t_start = time.perf_counter()
     L = build_layer(wl, rank, world, device)
     step, owner, launches = make_step(wl, L, world, device)
     t, h = wl["t"], wl["h"]
@@ -349,64 +627,104 @@ def run_gpu(args, wl):
     per_step = ms / args.steps
     tflops = flops / (per_step * 1e-3) / 1e12
     tflops_e2e = flops / (ms_e2e / args.steps * 1e-3) / 1e12
+    pk = peaks()
 
     roof = stage = None
+    sub = {}
     if world == 1:
         # stage durations with CUDA events on the launching stream (same inputs, same launches)
-        hq, hs = ks.nvfp4_quantize(x_dev, ACT_GLOBAL_SCALE)
-        ids, w = ks.route_topk(ks.router_logits(x_dev, L["gate_w"]), wl["k"], L["bias"])
+        hq, hs, ids, w = step.front(x_dev)
         acc = None
         reps = max(3, min(args.steps, 10))
         for _ in range(reps):
-            d = owner.run_profiled(ids, w, hq, hs.view(torch.uint8), L["w1q"], L["w1s"], L["w2q"], L["w2s"], state["out"],
+            d = owner.run_profiled(ids, w, hq, hs, L["w1q"], L["w1s"], L["w2q"], L["w2s"], state["out"],
                                    scale_up=L["scale_fc1"], scale_gate=L["scale_fc1"], scale_out=L["scale_fc2"])
             acc = d if acc is None else {k2: acc[k2] + v for k2, v in d.items()}
         stage = {k2: v / reps for k2, v in acc.items()}
         totals = owner.workspace()["totals"].cpu().tolist()
         stage["m_tiles"] = totals[0]
         stage["tile_fill"] = totals[2] / max(1, totals[0] * 128)
-        pk = peaks()
         fc1_flops = flops * 2.0 / 3.0
         rows_used = totals[1]
-        fc1_bytes = (int((owner.workspace()["counts"].cpu() > 0).sum()) * 2 * wl["i"] * h * 9 / 16      # weights of the experts touched
-                     + rows_used * h * 9 / 16 + rows_used * wl["i"] * 9 / 16)                           # permuted rows in, activations out
-        achieved = fc1_flops / (stage["fc1"] * 1e-3) / 1e12
-        peak = 4.0 * pk["bf16_sustained"]
         counts = owner.workspace()["counts"].cpu()
         touched = int((counts > 0).sum())
+        fc1_bytes = (touched * 2 * wl["i"] * h * 9 / 16                                   # weights of the experts touched
+                     + rows_used * h * 9 / 16 + rows_used * wl["i"] * 9 / 16)             # permuted rows in, activations out
+        achieved = fc1_flops / (stage["fc1"] * 1e-3) / 1e12
         weight_bytes = touched * 3 * wl["i"] * h * 9 / 16
         act_bytes = t * h * 2 * 2 + t * h * 9 / 16
         stage["experts_touched"] = touched
         stage["hbm_algorithmic_gbs"] = (weight_bytes + act_bytes) / (per_step * 1e-3) / 1e9
         stage["hbm_frac_of_measured"] = stage["hbm_algorithmic_gbs"] / pk["hbm_gbs"]
-        roof = dict(bound="tensor", kernel="k_gemm_nvfp4<FC1>", achieved=achieved, peak=peak, unit="TFLOP/s", frac=achieved / peak,
-                    peak_source=f"4 x bf16_tflops_sustained of {pk['source']} MEASURED_PEAKS (FP4:bf16 nominal ratio)",
-                    frac_of_nominal_fp4=achieved / FP4_NOMINAL_TFLOPS,
-                    traffic=FC1_DRAM_TRAFFIC.get(args.workload) if args.tokens is None and args.zipf is None else None,
-                    traffic_unit="bytes of DRAM traffic per FC1 launch (ncu)",
-                    algorithmic_bytes=fc1_bytes,
-                    layer_frac_of_nominal_fp4=tflops / FP4_NOMINAL_TFLOPS)
+        stage["fc2_tflops"] = flops / 3.0 / (stage["fc2"] * 1e-3) / 1e12
+        roof = tensor_roofline(achieved, pk, clocks, kernel="k_gemm_nvfp4<FC1>",
+                               traffic=FC1_DRAM_TRAFFIC.get(args.workload) if args.tokens is None and args.zipf is None else None,
+                               traffic_unit="bytes of DRAM traffic per FC1 launch (ncu capture summarised under profiles/)",
+                               algorithmic_bytes=fc1_bytes, layer_frac_of_nominal_fp4=tflops / FP4_NOMINAL_TFLOPS,
+                               fc1_hbm_gbs=fc1_bytes / (stage["fc1"] * 1e-3) / 1e9,
+                               fc1_hbm_frac_of_measured=fc1_bytes / (stage["fc1"] * 1e-3) / 1e9 / pk["hbm_gbs"])
+        if not args.no_sub and rank == 0:
+            def guarded(name, fn):
+                t0 = time.perf_counter()
+                try:
+                    sub[name] = fn()
+                except Exception as exc:       # a sub-record never takes the headline line down
+                    sub[name] = dict(error=repr(exc)[:300])
+                if isinstance(sub[name], dict):
+                    sub[name]["wall_s"] = round(time.perf_counter() - t0, 1)
+
+            if args.workload == "dsv3" and args.tokens is None:
+                guarded("dsv3_decode_T64", lambda: sub_layer_record("dsv3", 64, args, device, pk, L=L))
+                guarded("dsv3_decode_T256", lambda: sub_layer_record("dsv3", 256, args, device, pk, L=L))
+                guarded("qwen3_T16384", lambda: sub_layer_record("qwen3", None, args, device, pk))
+            guarded("dense_nvfp4_gemm", lambda: dict(sizes=sub_dense_records(pk)))
+            guarded("reference_kernel", lambda: sub_reference_kernel())
     ep_stage = None
     if world > 1:
         owner.profile = True
         resident()
         ep_stage = owner.stage_ms()
         owner.profile = False
+        if not args.no_sub:
+            sub["parity"] = ep_parity_record(wl, L, step, device, world, rank)
+            for name, tok, zipf in (("decode_T64", 64, None), ("decode_T256", 256, None), ("uniform_routing", None, 0.0)):
+                try:
+                    xx = x_dev[:tok] if tok else x_dev
+                    L2 = L if zipf is None else dict(L, bias=None)
+                    st2, own2, _ = (step, owner, None) if zipf is None else make_step(wl, L2, world, device)
+                    holder = {}
+
+                    def fn(st2=st2, xx=xx, holder=holder):
+                        holder["ids"] = st2(xx)[1]
+
+                    ms2 = timed(fn, 10, 3) / 10
+                    v2 = (holder["ids"] >= 0).sum().to(torch.float64)
+                    dist.all_reduce(v2)
+                    tt = xx.shape[0]
+                    fl2 = layer_flops(wl, float(v2.item()), tt * world)
+                    sub[name] = dict(tokens_per_gpu=tt, ms_per_step=ms2, tflops=fl2 / (ms2 * 1e-3) / 1e12,
+                                     tokens_per_s=tt * world / (ms2 * 1e-3), device_status=own2.status())
+                except Exception as exc:
+                    sub[name] = dict(error=repr(exc)[:300])
     if rank != 0:
         if world > 1:
+            failed = bool(sub.get("parity")) and not sub["parity"]["passed"]
             dist.destroy_process_group()
+            if failed:
+                raise SystemExit(3)
         return
     cpu = time_cpu(wl, 1, 0) if world == 1 else None
     line = dict(metric="nvfp4_moe_layer_tflops", value=tflops, unit="TFLOP/s", n_gpus=world, steps=args.steps, warmup=args.warmup,
                 ms_per_step=per_step, higher_is_better=True, scaling="weak", vs_baseline=None, dtype="nvfp4 (e2m1 x ue4m3, fp32 accumulate)",
                 data="synthetic", tokens_per_s=t * world / (per_step * 1e-3),
                 config=dict(workload=wl["label"], tokens_per_gpu=t, hidden=h, intermediate=wl["i"], experts=wl["e"], top_k=wl["k"],
-                            shared_experts=wl["s"], parallelism=f"ep{world}",
+                            shared_experts=wl["s"], parallelism=f"ep{world}", activation_global_scale=ACT_GLOBAL_SCALE,
                             l2="weights (%.2f GB per GPU) exceed the 126 MB L2; no flush needed" %
                                ((L["w1q"].numel() + L["w1s"].numel() + L["w2q"].numel() + L["w2s"].numel()) / 1e9)),
                 e2e=dict(value=tflops_e2e, unit="TFLOP/s", h2d_bytes_per_step=x_host.numel() * 2, d2h_bytes_per_step=out_host.numel() * 2,
                          ms_per_step=ms_e2e / args.steps),
-                gpu_launches=launches * args.steps, device_status=status, clocks=clocks)
+                gpu_launches=launches * args.steps, device_status=status, clocks=clocks,
+                frac_of_nominal_fp4=tflops / FP4_NOMINAL_TFLOPS)
     if graph_ms is not None:
         line["graph_replay"] = dict(ms_per_step=graph_ms, tokens_per_s=t / (graph_ms * 1e-3))
     if ep_stage:
@@ -416,11 +734,17 @@ def run_gpu(args, wl):
     if roof:
         line["roofline"] = roof
     if cpu:
-        line["cpu_baseline"] = dict(value=cpu["tflops"], unit="TFLOP/s", cores=cpu["cores"], kind="port", sample=cpu["sample"],
+        line["cpu_baseline"] = dict(value=cpu["tflops"], unit="TFLOP/s", cores=cpu["cores"], kind=cpu["kind"], sample=cpu["sample"],
                                     tokens_per_s=cpu["tokens_per_s"])
+    if sub:
+        line["sub"] = sub
+    line["wall_s"] = round(time.perf_counter() - t_start, 1)
     print(json.dumps(line))
+    failed = world > 1 and bool(sub.get("parity")) and not sub["parity"]["passed"]
     if world > 1:
         dist.destroy_process_group()
+    if failed:
+        raise SystemExit(3)
 
 
 def run_reference_gpu(args, wl):
@@ -504,8 +828,7 @@ def run_dense(args):
     tf = 2.0 * m * n * k / (ms * 1e-3) / 1e12
     print(json.dumps(dict(metric="nvfp4_dense_gemm_tflops", value=tf, unit="TFLOP/s", n_gpus=1, steps=args.steps, warmup=args.warmup,
                           ms_per_step=ms, higher_is_better=True, dtype="nvfp4", data="synthetic",
-                          config=dict(workload=f"dense_nvfp4_gemm_{m}x{n}x{k}", tile_n=args.tile_n,
-                                      kernel_switches=os.environ.get("B200MOE_DBG", "0")),
+                          config=dict(workload=f"dense_nvfp4_gemm_{m}x{n}x{k}", tile_n=args.tile_n),
                           frac_of_nominal_fp4=tf / FP4_NOMINAL_TFLOPS)))
 
 
@@ -568,6 +891,7 @@ def main():
     ap.add_argument("--dense", default=None, metavar="M,N,K", help="time the dense NVFP4 GEMM of this shape instead of the layer")
     ap.add_argument("--a-bf16", action="store_true", help="with --dense: keep A in bf16 (the bf16 x NVFP4 operator) instead of quantising it")
     ap.add_argument("--tile-n", type=int, default=0, help="GEMM tile for --dense (0 = default, 128, 256, 512 = CTA pair)")
+    ap.add_argument("--no-sub", action="store_true", help="leave the sub-records out (headline workload only)")
     args = ap.parse_args()
     if args.dense:
         return run_dense_w4a16(args) if args.a_bf16 else run_dense(args)

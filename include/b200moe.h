@@ -194,7 +194,8 @@ int b200moe_ep_pack(b200moe_handle plan, const void* hidden_states, const void* 
  * allocating routine. The first call on each device looks up the device address of that array (a host-side
  * query, no allocation); make that first call outside any CUDA stream capture. All calls on one device share the
  * array, so two calls whose kernels may overlap on the GPU (different streams) race; calls on one stream are safe.
- * Nothing in the scratch has to start at zero: every call overwrites the part it reads. */
+ * Nothing in the scratch has to start at zero: every call overwrites the part it reads. Host threads may make a device's
+ * first call concurrently (the address cache is an atomic; both look up the same value). */
 int b200moe_route_map_noalloc(const int32_t* topk_ids, const float* topk_weights, int32_t num_tokens, int32_t top_k,
                               int32_t num_shared_experts, int32_t num_experts, int32_t local_expert_offset, int32_t* counts,
                               int32_t* seg_start, int32_t* tile_expert, int32_t* tile_row0, int32_t* tile_rows, int32_t* totals,

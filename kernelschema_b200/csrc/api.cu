@@ -11,6 +11,20 @@
 using namespace b200;
 
 namespace b200 {
+int sm_count() {
+  static std::atomic<int> cached[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+  if (dev < 64) {
+    const int v = cached[dev].load(std::memory_order_relaxed);
+    if (v > 0) return v;
+  }
+  int sms = 0;
+  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) return 148;
+  if (dev < 64) cached[dev].store(sms, std::memory_order_relaxed);
+  return sms;
+}
+
 bool pdl_enabled() {
   static const bool on = [] {
     const char* v = getenv("B200MOE_PDL");
@@ -194,7 +208,6 @@ int run_impl(b200moe_layer* h, const b200moe_args* a, cudaStream_t st, cudaEvent
   g.tile_rows = h->rm.tile_rows;
   g.n_tiles_ptr = h->rm.totals;
   g.status = h->status;
-  if (const char* dbg = getenv("B200MOE_DBG")) g.dbg = atoi(dbg);   // timing experiments only
   // FC1: [rows, H] x [2I, H]^T -> activation -> NVFP4 [rows, I]
   g.N = 2 * c.intermediate;
   g.K = c.hidden;
@@ -306,14 +319,10 @@ int b200moe_router_logits(const void* x, const void* w, int64_t T, int32_t H, in
   if (T < 0 || H <= 0 || H % 8 || E <= 0) return fail(752, "router_logits: hidden must be a positive multiple of 8");
   if (T && (!x || !w || !logits)) return fail(753, "router_logits: null pointer");
   if (((uintptr_t)x | (uintptr_t)w) & 15) return fail(754, "router_logits: operands must be 16-byte aligned");
-  // tensor-core path: whole gate matrix as one B tile (E <= 256), K in 64-element stages, 16-byte aligned rows
-  static const int forced = [] {
-    const char* v = getenv("B200MOE_ROUTER_PATH");      // timing experiments only: 1 = tensor cores, 2 = SIMT, 3 = decode kernel
-    return v ? atoi(v) : 0;
-  }();
-  if ((forced == 0 || forced == 3) && T <= 16)      // decode sizes: stream the gate matrix over the whole device
+  if (T <= 16)      // decode sizes: stream the gate matrix over the whole device
     return cuda_fail(launch_router_logits_small(x, w, T, H, E, logits, (cudaStream_t)stream), "router_logits");
-  if (forced != 2 && E <= 256 && H % 64 == 0 && E % 8 == 0)
+  // tensor-core path: whole gate matrix as one B tile (E <= 256), K in 64-element stages, 16-byte aligned rows
+  if (E <= 256 && H % 64 == 0 && E % 8 == 0)
     return cuda_fail(launch_router_logits_tc(x, w, T, H, E, logits, nullptr, (cudaStream_t)stream), "router_logits");
   return cuda_fail(launch_router_logits(x, w, T, H, E, logits, (cudaStream_t)stream), "router_logits");
 }
@@ -347,10 +356,7 @@ int b200moe_gemm_nvfp4(const void* a_q, const void* a_sf, const void* b_q, const
   g.out_stride = out_stride;
   g.dense_alpha = alpha;
   g.status = status;
-  if (const char* dbg = getenv("B200MOE_DBG")) g.dbg = atoi(dbg);   // timing experiments only
-  int dev = 0, sms = 0;
-  cudaGetDevice(&dev);
-  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int sms = sm_count();
   if (bn == 512) {
     CUtensorMap tsa, tsb;
     rc = make_sf_map(&tsa, a_sf, (uint64_t)((m + 127) / 128) * (k / 64));
@@ -408,10 +414,8 @@ int b200moe_create(const b200moe_config* cfg, b200moe_handle* out) {
   h->row_capacity = p.row_capacity;
   h->tile_capacity = p.tile_capacity;
   h->bn = cfg->tile_n ? cfg->tile_n : ((2 * cfg->intermediate) % 256 == 0 && cfg->hidden % 256 == 0 ? 256 : 128);
-  int dev = 0;
-  cudaError_t e = cudaGetDevice(&dev);
-  if (e == cudaSuccess) e = cudaDeviceGetAttribute(&h->sm_count, cudaDevAttrMultiProcessorCount, dev);
-  if (e == cudaSuccess) e = cudaMalloc(&h->base, (size_t)p.total);
+  h->sm_count = sm_count();
+  cudaError_t e = cudaMalloc(&h->base, (size_t)p.total);
   if (e != cudaSuccess) {
     delete h;
     return cuda_fail((int)e, "create: workspace allocation");

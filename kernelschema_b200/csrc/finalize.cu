@@ -46,10 +46,11 @@ __global__ void __launch_bounds__(128) k_finalize(const __nv_bfloat16* __restric
 int launch_finalize(const void* rout, const int32_t* row_of, const float* weight_of_row, int64_t T, int KK, int H, void* out,
                     int64_t out_stride, cudaStream_t st) {
   if (T == 0) return 0;
-  const int64_t blocks = T < 148 * 16 ? T : 148 * 16;
+  const int sms = sm_count();
+  const int64_t blocks = T < sms * 16 ? T : sms * 16;
   // few tokens: spread each token's row over several blocks so that the whole GPU pulls on HBM
   const int chunks = (H / 8 + 127) / 128;
-  const int by = blocks >= 148 * 4 ? 1 : (int)(chunks < (148 * 4 + blocks - 1) / blocks ? chunks : (148 * 4 + blocks - 1) / blocks);
+  const int by = blocks >= sms * 4 ? 1 : (int)(chunks < (sms * 4 + blocks - 1) / blocks ? chunks : (sms * 4 + blocks - 1) / blocks);
   return (int)launch_chain(k_finalize, dim3((unsigned)blocks, (unsigned)by), dim3(128), 0, st, (const __nv_bfloat16*)rout, row_of,
                            weight_of_row, T, KK, H, (__nv_bfloat16*)out, out_stride);
 }

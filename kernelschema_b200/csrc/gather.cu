@@ -54,7 +54,7 @@ int launch_gather_rows(const void* hid_q, const void* hid_sf, int hid_sf_tiled, 
   // per row of the capacity, so that every row's index -> source -> copy chain is in flight at once (DeepSeek-V3 geometry,
   // 3.5 KB rows: 112 us against 128 us); rows past the count in `totals` exit at once.
   int64_t blocks = (row_capacity + 7) / 8;
-  if (H <= 4096 && blocks > 148 * 8) blocks = 148 * 8;
+  if (H <= 4096 && blocks > (int64_t)sm_count() * 8) blocks = (int64_t)sm_count() * 8;
   return (int)launch_chain(k_gather_rows, dim3((unsigned)blocks), dim3(256), 0, st, (const uint8_t*)hid_q, (const uint8_t*)hid_sf,
                            hid_sf_tiled, q_stride > 0 ? q_stride : (int64_t)(H / 2), sf_stride > 0 ? sf_stride : (int64_t)(H / 16),
                            tok_of_row, tile_rows, totals, H, (uint8_t*)a_q, (uint8_t*)a_sf);
@@ -126,7 +126,7 @@ int launch_ep_pack(const void* hid_q, const void* hid_sf, const int32_t* ids, co
                    int world, int64_t row_bytes, int64_t row_capacity, void* out, cudaStream_t st) {
   if (row_capacity == 0) return 0;
   int64_t blocks = (row_capacity + 7) / 8;
-  if (blocks > 148 * 8) blocks = 148 * 8;
+  if (blocks > (int64_t)sm_count() * 8) blocks = (int64_t)sm_count() * 8;
   k_ep_pack<<<(unsigned)blocks, 256, 0, st>>>((const uint8_t*)hid_q, (const uint8_t*)hid_sf, ids, weights, tok_of_row, tile_expert,
                                              tile_rows, totals, H, K, experts_per_rank, world, row_bytes, (uint8_t*)out);
   return (int)cudaGetLastError();

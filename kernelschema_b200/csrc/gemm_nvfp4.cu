@@ -14,8 +14,14 @@
 //        32-column block is exactly one 16-channel NVFP4 block of the intermediate activation;
 //   FC2: column 8a+b is output channel 4b+a.
 //
-// One CTA per SM, warp-specialised: TMA producer, MMA issuer, scale-factor copier, epilogue warps (roles are listed
+// One CTA per SM, warp-specialised: TMA producer, MMA issuer, scale-factor copiers, epilogue warps (roles are listed
 // at each kernel). Stage = 256 FP4 of K: A 16 KB, B BN*128 B, scale factors 2 KB per 128 rows.
+//
+// What bounds the mainloop is the rate at which ONE thread can issue tcgen05 instructions: about 48 cycles per
+// instruction (tcgen05.cp, tcgen05.mma and tcgen05.commit alike), measured on B200 with an issue-only loop. A 128 x 256
+// stage needs 12 scale-factor copies + 4 MMAs (512 tensor cycles): 16 x 48 = 770 cycles from one thread, 12 x 48 + a
+// wait + a commit = 880 from one copier thread beside an MMA thread. Different warps issue concurrently, so the copies
+// are split over kCopiers warps (6 each for BN = 256): every issuing thread stays below the 512 cycles of its stage.
 #include "kernels.cuh"
 #include "ptx.cuh"
 
@@ -24,7 +30,7 @@ namespace b200 {
 constexpr int kBM = 128;
 constexpr int kStageK = 256;             // FP4 elements of K per pipeline stage (128 payload bytes per row)
 constexpr int kSfChunk = 512;            // bytes of one (128 rows x 64 K) scale-factor chunk
-constexpr int kNumSfBuf = 4;             // TMEM scale-factor buffers in rotation
+constexpr int kCopiers = 2;              // warps that issue the scale-factor copies of a stage, half of them each
 
 template <int BN>
 struct GemmCfg {
@@ -38,8 +44,25 @@ struct GemmCfg {
   static constexpr int kSfCols = 16 + 16 * (BN / 128);          // TMEM columns of one scale-factor buffer
   static constexpr int kSfBase = kAccBufs * BN;                  // first scale-factor column
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
-  static_assert(kSfBase + kNumSfBuf * kSfCols <= 512, "TMEM budget");
+  // one TMEM scale-factor buffer per pipeline stage: a copier can run as far ahead of the MMA thread as the stage ring lets it
+  static_assert(kSfBase + kStages * kSfCols <= 512, "TMEM budget");
+  static constexpr int kSfCopies = 4 + 4 * (BN / 128);           // tcgen05.cp per stage
+  static_assert(kSfCopies % kCopiers == 0, "copies split evenly over the copier warps");
 };
+
+// Cycle accounting of the MMA thread (where it waits), compiled only into experiment builds (-DB200MOE_PROBE).
+#ifdef B200MOE_PROBE
+__device__ long long g_probe[1024 * 4];
+#define PROBE_DECL long long pr_acc = 0, pr_sf = 0, pr_c = 0; const long long pr_t0 = clock64();
+#define PROBE_T(var) const long long var = clock64();
+#define PROBE_ADD(acc, t0) acc += clock64() - (t0);
+#define PROBE_STORE if (blockIdx.x < 1024) { g_probe[blockIdx.x * 4] = clock64() - pr_t0; g_probe[blockIdx.x * 4 + 1] = pr_acc; g_probe[blockIdx.x * 4 + 2] = pr_sf; g_probe[blockIdx.x * 4 + 3] = pr_c; }
+#else
+#define PROBE_DECL
+#define PROBE_T(var)
+#define PROBE_ADD(acc, t0)
+#define PROBE_STORE
+#endif
 
 DEV void report(int32_t* status, int code) {
   if (status) atomicCAS(status, 0, code);
@@ -61,7 +84,6 @@ DEV float tanh_fast(float x) {
 template <int MODE, int EC, class Release>
 DEV void epilogue_cols(const GemmParams& p, uint32_t taddr, int e, size_t row, bool live, int col0, Release release) {
   constexpr int NCB = EC / 32;
-  if (p.dbg & 8) live = false;
   // a warp whose 32 rows are all padding (decode: a few routes per expert) neither reads the accumulator nor computes
   if (!__any_sync(0xFFFFFFFFu, live)) {
     release();
@@ -168,10 +190,48 @@ DEV void epilogue_cols(const GemmParams& p, uint32_t taddr, int e, size_t row, b
   }
 }
 
-// Warp roles: 0 = TMA producer, 1 = TMEM owner + MMA issuer, 2 = scale-factor copier (shared memory -> TMEM),
-// 3 .. 3 + 4 * BN/EC - 1 = epilogue; epilogue warp w owns TMEM lane quadrant w & 3 and the EC-column group (w - 3) / 4.
+// Warp roles: 0 = TMA producer, 1 = TMEM owner + MMA issuer, 2 .. 1 + kCopiers = scale-factor copiers (shared memory ->
+// TMEM), then 4 * BN/EC epilogue warps; epilogue warp w owns TMEM lane quadrant w & 3 and the EC-column group
+// (w - kFirstEpiWarp) / 4.
+constexpr int kFirstEpiWarp = 2 + kCopiers;
+static_assert(kFirstEpiWarp % 4 == 0, "epilogue warp w must own lane quadrant w & 3 with groups of four consecutive warps");
 template <int BN, int EC>
-constexpr int gemm_threads() { return 32 * (3 + 4 * BN / EC); }
+constexpr int gemm_threads() { return 32 * (kFirstEpiWarp + 4 * BN / EC); }
+
+// Scale-factor copy j of a stage (j < 4: A scales of k-block j; then B scales, 128-row half h, k-block q) from the
+// stage's shared-memory slots into its TMEM buffer.
+template <int BN>
+DEV void sf_copy(int j, uint32_t sf_t, uint32_t sfa_lo, uint32_t sfb_lo) {
+  constexpr uint32_t kHiSf = (128u >> 4) | (1u << 14);                 // SBO 128, descriptor version 1, no swizzle
+  if (j < 4) {
+    tmem_cp_sf(sf_t + 4 * j, ((uint64_t)kHiSf << 32) | (sfa_lo + j * (kSfChunk >> 4)));
+  } else {
+    const int h = (j - 4) >> 2, q = (j - 4) & 3;
+    tmem_cp_sf(sf_t + 16 + (BN / 128) * 4 * q + 4 * h, ((uint64_t)kHiSf << 32) | (sfb_lo + (h * 4 + q) * (kSfChunk >> 4)));
+  }
+}
+
+// The scale-factor copies of copier warp C: copies [C * n, (C + 1) * n) of every stage, n = kSfCopies / kCopiers.
+template <int BN, int C>
+DEV void copier_loop(const GemmParams& p, uint32_t tmem, uint32_t s_sfa, uint32_t s_sfb, uint32_t bar_full, uint32_t bar_sf,
+                     long long total_items, int nk) {
+  using Cfg = GemmCfg<BN>;
+  constexpr int kPer = Cfg::kSfCopies / kCopiers;
+  const uint32_t sfa_lo0 = (s_sfa >> 4) & 0x3FFF, sfb_lo0 = (s_sfb >> 4) & 0x3FFF;
+  uint32_t s = 0, ph = 0;
+  for (long long item = blockIdx.x; item < total_items; item += gridDim.x) {
+    for (int ks = 0; ks < nk; ++ks) {
+      if (!mbar_wait(bar_full + 8 * s, ph)) { report(p.status, 105); return; }
+      tc_fence_after();
+      const uint32_t sf_t = tmem + Cfg::kSfBase + s * Cfg::kSfCols;
+      const uint32_t sfa_lo = sfa_lo0 + s * (Cfg::kSfaBytes >> 4), sfb_lo = sfb_lo0 + s * (Cfg::kSfbBytes >> 4);
+#pragma unroll
+      for (int j = C * kPer; j < (C + 1) * kPer; ++j) sf_copy<BN>(j, sf_t, sfa_lo, sfb_lo);
+      mma_commit(bar_sf + 8 * s);                      // arrives once this thread's copies have landed
+      if (++s == Cfg::kStages) { s = 0; ph ^= 1; }
+    }
+  }
+}
 
 template <int MODE, int BN, int EC>
 __global__ void __launch_bounds__(gemm_threads<BN, EC>(), 1)
@@ -186,7 +246,7 @@ k_gemm_nvfp4(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
   const uint32_t s_sfb = s_sfa + C::kStages * C::kSfaBytes;
   const uint32_t s_bar = s_sfb + C::kStages * C::kSfbBytes;
   const uint32_t bar_full = s_bar;                              // [kStages] TMA bytes landed
-  const uint32_t bar_sf = bar_full + 8 * C::kStages;            // [kStages] scale factors of the stage are in TMEM
+  const uint32_t bar_sf = bar_full + 8 * C::kStages;            // [kStages] scale factors of the stage are in TMEM (all copiers)
   const uint32_t bar_empty = bar_sf + 8 * C::kStages;           // [kStages] MMAs of the stage retired
   const uint32_t bar_acc_full = bar_empty + 8 * C::kStages;     // [kAccBufs]
   const uint32_t bar_acc_empty = bar_acc_full + 8 * C::kAccBufs;
@@ -198,7 +258,7 @@ k_gemm_nvfp4(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::kStages; ++s) {
       mbar_init(bar_full + 8 * s, 1);
-      mbar_init(bar_sf + 8 * s, 1);
+      mbar_init(bar_sf + 8 * s, kCopiers);
       mbar_init(bar_empty + 8 * s, 1);
     }
     for (int b = 0; b < C::kAccBufs; ++b) {
@@ -250,92 +310,68 @@ k_gemm_nvfp4(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
         for (int ks = 0; ks < nk; ++ks) {
           if (!mbar_wait(bar_empty + 8 * s, ph)) { report(p.status, 101); ok = false; break; }
           const uint32_t full = bar_full + 8 * s;
-          if (p.dbg & 1) {
-            mbar_arrive(full);
-          } else {
-            mbar_expect_tx(full, C::kStageBytes);
-            tma_load_2d(s_a + s * C::kABytes, &tm_a, full, ks * 128, row0);
-            tma_load_2d(s_b + s * C::kBBytes, &tm_b, full, ks * 128, brow0);
-            bulk_load_1d(s_sfa + s * C::kSfaBytes, sfa_src + (size_t)ks * 4 * kSfChunk, 4 * kSfChunk, full);
+          mbar_expect_tx(full, C::kStageBytes);
+          tma_load_2d(s_a + s * C::kABytes, &tm_a, full, ks * 128, row0);
+          tma_load_2d(s_b + s * C::kBBytes, &tm_b, full, ks * 128, brow0);
+          bulk_load_1d(s_sfa + s * C::kSfaBytes, sfa_src + (size_t)ks * 4 * kSfChunk, 4 * kSfChunk, full);
 #pragma unroll
-            for (int h = 0; h < BN / 128; ++h)
-              bulk_load_1d(s_sfb + s * C::kSfbBytes + h * 4 * kSfChunk,
-                           sfb_src + ((size_t)h * chunks_per_row + (size_t)ks * 4) * kSfChunk, 4 * kSfChunk, full);
-          }
+          for (int h = 0; h < BN / 128; ++h)
+            bulk_load_1d(s_sfb + s * C::kSfbBytes + h * 4 * kSfChunk,
+                         sfb_src + ((size_t)h * chunks_per_row + (size_t)ks * 4) * kSfChunk, 4 * kSfChunk, full);
           if (++s == C::kStages) { s = 0; ph ^= 1; }
         }
       }
       // this CTA has asked for its last bytes: the next kernel of the stream may start its prologue under our tail
       pdl_trigger();
     }
-  } else if (warp == 2) {
-    // ------------------------------------------------------------------ scale-factor copier: shared memory -> TMEM
-    // A separate issuing thread keeps the 8 or 12 tcgen05.cp per stage off the MMA thread's instruction stream;
-    // the commit that follows them arrives on bar_sf once the copies have landed.
+  } else if (warp >= 2 && warp < kFirstEpiWarp) {
+    // ------------------------------------------------------------------ scale-factor copiers: shared memory -> TMEM
     if (lane == 0) {
-      constexpr uint32_t kHiSf = (128u >> 4) | (1u << 14);                 // SBO 128, descriptor version 1, no swizzle
-      const uint32_t sfa_lo0 = (s_sfa >> 4) & 0x3FFF, sfb_lo0 = (s_sfb >> 4) & 0x3FFF;
-      uint32_t s = 0, ph = 0, sfi = 0;
-      bool ok = true;
-      for (long long item = blockIdx.x; ok && item < total_items; item += gridDim.x) {
-        for (int ks = 0; ks < nk; ++ks) {
-          if (!mbar_wait(bar_full + 8 * s, ph)) { report(p.status, 105); ok = false; break; }
-          tc_fence_after();
-          if (!(p.dbg & 4)) {
-            const uint32_t sf_t = tmem + C::kSfBase + sfi * C::kSfCols;
-            const uint32_t sfa_lo = sfa_lo0 + s * (C::kSfaBytes >> 4), sfb_lo = sfb_lo0 + s * (C::kSfbBytes >> 4);
-#pragma unroll
-            for (int q = 0; q < 4; ++q) tmem_cp_sf(sf_t + 4 * q, ((uint64_t)kHiSf << 32) | (sfa_lo + q * (kSfChunk >> 4)));
-#pragma unroll
-            for (int h = 0; h < BN / 128; ++h)
-#pragma unroll
-              for (int q = 0; q < 4; ++q)
-                tmem_cp_sf(sf_t + 16 + (BN / 128) * 4 * q + 4 * h, ((uint64_t)kHiSf << 32) | (sfb_lo + (h * 4 + q) * (kSfChunk >> 4)));
-          }
-          mma_commit(bar_sf + 8 * s);
-          if (++s == C::kStages) { s = 0; ph ^= 1; }
-          sfi = (sfi + 1) & (kNumSfBuf - 1);
-        }
-      }
+      if (warp == 2) copier_loop<BN, 0>(p, tmem, s_sfa, s_sfb, bar_full, bar_sf, total_items, nk);
+      else copier_loop<BN, kCopiers - 1>(p, tmem, s_sfa, s_sfb, bar_full, bar_sf, total_items, nk);
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      // One thread feeds the tensor pipe: everything is 32-bit, the stage ring is walked with counters and the
-      // shared-memory descriptors are base + stage * stride.
+      // One thread feeds the tensor pipe with four instructions per stage: everything is 32-bit, the stage ring is
+      // walked with counters and the shared-memory descriptors are base + stage * stride.
       constexpr uint32_t idesc = make_idesc_nvf4(kBM, BN);
       constexpr uint32_t kHiOp = (1024u >> 4) | (1u << 14) | (2u << 29);   // SBO 1024, version 1, SWIZZLE_128B
       const uint32_t a_lo0 = ((s_a >> 4) & 0x3FFF) | (1u << 16), b_lo0 = ((s_b >> 4) & 0x3FFF) | (1u << 16);
-      uint32_t s = 0, ph = 0, sfi = 0, it = 0;
+      uint32_t s = 0, ph = 0, it = 0;
       bool ok = true;
+      PROBE_DECL
       for (long long item = blockIdx.x; ok && item < total_items; item += gridDim.x, ++it) {
         const uint32_t buf = it % C::kAccBufs;
+        PROBE_T(pr_a)
         if (!mbar_wait(bar_acc_empty + 8 * buf, ((it / C::kAccBufs) & 1) ^ 1)) { report(p.status, 102); break; }
+        PROBE_ADD(pr_acc, pr_a)
         tc_fence_after();
         const uint32_t acc = tmem + buf * BN;
         for (int ks = 0; ks < nk; ++ks) {
+          // the copiers waited for the stage's TMA bytes before they copied: their barrier covers the operands too
+          PROBE_T(pr_b)
           if (!mbar_wait(bar_sf + 8 * s, ph)) { report(p.status, 103); ok = false; break; }
+          PROBE_ADD(pr_sf, pr_b)
           tc_fence_after();
-          if (!(p.dbg & 2)) {
-            const uint32_t sf_t = tmem + C::kSfBase + sfi * C::kSfCols;
-            const uint32_t a_lo = a_lo0 + s * (C::kABytes >> 4), b_lo = b_lo0 + s * (C::kBBytes >> 4);
-            mma_nvf4(acc, ((uint64_t)kHiOp << 32) | a_lo, ((uint64_t)kHiOp << 32) | b_lo, idesc, sf_t, sf_t + 16, ks ? 1u : 0u);
+          const uint32_t sf_t = tmem + C::kSfBase + s * C::kSfCols;
+          const uint32_t a_lo = a_lo0 + s * (C::kABytes >> 4), b_lo = b_lo0 + s * (C::kBBytes >> 4);
+          mma_nvf4(acc, ((uint64_t)kHiOp << 32) | a_lo, ((uint64_t)kHiOp << 32) | b_lo, idesc, sf_t, sf_t + 16, ks ? 1u : 0u);
 #pragma unroll
-            for (int q = 1; q < 4; ++q)
-              mma_nvf4(acc, ((uint64_t)kHiOp << 32) | (a_lo + 2 * q), ((uint64_t)kHiOp << 32) | (b_lo + 2 * q), idesc, sf_t + 4 * q,
-                       sf_t + 16 + (BN / 128) * 4 * q, 1u);
-          }
+          for (int q = 1; q < 4; ++q)
+            mma_nvf4(acc, ((uint64_t)kHiOp << 32) | (a_lo + 2 * q), ((uint64_t)kHiOp << 32) | (b_lo + 2 * q), idesc, sf_t + 4 * q,
+                     sf_t + 16 + (BN / 128) * 4 * q, 1u);
           mma_commit(bar_empty + 8 * s);
           if (++s == C::kStages) { s = 0; ph ^= 1; }
-          sfi = (sfi + 1) & (kNumSfBuf - 1);
         }
         if (ok) mma_commit(bar_acc_full + 8 * buf);
       }
+      PROBE_STORE
     }
   } else {
     // ------------------------------------------------------------------ epilogue
     const int quad = warp & 3;
-    const int group = (warp - 3) >> 2;               // which EC accumulator columns
+    const int group = (warp - kFirstEpiWarp) >> 2;   // which EC accumulator columns
     const int r_in_tile = quad * 32 + lane;
     uint32_t it = 0;
     for (long long item = blockIdx.x; item < total_items; item += gridDim.x, ++it) {
@@ -371,7 +407,8 @@ k_gemm_nvfp4(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
 // single-CTA tile. Work item = (pair of consecutive 128-row m-tiles of one expert, 256 weight rows).
 // Barriers: `full` lives in the leader (2 producer arrivals + both CTAs' TMA bytes); `empty` and `acc_full` exist
 // in both CTAs and are signalled by the leader's tcgen05.commit to both; `acc_empty` lives in the leader and
-// collects the 32 epilogue warps of the pair.
+// collects the 32 epilogue warps of the pair. The scale-factor copies are issued by kCopiers warps of the leader, half
+// of a stage's twelve each (one tcgen05.cp.cta_group::2 copies in both CTAs, each from its own shared memory).
 struct PairCfg {
   static constexpr int kStages = 5;
   static constexpr int kABytes = 128 * 128;
@@ -382,9 +419,10 @@ struct PairCfg {
   static constexpr int kSfCols = 48;
   static constexpr int kSfBase = 256;
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+  static_assert(kSfBase + kStages * kSfCols <= 512, "TMEM budget: one scale-factor buffer per stage");
 };
 
-constexpr int kPairThreads = 32 * 19;    // TMA, MMA, scale-factor copier, 16 epilogue warps
+constexpr int kPairThreads = 32 * (kFirstEpiWarp + 16);    // TMA, MMA, scale-factor copiers, 16 epilogue warps
 
 template <int MODE>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
@@ -414,7 +452,7 @@ k_gemm_nvfp4_pair(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::kStages; ++s) {
       mbar_init(bar_full + 8 * s, 2);
-      mbar_init(bar_sf + 8 * s, 1);
+      mbar_init(bar_sf + 8 * s, kCopiers);
       mbar_init(bar_empty + 8 * s, 1);
     }
     mbar_init(bar_acc_full, 1);
@@ -453,46 +491,44 @@ k_gemm_nvfp4_pair(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         for (int ks = 0; ks < nk; ++ks) {
           if (!mbar_wait(bar_empty + 8 * s, ph)) { report(p.status, 201); ok = false; break; }
           const uint32_t full = full0 + 8 * s;
-          if (p.dbg & 1) {
-            mbar_arrive_remote(full);
-          } else {
-            mbar_expect_tx_remote(full, C::kStageBytes);
-            tma_load_2d_pair(s_a + s * C::kABytes, &tm_a, full, ks * 128, row0);
-            tma_load_2d_pair(s_b + s * C::kBBytes, &tm_b, full, ks * 128, brow0 + (int)rank * 128);
-            tma_load_2d_pair(s_sfa + s * C::kSfaBytes, &tm_sfa, full, 0, sfa_y + ks * 4);
-            tma_load_2d_pair(s_sfb + s * C::kSfbBytes, &tm_sfb, full, 0, sfb_y + ks * 4);
-            tma_load_2d_pair(s_sfb + s * C::kSfbBytes + 4 * kSfChunk, &tm_sfb, full, 0, sfb_y + chunks_per_row + ks * 4);
-          }
+          mbar_expect_tx_remote(full, C::kStageBytes);
+          tma_load_2d_pair(s_a + s * C::kABytes, &tm_a, full, ks * 128, row0);
+          tma_load_2d_pair(s_b + s * C::kBBytes, &tm_b, full, ks * 128, brow0 + (int)rank * 128);
+          tma_load_2d_pair(s_sfa + s * C::kSfaBytes, &tm_sfa, full, 0, sfa_y + ks * 4);
+          tma_load_2d_pair(s_sfb + s * C::kSfbBytes, &tm_sfb, full, 0, sfb_y + ks * 4);
+          tma_load_2d_pair(s_sfb + s * C::kSfbBytes + 4 * kSfChunk, &tm_sfb, full, 0, sfb_y + chunks_per_row + ks * 4);
           if (++s == C::kStages) { s = 0; ph ^= 1; }
         }
       }
       pdl_trigger();
     }
-  } else if (warp == 2) {
-    // ------------------------------------------------------------------ scale-factor copier (leader; acts on both CTAs)
+  } else if (warp >= 2 && warp < kFirstEpiWarp) {
+    // ------------------------------------------------------------------ scale-factor copiers (leader; every copy acts on both CTAs)
     if (leader && lane == 0) {
       constexpr uint32_t kHiSf = (128u >> 4) | (1u << 14);
+      constexpr int kPer = 12 / kCopiers;
+      const int j0 = (warp - 2) * kPer;
       const uint32_t sfa_lo0 = (s_sfa >> 4) & 0x3FFF, sfb_lo0 = (s_sfb >> 4) & 0x3FFF;
-      uint32_t s = 0, ph = 0, sfi = 0;
+      uint32_t s = 0, ph = 0;
       bool ok = true;
       for (long long item = first; ok && item < total_items; item += stride) {
         for (int ks = 0; ks < nk; ++ks) {
           if (!mbar_wait_cluster(bar_full + 8 * s, ph)) { report(p.status, 205); ok = false; break; }
           tc_fence_after();
-          if (!(p.dbg & 4)) {
-            const uint32_t sf_t = tmem + C::kSfBase + sfi * C::kSfCols;
-            const uint32_t sfa_lo = sfa_lo0 + s * (C::kSfaBytes >> 4), sfb_lo = sfb_lo0 + s * (C::kSfbBytes >> 4);
+          const uint32_t sf_t = tmem + C::kSfBase + s * C::kSfCols;
+          const uint32_t sfa_lo = sfa_lo0 + s * (C::kSfaBytes >> 4), sfb_lo = sfb_lo0 + s * (C::kSfbBytes >> 4);
 #pragma unroll
-            for (int q = 0; q < 4; ++q) tmem_cp_sf_pair(sf_t + 4 * q, ((uint64_t)kHiSf << 32) | (sfa_lo + q * (kSfChunk >> 4)));
-#pragma unroll
-            for (int h = 0; h < 2; ++h)
-#pragma unroll
-              for (int q = 0; q < 4; ++q)
-                tmem_cp_sf_pair(sf_t + 16 + 8 * q + 4 * h, ((uint64_t)kHiSf << 32) | (sfb_lo + (h * 4 + q) * (kSfChunk >> 4)));
+          for (int jj = 0; jj < kPer; ++jj) {
+            const int j = j0 + jj;                       // copy j of the stage: 0..3 A scales, then B scales (half h, k-block q)
+            if (j < 4) {
+              tmem_cp_sf_pair(sf_t + 4 * j, ((uint64_t)kHiSf << 32) | (sfa_lo + j * (kSfChunk >> 4)));
+            } else {
+              const int h = (j - 4) >> 2, q = (j - 4) & 3;
+              tmem_cp_sf_pair(sf_t + 16 + 8 * q + 4 * h, ((uint64_t)kHiSf << 32) | (sfb_lo + (h * 4 + q) * (kSfChunk >> 4)));
+            }
           }
           mma_commit_pair_local(bar_sf + 8 * s);
           if (++s == C::kStages) { s = 0; ph ^= 1; }
-          sfi = (sfi + 1) & (kNumSfBuf - 1);
         }
       }
     }
@@ -502,7 +538,7 @@ k_gemm_nvfp4_pair(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       constexpr uint32_t idesc = make_idesc_nvf4(256, BN);
       constexpr uint32_t kHiOp = (1024u >> 4) | (1u << 14) | (2u << 29);
       const uint32_t a_lo0 = ((s_a >> 4) & 0x3FFF) | (1u << 16), b_lo0 = ((s_b >> 4) & 0x3FFF) | (1u << 16);
-      uint32_t s = 0, ph = 0, sfi = 0, it = 0;
+      uint32_t s = 0, ph = 0, it = 0;
       bool ok = true;
       for (long long item = first; ok && item < total_items; item += stride, ++it) {
         if (!mbar_wait_cluster(bar_acc_empty, (it & 1) ^ 1)) { report(p.status, 202); break; }
@@ -510,18 +546,15 @@ k_gemm_nvfp4_pair(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         for (int ks = 0; ks < nk; ++ks) {
           if (!mbar_wait(bar_sf + 8 * s, ph)) { report(p.status, 203); ok = false; break; }
           tc_fence_after();
-          if (!(p.dbg & 2)) {
-            const uint32_t sf_t = tmem + C::kSfBase + sfi * C::kSfCols;
-            const uint32_t a_lo = a_lo0 + s * (C::kABytes >> 4), b_lo = b_lo0 + s * (C::kBBytes >> 4);
-            mma_nvf4_pair(tmem, ((uint64_t)kHiOp << 32) | a_lo, ((uint64_t)kHiOp << 32) | b_lo, idesc, sf_t, sf_t + 16, ks ? 1u : 0u);
+          const uint32_t sf_t = tmem + C::kSfBase + s * C::kSfCols;
+          const uint32_t a_lo = a_lo0 + s * (C::kABytes >> 4), b_lo = b_lo0 + s * (C::kBBytes >> 4);
+          mma_nvf4_pair(tmem, ((uint64_t)kHiOp << 32) | a_lo, ((uint64_t)kHiOp << 32) | b_lo, idesc, sf_t, sf_t + 16, ks ? 1u : 0u);
 #pragma unroll
-            for (int q = 1; q < 4; ++q)
-              mma_nvf4_pair(tmem, ((uint64_t)kHiOp << 32) | (a_lo + 2 * q), ((uint64_t)kHiOp << 32) | (b_lo + 2 * q), idesc,
-                            sf_t + 4 * q, sf_t + 16 + 8 * q, 1u);
-          }
+          for (int q = 1; q < 4; ++q)
+            mma_nvf4_pair(tmem, ((uint64_t)kHiOp << 32) | (a_lo + 2 * q), ((uint64_t)kHiOp << 32) | (b_lo + 2 * q), idesc,
+                          sf_t + 4 * q, sf_t + 16 + 8 * q, 1u);
           mma_commit_pair(bar_empty + 8 * s);
           if (++s == C::kStages) { s = 0; ph ^= 1; }
-          sfi = (sfi + 1) & (kNumSfBuf - 1);
         }
         if (ok) mma_commit_pair(bar_acc_full);
       }
@@ -529,7 +562,7 @@ k_gemm_nvfp4_pair(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   } else {
     // ------------------------------------------------------------------ epilogue (both CTAs: own 128 rows x 256 columns)
     const int quad = warp & 3;
-    const int group = (warp - 3) >> 2;
+    const int group = (warp - kFirstEpiWarp) >> 2;
     const int r_in_tile = quad * 32 + lane;
     const uint32_t acc_empty_leader = map_to_cta(bar_acc_empty, 0);
     uint32_t it = 0;
@@ -610,12 +643,8 @@ template <int MODE>
 static int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tsa, const CUtensorMap& tsb,
                        const GemmParams& p, int grid, cudaStream_t st) {
   auto kern = k_gemm_nvfp4_pair<MODE>;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg::kSmemBytes);
-    if (e != cudaSuccess) return (int)e;
-    configured = true;
-  }
+  static SmemOptIn opt_in;
+  if (int e = opt_in.ensure(kern, PairCfg::kSmemBytes)) return e;
   return (int)launch_chain(kern, dim3(grid), dim3(kPairThreads), PairCfg::kSmemBytes, st, ta, tb, tsa, tsb, p);
 }
 
@@ -633,24 +662,13 @@ int launch_gemm_nvfp4_pair(int mode, const CUtensorMap& ta, const CUtensorMap& t
 template <int MODE, int BN, int EC>
 static int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid, cudaStream_t st) {
   auto kern = k_gemm_nvfp4<MODE, BN, EC>;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmCfg<BN>::kSmemBytes);
-    if (e != cudaSuccess) return (int)e;
-    configured = true;
-  }
+  static SmemOptIn opt_in;
+  if (int e = opt_in.ensure(kern, GemmCfg<BN>::kSmemBytes)) return e;
   return (int)launch_chain(kern, dim3(grid), dim3(gemm_threads<BN, EC>()), GemmCfg<BN>::kSmemBytes, st, ta, tb, p);
 }
 
 // Epilogue columns per warp: 64 when a tile's k-loop is too short to hide the eight-warp epilogue (see epilogue_cols).
-static int epilogue_cols_for(int k) {
-  static const int forced = [] {
-    const char* v = getenv("B200MOE_EPI_COLS");      // timing experiments only
-    return v ? atoi(v) : 0;
-  }();
-  if (forced == 64 || forced == 128) return forced;
-  return k >= 4096 ? 128 : 64;
-}
+static int epilogue_cols_for(int k) { return k >= 4096 ? 128 : 64; }
 
 template <int MODE>
 static int launch_mode(int bn, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid, cudaStream_t st) {
@@ -668,5 +686,11 @@ int launch_gemm_nvfp4(int mode, int bn, const CUtensorMap& ta, const CUtensorMap
   if (mode == kGemmFc2) return launch_mode<kGemmFc2>(bn, ta, tb, p, grid, st);
   return launch_mode<kGemmDense>(bn, ta, tb, p, grid, st);
 }
+
+#ifdef B200MOE_PROBE
+extern "C" int b200moe_probe_read(long long* host, int n) {
+  return (int)cudaMemcpyFromSymbol(host, g_probe, sizeof(long long) * n);
+}
+#endif
 
 }  // namespace b200

@@ -366,21 +366,15 @@ static int w4a16_splits(int64_t m, int64_t n, int64_t k, int sms) {
 }
 
 int64_t gemm_w4a16_workspace_bytes(int64_t m, int64_t n, int64_t k) {
-  int dev = 0, sms = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) sms = 148;
-  const int s = w4a16_splits(m, n, k, sms);
+  const int s = w4a16_splits(m, n, k, sm_count());
   return s > 1 ? (int64_t)s * m * n * 4 : 0;
 }
 
 template <int BN>
 static int launch_w4a16(const CUtensorMap& ta, const W4A16Params& p, int sms, cudaStream_t st) {
   auto kern = k_gemm_w4a16<BN>;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, WCfg<BN>::kSmem);
-    if (e != cudaSuccess) return (int)e;
-    configured = true;
-  }
+  static SmemOptIn opt_in;
+  if (int e = opt_in.ensure(kern, WCfg<BN>::kSmem)) return e;
   const int64_t items = (int64_t)((p.M + 255) / 256) * (p.N / BN) * p.splits;
   return (int)launch_chain(kern, dim3((unsigned)(items < sms ? items : sms)), dim3(WCfg<BN>::kThreads), WCfg<BN>::kSmem, st, ta, p);
 }
@@ -389,18 +383,11 @@ int launch_gemm_w4a16(const void* a, int64_t a_stride, const void* b_q, const vo
                       int64_t k, void* out, int64_t out_stride, void* workspace, int64_t workspace_bytes, int32_t* status,
                       cudaStream_t st) {
   if (m == 0) return 0;
-  static const int forced = [] {
-    const char* v = getenv("B200MOE_W4A16_TILE_N");      // timing experiments only
-    return v ? atoi(v) : 0;
-  }();
-  int bn = (n % 256 == 0 && m > 128) ? 256 : 128;
-  if ((forced == 128 || forced == 256) && n % forced == 0) bn = forced;
+  const int bn = (n % 256 == 0 && m > 128) ? 256 : 128;
   CUtensorMap ta;
   int rc = make_operand_map(&ta, a, (uint64_t)m, (uint64_t)k * 2, 256, (uint64_t)a_stride * 2);
   if (rc) return rc;
-  int dev = 0, sms = 0;
-  cudaGetDevice(&dev);
-  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int sms = sm_count();
   W4A16Params p;
   p.b_q = (const uint8_t*)b_q;
   p.b_sf = (const uint8_t*)b_sf;
@@ -424,7 +411,7 @@ int launch_gemm_w4a16(const void* a, int64_t a_stride, const void* b_q, const vo
   if (rc || p.splits == 1) return rc;
   const int64_t quads = m * n / 4;
   const int64_t blocks = (quads + 255) / 256;
-  return (int)launch_chain(k_w4a16_reduce, dim3((unsigned)(blocks < 148 * 8 ? blocks : 148 * 8)), dim3(256), 0, st, (const float*)p.partial,
+  return (int)launch_chain(k_w4a16_reduce, dim3((unsigned)(blocks < (int64_t)sms * 8 ? blocks : (int64_t)sms * 8)), dim3(256), 0, st, (const float*)p.partial,
                            alpha, p.splits, m, n, (__nv_bfloat16*)out, out_stride);
 }
 

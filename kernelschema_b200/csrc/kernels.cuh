@@ -5,6 +5,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 namespace b200 {
 
 enum { kGemmDense = 0, kGemmFc1 = 1, kGemmFc2 = 2 };
@@ -12,6 +14,29 @@ enum { kGemmDense = 0, kGemmFc1 = 1, kGemmFc2 = 2 };
 // True unless the environment says B200MOE_PDL=0 (read once): launches carry the programmatic-stream-serialization
 // attribute, so consecutive kernels of the layer overlap launch latency and prologue (see pdl_wait in ptx.cuh).
 bool pdl_enabled();
+
+// Multiprocessors of the current device (queried once per device, then cached).
+int sm_count();
+
+// cudaFuncAttributeMaxDynamicSharedMemorySize belongs to a (kernel, device) pair: one of these per kernel remembers on
+// which devices the opt-in has been made, so that a process driving several GPUs configures each of them.
+struct SmemOptIn {
+  std::atomic<unsigned long long> done{0};
+  template <class Kernel>
+  int ensure(Kernel kern, int bytes) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    const unsigned long long bit = 1ull << (dev & 63);
+    if (dev < 64 && (done.load(std::memory_order_acquire) & bit)) return 0;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 64) done.fetch_or(bit, std::memory_order_release);
+    return 0;
+  }
+  // which devices have been configured (bit d = device d); for tests of the bookkeeping
+  unsigned long long mask() const { return done.load(std::memory_order_acquire); }
+};
 
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_chain(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
@@ -70,7 +95,6 @@ struct GemmParams {
   int act_type;                 // 3 = SwiGLU form gate*sigmoid(alpha*gate)*(up+beta); 10 = SiTU
   const float* out_scale;       // per expert multiplier of the FC2 accumulator (null = 1)
   float dense_alpha;
-  int dbg;                      // timing experiments only: 1 = no loads, 2 = no MMA/cp, 4 = no scale-factor cp, 8 = no epilogue stores
   int32_t* status;              // device word; first non-zero code sticks (bounded waits report here)
 };
 

@@ -19,11 +19,16 @@ DEV size_t sf_tiled_offset(int64_t row, int64_t blk, int64_t chunks_per_row) {
          (size_t)(blk & 3);
 }
 
-// GLOBAL_SCALE = false also serves power-of-two global scales: dividing by 2^k is exact, so
-// quantize(x, 2^k) == quantize(x * 2^-k, 1) bit for bit and `prescale` = 2^-k is applied to the loaded values.
-template <bool GLOBAL_SCALE>
+// Quotients x / (stored * gs) without sixteen IEEE divisions per block. With d = RN(stored * gs) (what the reference
+// divides by), r = RN(1 / d), q0 = RN(x * r), the residual rem = x - q0 * d is exact in one fma (q0 is within 1.5 ulp of
+// x / d and x has only 8 significant bits), and q1 = RN(q0 + rem * r) is the correctly rounded quotient (Markstein's
+// residual correction with a correctly rounded reciprocal). The E2M1 code only depends on the side of seven thresholds
+// the quotient lies on, so a last-bit error could matter only when x / d is within an ulp of a threshold; the test suite
+// sweeps every bf16 value against every E4M3 scale x a set of global scales and compares the codes with true division.
+// EXACT_DIV selects IEEE division instead (global scales so small or large that the residual could leave the normal range).
+template <bool EXACT_DIV>
 __global__ void __launch_bounds__(256) k_quantize_nvfp4(const __nv_bfloat16* __restrict__ x, int64_t rows, int64_t cols,
-                                                        int64_t row_stride, float gs, float prescale, uint8_t* __restrict__ payload,
+                                                        int64_t row_stride, float gs, uint8_t* __restrict__ payload,
                                                         uint8_t* __restrict__ scales, int sf_layout) {
   // One block walks rows, its threads walk the 16-element blocks of a row: no integer division anywhere.
   const int blocks_per_row = (int)(cols >> 4);
@@ -41,21 +46,18 @@ __global__ void __launch_bounds__(256) k_quantize_nvfp4(const __nv_bfloat16* __r
     for (int i = 0; i < 8; ++i) {
       v[2 * i] = __uint_as_float(w[i] << 16);
       v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
-      if (!GLOBAL_SCALE) { v[2 * i] *= prescale; v[2 * i + 1] *= prescale; }
     }
     float peak = 0.f;
 #pragma unroll
     for (int i = 0; i < 16; ++i) peak = fmaxf(peak, fabsf(v[i]));
-    peak = fmaxf(peak, 9.5367431640625e-07f);                       // clamp_min(2^-20)
+    peak = fmaxf(peak, 9.5367431640625e-07f);                       // clamp_min(2^-20), before the global scale
     float scale = __fdiv_rn(peak, 6.0f);
-    if (GLOBAL_SCALE) scale = __fdiv_rn(scale, gs);
+    if (gs != 1.0f) scale = __fdiv_rn(scale, gs);
     scale = fminf(fmaxf(scale, 0.001953125f), 448.0f);               // clamp(2^-9, 448)
     const uint32_t sbyte = cvt_e4m3(scale);
-    const float sf = e4m3_to_f32(sbyte);
+    const float d = __fmul_rn(e4m3_to_f32(sbyte), gs);               // the reference divides by stored * gs
     uint32_t packed[2];
-    if (GLOBAL_SCALE) {
-      // The divisor stored*gs is an arbitrary fp32 number: only the correctly rounded quotient matches the reference.
-      const float d = __fmul_rn(sf, gs);
+    if (EXACT_DIV) {
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         uint32_t word = 0;
@@ -65,10 +67,7 @@ __global__ void __launch_bounds__(256) k_quantize_nvfp4(const __nv_bfloat16* __r
         packed[h] = word;
       }
     } else {
-      // x is bf16 (8 significant bits) and sf has 4, so x/sf is either exactly on an E2M1 midpoint or at least
-      // 2^-9 (relative) away from it. One residual-corrected reciprocal multiply is exact on the ties and
-      // accurate to ~2^-23 elsewhere, hence yields the same codes as the IEEE division the reference performs.
-      const float r = __frcp_rn(sf);
+      const float r = __frcp_rn(d);
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         uint32_t word = 0;
@@ -76,8 +75,8 @@ __global__ void __launch_bounds__(256) k_quantize_nvfp4(const __nv_bfloat16* __r
         for (int i = 0; i < 4; ++i) {
           const float a = v[8 * h + 2 * i], b = v[8 * h + 2 * i + 1];
           float qa = a * r, qb = b * r;
-          qa = copysignf(fmaf(fmaf(-qa, sf, a), r, qa), a);     // keep -0 and negative underflow: they encode as 8
-          qb = copysignf(fmaf(fmaf(-qb, sf, b), r, qb), b);
+          qa = copysignf(fmaf(fmaf(-qa, d, a), r, qa), a);     // keep -0 and negative underflow: they encode as 8
+          qb = copysignf(fmaf(fmaf(-qb, d, b), r, qb), b);
           word |= cvt_e2m1x2(qa, qb) << (8 * i);
         }
         packed[h] = word;
@@ -113,14 +112,15 @@ int launch_quantize_nvfp4(const void* x, int64_t rows, int64_t cols, int64_t row
   const int passes = (bpr + 255) / 256;
   int threads = ((bpr + passes - 1) / passes + 31) / 32 * 32;
   if (threads > 256) threads = 256;
-  const int64_t blocks = rows < 148LL * 32 ? rows : 148LL * 32;
-  int exp2 = 0;
-  const bool pow2 = frexpf(gs, &exp2) == 0.5f && exp2 > -100 && exp2 < 100;     // gs = 2^(exp2-1): exact pre-scaling
-  if (pow2)
+  const int64_t resident = (int64_t)sm_count() * 32;
+  const int64_t blocks = rows < resident ? rows : resident;
+  // stored * gs stays a normal number with room for the residual of a bf16 numerator inside 2^-40 .. 2^40
+  const bool fast = gs >= 0x1p-40f && gs <= 0x1p40f;
+  if (fast)
     return (int)launch_chain(k_quantize_nvfp4<false>, dim3((unsigned)blocks), dim3(threads), 0, st, (const __nv_bfloat16*)x, rows, cols,
-                             row_stride, gs, ldexpf(1.0f, 1 - exp2), (uint8_t*)payload, (uint8_t*)scales, sf_layout);
+                             row_stride, gs, (uint8_t*)payload, (uint8_t*)scales, sf_layout);
   return (int)launch_chain(k_quantize_nvfp4<true>, dim3((unsigned)blocks), dim3(threads), 0, st, (const __nv_bfloat16*)x, rows, cols,
-                           row_stride, gs, 1.0f, (uint8_t*)payload, (uint8_t*)scales, sf_layout);
+                           row_stride, gs, (uint8_t*)payload, (uint8_t*)scales, sf_layout);
 }
 
 int launch_sf_to_tiles(const void* src, int64_t rows, int64_t blocks_per_row, void* dst, cudaStream_t st) {
@@ -128,7 +128,7 @@ int launch_sf_to_tiles(const void* src, int64_t rows, int64_t blocks_per_row, vo
   const int64_t total = rows_pad * (blocks_per_row >> 2);
   if (total == 0) return 0;
   int64_t blocks = (total + 255) / 256;
-  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (blocks > (int64_t)sm_count() * 16) blocks = (int64_t)sm_count() * 16;
   k_sf_to_tiles<<<(unsigned)blocks, 256, 0, st>>>((const uint8_t*)src, rows, blocks_per_row, (uint8_t*)dst);
   return (int)cudaGetLastError();
 }

@@ -411,7 +411,9 @@ constexpr int kStaticMaxExperts = 264;     // routed + shared experts
 static __device__ __align__(256) int32_t g_route_scratch[kStaticMaxBlocks * kStaticMaxExperts];
 
 constexpr int kMaxDevices = 64;
-static int32_t* g_route_scratch_ptr[kMaxDevices];   // device address of g_route_scratch, per device, filled on first use
+// device address of g_route_scratch, per device, filled on first use; atomic so that host threads making a device's first
+// call at the same time both store the same value without a data race
+static std::atomic<int32_t*> g_route_scratch_ptr[kMaxDevices];
 
 int launch_route_map_static(const int32_t* ids, const float* scores, int64_t T, int K, int S, int E, int expert_offset,
                             RouteMapBuffers b, cudaStream_t st) {
@@ -423,15 +425,17 @@ int launch_route_map_static(const int32_t* ids, const float* scores, int64_t T, 
   cudaError_t err = cudaGetDevice(&dev);
   if (err != cudaSuccess) return (int)err;
   if (dev < 0 || dev >= kMaxDevices) return 771;
-  if (!g_route_scratch_ptr[dev]) {
+  int32_t* scratch = g_route_scratch_ptr[dev].load(std::memory_order_acquire);
+  if (!scratch) {
     // The array's name is only a host-side handle: kernels need its device address, looked up once per device
     // with that device current.
     void* p = nullptr;
     err = cudaGetSymbolAddress(&p, g_route_scratch);
     if (err != cudaSuccess) return (int)err;
-    g_route_scratch_ptr[dev] = (int32_t*)p;
+    scratch = (int32_t*)p;
+    g_route_scratch_ptr[dev].store(scratch, std::memory_order_release);
   }
-  b.block_hist = g_route_scratch_ptr[dev];
+  b.block_hist = scratch;
   return launch_route_map(ids, scores, 0, T, K, S, E, expert_offset, b, st);
 }
 

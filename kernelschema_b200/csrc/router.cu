@@ -288,15 +288,9 @@ int launch_router_logits_tc(const void* x, const void* w, int64_t T, int H, int 
   if (rc) return rc;
   rc = make_operand_map(&tw, w, (uint64_t)E, (uint64_t)H * 2, (uint32_t)e_pad);
   if (rc) return rc;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(k_router_logits_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, kLgSmem);
-    if (e != cudaSuccess) return (int)e;
-    configured = true;
-  }
-  int dev = 0, sms = 0;
-  cudaGetDevice(&dev);
-  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  static SmemOptIn opt_in;
+  if (int e = opt_in.ensure(k_router_logits_tc, kLgSmem)) return e;
+  const int sms = sm_count();
   const int n_tiles = (int)((T + 127) / 128);
   return (int)launch_chain(k_router_logits_tc, dim3(n_tiles < sms ? n_tiles : sms), dim3(192), kLgSmem, st, tx, tw, (int)T, H, E, e_pad,
                            logits, status);

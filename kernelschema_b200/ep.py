@@ -158,9 +158,7 @@ class ExpertParallelMoE:
         # GEMM grids then stay off `sm_margin` SMs so that the collective's kernels find room next to them. Measured on
         # B200s it does not pay (2 ranks: 3.78 against 3.22 ms; 8 ranks: 5.37 against 5.16 ms per step): every half re-reads
         # this rank's expert weights and the GEMMs lose the SMs they leave free. Off unless asked for.
-        import os
-        env = os.environ.get("B200MOE_EP_MICRO_BATCHES")
-        self.micro_batches = int(env) if env else (micro_batches or 1)
+        self.micro_batches = micro_batches or 1
         self.sm_margin = (sm_margin if sm_margin is not None else 16) if self.micro_batches > 1 else 0
         self._routed = self._shared = self._plan = None
         self._plans = {}

@@ -39,8 +39,11 @@ def _ptr(t) -> int | None:
     return None if t is None else t.data_ptr()
 
 
-def nvfp4_quantize(x: torch.Tensor, global_scale: float = 1.0, tiled_scales: bool = False):
+def nvfp4_quantize(x: torch.Tensor, global_scale: float = 1.0, tiled_scales: bool = False, out=None):
     """bf16 [rows, cols] -> (payload uint8 [rows, cols/2], scales float8_e4m3fn).
+
+    ``out = (payload, scales)`` reuses caller-owned buffers of those shapes (uint8; a steady-state loop then allocates
+    nothing); padding rows of a tiled scale buffer are left as they are.
 
     Same bytes as the reference generator's ``quantize(value, 16)`` (problem/input.py:53-71) and, with a
     global scale, as the dense GEMM problem's ``quantize`` (bf16_nvfp4_gemm/problem/input.py:40-64).
@@ -53,11 +56,21 @@ def nvfp4_quantize(x: torch.Tensor, global_scale: float = 1.0, tiled_scales: boo
     if x.stride(1) != 1:
         x = x.contiguous()
     rows, cols = x.shape
-    payload = torch.empty((rows, cols // 2), dtype=torch.uint8, device=x.device)
-    if tiled_scales:
-        scales = torch.zeros(((rows + 127) // 128, cols // 64, 32, 16), dtype=torch.uint8, device=x.device)
+    if out is not None:
+        payload, scales = out
+        _need_cuda(payload, scales)
+        want = ((rows + 127) // 128 * (cols // 64) * 512) if tiled_scales else rows * (cols // 16)
+        if payload.dtype != torch.uint8 or payload.numel() != rows * (cols // 2) or not payload.is_contiguous():
+            raise ValueError("out[0] must be a contiguous uint8 tensor of rows * cols / 2 bytes")
+        scales = scales.view(torch.uint8) if scales.dtype != torch.uint8 else scales
+        if scales.numel() != want or not scales.is_contiguous():
+            raise ValueError("out[1] must be a contiguous 1-byte tensor of the scale layout's size")
     else:
-        scales = torch.empty((rows, cols // 16), dtype=torch.uint8, device=x.device)
+        payload = torch.empty((rows, cols // 2), dtype=torch.uint8, device=x.device)
+        if tiled_scales:
+            scales = torch.zeros(((rows + 127) // 128, cols // 64, 32, 16), dtype=torch.uint8, device=x.device)
+        else:
+            scales = torch.empty((rows, cols // 16), dtype=torch.uint8, device=x.device)
     lib = _lib.load()
     _lib.check(lib.b200moe_quantize_nvfp4(x.data_ptr(), rows, cols, x.stride(0), float(global_scale), payload.data_ptr(),
                                           scales.data_ptr(), _lib.SF_TILED if tiled_scales else _lib.SF_ROW_MAJOR, _stream()),
@@ -76,25 +89,36 @@ def scales_to_tiles(scales: torch.Tensor) -> torch.Tensor:
     return out
 
 
-def route_topk(logits: torch.Tensor, top_k: int, bias: torch.Tensor | None = None):
-    """fp32 logits [T, E] -> (ids int32 [T, K], weights fp32 [T, K]); problem/input.py:35-36."""
+def route_topk(logits: torch.Tensor, top_k: int, bias: torch.Tensor | None = None, out=None):
+    """fp32 logits [T, E] -> (ids int32 [T, K], weights fp32 [T, K]); problem/input.py:35-36.
+    ``out = (ids, weights)`` reuses caller-owned contiguous buffers."""
     _need_cuda(logits, bias)
     lg = logits.contiguous().float()
     t, e = lg.shape
-    ids = torch.empty((t, top_k), dtype=torch.int32, device=lg.device)
-    w = torch.empty((t, top_k), dtype=torch.float32, device=lg.device)
+    if out is not None:
+        ids, w = out
+        _need_cuda(ids, w)
+        if ids.dtype != torch.int32 or w.dtype != torch.float32 or tuple(ids.shape) != (t, top_k) or tuple(w.shape) != (t, top_k) \
+                or not ids.is_contiguous() or not w.is_contiguous():
+            raise ValueError("out must be (int32 [T, K], float32 [T, K]), contiguous")
+    else:
+        ids = torch.empty((t, top_k), dtype=torch.int32, device=lg.device)
+        w = torch.empty((t, top_k), dtype=torch.float32, device=lg.device)
     b = None if bias is None else bias.contiguous().float()
     _lib.check(_lib.load().b200moe_route_topk(lg.data_ptr(), _ptr(b), t, e, top_k, ids.data_ptr(), w.data_ptr(), _stream()),
                "b200moe_route_topk")
     return ids, w
 
 
-def router_logits(x: torch.Tensor, gate_weight: torch.Tensor) -> torch.Tensor:
-    """bf16 x [T, H] times bf16 gate [E, H]^T -> fp32 logits [T, E]."""
-    _need_cuda(x, gate_weight)
+def router_logits(x: torch.Tensor, gate_weight: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """bf16 x [T, H] times bf16 gate [E, H]^T -> fp32 logits [T, E] (``out``: caller-owned contiguous fp32 [T, E])."""
+    _need_cuda(x, gate_weight, out)
     x = x.contiguous()
     g = gate_weight.contiguous()
-    out = torch.empty((x.shape[0], g.shape[0]), dtype=torch.float32, device=x.device)
+    if out is None:
+        out = torch.empty((x.shape[0], g.shape[0]), dtype=torch.float32, device=x.device)
+    elif out.dtype != torch.float32 or tuple(out.shape) != (x.shape[0], g.shape[0]) or not out.is_contiguous():
+        raise ValueError("out must be a contiguous float32 [T, E] tensor")
     _lib.check(_lib.load().b200moe_router_logits(x.data_ptr(), g.data_ptr(), x.shape[0], x.shape[1], g.shape[0], out.data_ptr(),
                                                  _stream()), "b200moe_router_logits")
     return out

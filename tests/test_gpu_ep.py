@@ -71,3 +71,31 @@ def test_expert_parallel_two_gpus_pipelined():
         results = mgr.dict()
         mp.spawn(_worker, args=(2, _free_port(), results, 384, 2), nprocs=2, join=True)
         assert sorted(results.keys()) == [0, 1]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_one_process_drives_two_devices():
+    """The dynamic-shared-memory opt-in of the large kernels belongs to a (kernel, device) pair: a process that runs the
+    layer, the dense GEMMs and the router on cuda:0 and then on cuda:1 must succeed on both."""
+    import kernelschema_b200 as ks
+    import sys
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from helpers import assert_layer_parity, make_moe_case
+    from gpu_util import run_model
+    from oracle import nvfp4_oracle as o
+    p = make_moe_case(5, 200, 512, 256, 8, 2, shared=1)
+    want = o.moe_expected(p)
+    for dev in (0, 1):
+        with torch.cuda.device(dev):
+            got, _, model = run_model(p)
+            assert_layer_parity(got, want, f"device {dev}")
+            x = torch.randn(256, 512, device="cuda").to(torch.bfloat16)
+            g = (torch.randn(64, 512, device="cuda") * 0.02).to(torch.bfloat16)
+            lg = ks.router_logits(x, g)
+            assert torch.allclose(lg, x.float() @ g.float().t(), atol=1e-3, rtol=1e-3)
+            aq, asf = ks.nvfp4_quantize(x, 1.0, tiled_scales=True)
+            bq, bsf = ks.nvfp4_quantize(g.repeat(2, 1), 1.0, tiled_scales=True)
+            y = ks.mm_nvfp4(aq, asf, bq, bsf)
+            y2 = ks.mm_bf16_nvfp4(x, *[t.view(torch.uint8) for t in ks.nvfp4_quantize(g.repeat(2, 1), 1.0)])
+            torch.cuda.synchronize()
+            assert bool(torch.isfinite(y.float()).all()) and bool(torch.isfinite(y2.float()).all())

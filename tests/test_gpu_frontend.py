@@ -48,6 +48,75 @@ def test_quantize_matches_oracle(rows, cols, scale):
         assert np.array_equal(ks.scales_to_tiles(ks.nvfp4_quantize(x.cuda())[1]).cpu().numpy(), ref_t)
 
 
+def _torch_quantize_true_division(x, gs):
+    """The reference quantize() (gemm/dense/bf16_nvfp4_gemm/problem/input.py:40-64) in torch ops on the device with
+    tensor / tensor divisions only (IEEE round-to-nearest; tensor / python-scalar would multiply by a reciprocal)."""
+    dev = x.device
+    groups = x.float().view(-1, 16)
+    t = lambda v: torch.tensor(v, dtype=torch.float32, device=dev)
+    peak = groups.abs().amax(-1).clamp_min(2.0 ** -20)
+    scale = torch.div(torch.div(peak, t(6.0)), t(gs)) if gs != 1.0 else torch.div(peak, t(6.0))
+    stored = scale.clamp(2.0 ** -9, 448.0).to(torch.float8_e4m3fn)
+    d = stored.float() * t(gs)
+    q = torch.div(groups, d[:, None])
+    mag = q.abs()
+    code = torch.zeros_like(mag, dtype=torch.int32)
+    for i, mid in enumerate((0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0)):
+        code += (mag > mid if i % 2 == 0 else mag >= mid).int()
+    code |= torch.signbit(q).int() << 3
+    code = code.view(-1, 8, 2)
+    return (code[..., 0] | (code[..., 1] << 4)).to(torch.uint8), stored.view(torch.uint8)
+
+
+@pytest.mark.parametrize("gs", [1.0, 2.0 ** -9, 3.0, 0.7431, 1.0 / (6 * 448) * 5.3, 1.9999999, 1.0000001, 12.375e-3, 6.1e-5, 977.25])
+def test_quantize_reciprocal_path_equals_true_division_all_bf16(gs):
+    """Every finite bf16 value as a numerator against every E4M3 block scale (the block's first element sets the scale)
+    x a set of global scales incl. mantissas of all ones and 1 + ulp: the residual-corrected reciprocal multiply of the
+    kernel must give the codes of IEEE division."""
+    import kernelschema_b200 as ks
+    dev = "cuda"
+    bits = torch.arange(0, 65536, dtype=torch.int32, device=dev).to(torch.int16)
+    vals = bits.view(torch.bfloat16).float()
+    finite = torch.isfinite(vals)
+    codes = torch.arange(1, 127, dtype=torch.uint8, device=dev)
+    peaks = (codes.view(torch.float8_e4m3fn).float() * 6.0 * gs).to(torch.bfloat16)
+    peaks = peaks[torch.isfinite(peaks.float()) & (peaks.float() > 0)]
+    rows = []
+    for pk in peaks.unique():
+        cand = vals[finite & (vals.abs() <= pk.float())].to(torch.bfloat16)
+        pad = (-cand.numel()) % 15
+        cand = torch.cat([cand, cand.new_zeros(pad)]).view(-1, 15)
+        rows.append(torch.cat([pk.expand(cand.shape[0], 1), cand], 1))
+    x = torch.cat(rows).reshape(-1)
+    x = torch.cat([x, x.new_zeros((-x.numel()) % 1024)]).view(-1, 1024)
+    q, s = ks.nvfp4_quantize(x, gs)
+    rq, rs = _torch_quantize_true_division(x, gs)
+    assert torch.equal(s.view(torch.uint8).reshape(-1), rs)
+    assert torch.equal(q.reshape(-1, 8), rq), int((q.reshape(-1, 8) != rq).sum())
+    # the torch formulation itself against the numpy oracle (pinned by the reference's fixtures) on a slice
+    sub = x[:: max(1, x.shape[0] // 64)]
+    oq, os_ = o.quantize(sub.float().cpu().numpy(), 16, gs)
+    sq, ss = _torch_quantize_true_division(sub.contiguous(), gs)
+    assert np.array_equal(sq.reshape(sub.shape[0], -1).cpu().numpy(), oq) and np.array_equal(ss.reshape(sub.shape[0], -1).cpu().numpy(), os_)
+
+
+def test_quantize_tiny_global_scale_and_tiny_blocks():
+    """Blocks below the 2^-20 peak floor (all-zero, |x| < 1e-6) with small power-of-two and general global scales: the
+    floor applies to the unscaled peak (problem/input.py of the dense operator, lines 40-64)."""
+    import kernelschema_b200 as ks
+    x = torch.zeros(4, 64, dtype=torch.float32)
+    x[0, 16:32] = torch.linspace(-9e-7, 9e-7, 16)
+    x[1, :16] = torch.linspace(-3e-7, 5e-7, 16)
+    x[2] = torch.randn(64, generator=torch.Generator().manual_seed(1)) * 1e-5
+    x[3, 48:] = 2.0 ** -21
+    xb = x.to(torch.bfloat16)
+    for gs in (2.0 ** -16, 2.0 ** -14, 2.0 ** -20, 3.3e-5, 1.0):
+        q, s = ks.nvfp4_quantize(xb.cuda(), gs)
+        oq, os_ = o.quantize(xb.float().numpy(), 16, gs)
+        assert np.array_equal(s.view(torch.uint8).cpu().numpy(), os_), gs
+        assert np.array_equal(q.cpu().numpy(), oq), gs
+
+
 def test_quantize_strided_rows():
     import kernelschema_b200 as ks
     x = torch.randn(50, 512, device="cuda").to(torch.bfloat16)

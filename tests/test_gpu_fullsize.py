@@ -1,4 +1,4 @@
-"""The layer at BASELINE's full sizes (Qwen3-30B-A3B T=16384; DeepSeek-V3 T=8192 + shared expert, Zipf routing),
+"""The layer at the benchmark's full sizes (Qwen3-30B-A3B T=16384; DeepSeek-V3 T=8192 + shared expert, Zipf routing),
 checked through size-independent properties and a handful of sampled tokens against the oracle.
 
 * token permutation: rows are independent, so permuting the tokens permutes the output bit for bit;

@@ -44,6 +44,17 @@ def test_dense_gemm_matches_oracle(m, n, k, tile_n):
     assert r["max_abs"] <= 2e-2 * r["rms"], r
 
 
+@pytest.mark.parametrize("m,n,k,tile_n", [(128 * 600, 128, 256, 128), (128 * 400, 256, 512, 256), (256 * 300, 256, 512, 512),
+                                          (128 * 330, 512, 768, 256)])
+def test_dense_gemm_many_items_per_cta(m, n, k, tile_n):
+    """Short K and several work items per CTA (or CTA pair): the stage ring and the per-stage scale-factor buffers wrap
+    across tiles, the accumulator phases flip and the tile-table entries are prefetched one item ahead."""
+    got, ref = _dense_case(m, n, k, seed=7 + tile_n, tile_n=tile_n)
+    r = compare_outputs(got, ref)
+    assert r["rel_l2"] <= 2e-3 and r["max_abs"] <= 2e-2 * r["rms"], r
+    assert (o.bf16_bits(got) != o.bf16_bits(ref)).mean() <= 0.05
+
+
 def test_dense_gemm_golden_weights():
     """B operand and scales from the reference's dense problem generator; A quantised on the device."""
     import kernelschema_b200 as ks
@@ -62,7 +73,7 @@ def test_dense_gemm_golden_weights():
 
 
 def test_dense_gemm_linearity_full_size():
-    """Size-independent property at a BASELINE size: scaling A by 2 (exact in bf16 and in the block scales) doubles the output."""
+    """Size-independent property at a benchmark size: scaling A by 2 (exact in bf16 and in the block scales) doubles the output."""
     import kernelschema_b200 as ks
     gen = torch.Generator(device="cuda").manual_seed(3)
     a = torch.randn(4096, 4096, device="cuda", generator=gen).to(torch.bfloat16)

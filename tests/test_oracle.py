@@ -98,6 +98,37 @@ def test_moe_layer_matches_reference(name):
     assert (o.bf16_bits(out) != g["out"]).mean() <= 0.02, (o.bf16_bits(out) != g["out"]).mean()
 
 
+def test_moe_c1_shape_matches_reference_output():
+    """The small benchmark shape (T=256, H=1024, I=512, E=8, top-2, seed 0): inputs regenerated with the same torch CPU
+    generator calls and the oracle quantiser, pinned by the digests stored beside the reference's own output."""
+    import hashlib
+    torch = pytest.importorskip("torch")
+    g = load_golden("moe_c1")
+    t, h, i, e, k = 256, 1024, 512, 8, 2
+    torch.manual_seed(0)
+    x = torch.randn(t, h).to(torch.bfloat16)
+    torch.randn(e, h)                                  # the gate matrix: drawn to keep the generator in step
+    w1 = (torch.randn(e, 2 * i, h) * 0.02).to(torch.bfloat16)
+    w2 = (torch.randn(e, h, i) * 0.02).to(torch.bfloat16)
+    hq, hs = o.quantize(x.float().numpy())
+    q1, s1 = o.prepare_weights(*o.quantize(w1.float().numpy()), True)
+    q2, s2 = o.prepare_weights(*o.quantize(w2.float().numpy()), False)
+    made = dict(hidden_states=hq, hidden_states_scale=hs, gemm1_weights=q1, gemm1_weights_scale=s1, gemm2_weights=q2,
+                gemm2_weights_scale=s2)
+    want = dict(zip(g["digest_names"].tolist(), g["digest_values"].tolist()))
+    for name, arr in made.items():
+        assert hashlib.sha256(np.ascontiguousarray(arr).tobytes()).hexdigest() == want[name], name
+    ids, scores = o.route_topk(g["logits"], k)
+    assert np.array_equal(ids, g["ids"])
+    assert np.abs(scores - g["scores"]).max() <= 4 * np.finfo(np.float32).eps
+    p = dict(made, topk_ids=(g["ids"], g["scores"]), gemm1_alpha=np.ones(e, np.float32), gemm1_beta=np.zeros(e, np.float32),
+             gemm1_clamp_limit=None, num_experts=e, top_k=k, intermediate_size=i, activation_type=3)
+    out = o.moe_expected(p)
+    r = compare_outputs(out, o.bf16_from_bits(g["out"]))
+    assert r["max_abs"] <= 2e-2 * r["rms"] and r["rel_l2"] <= 2e-3, r
+    assert (o.bf16_bits(out) != g["out"]).mean() <= 0.02
+
+
 def test_dense_matches_reference():
     g = load_golden("dense")
     out = o.dense_expected(o.bf16_from_bits(g["a"]), g["b"], g["b_descale"], float(g["alpha"][0]))

@@ -68,6 +68,16 @@ def test_noalloc_route_map_equals_regular_entry_point_twice():
         live[ws["row_of"][:tt][ws["row_of"][:tt] >= 0].long()] = True
         assert torch.equal(got["tok_of_row"][:rows][live], ws["tok_of_row"][:rows][live])
         assert torch.equal(got["weight_of_row"][:rows][live], ws["weight_of_row"][:rows][live])   # exact: copied values
+        # and directly against the CPU oracle's route map (shared experts: one extra always-routed id per token)
+        from oracle import nvfp4_oracle as o
+        ref = o.route_map(ids, e, 128, expert_offset=offset, shared_experts=shared)
+        assert np.array_equal(got["counts"].cpu().numpy(), ref["counts"])
+        assert np.array_equal(got["seg_start"].cpu().numpy(), ref["seg_start"])
+        assert np.array_equal(got["row_of"].cpu().numpy(), ref["row_of"])
+        assert np.array_equal(got["tile_rows"][:n_tiles].cpu().numpy(), ref["tile_rows"])
+        assert np.array_equal(got["tile_expert"][:n_tiles].cpu().numpy(), ref["tile_expert"])
+        live_rows = ref["row_of"][ref["row_of"] >= 0]
+        assert np.array_equal(got["tok_of_row"].cpu().numpy()[live_rows], ref["tok_of_row"][live_rows])
     layer.close()
 
 
