@@ -658,7 +658,7 @@ def run_gpu(args, wl):
         stage["hbm_frac_of_measured"] = stage["hbm_algorithmic_gbs"] / pk["hbm_gbs"]
         stage["fc2_tflops"] = flops / 3.0 / (stage["fc2"] * 1e-3) / 1e12
         roof = tensor_roofline(achieved, pk, clocks, kernel="k_gemm_nvfp4<FC1>",
-                               traffic=FC1_DRAM_TRAFFIC.get(args.workload) if args.tokens is None and args.zipf is None else None,
+                               traffic=FC1_DRAM_TRAFFIC.get(args.workload) if args.tokens is None and args.zipf is None and args.experts is None else None,
                                traffic_unit="bytes of DRAM traffic per FC1 launch (ncu capture summarised under profiles/)",
                                algorithmic_bytes=fc1_bytes, layer_frac_of_nominal_fp4=tflops / FP4_NOMINAL_TFLOPS,
                                fc1_hbm_gbs=fc1_bytes / (stage["fc1"] * 1e-3) / 1e9,
@@ -673,7 +673,7 @@ def run_gpu(args, wl):
                 if isinstance(sub[name], dict):
                     sub[name]["wall_s"] = round(time.perf_counter() - t0, 1)
 
-            if args.workload == "dsv3" and args.tokens is None:
+            if args.workload == "dsv3" and args.tokens is None and args.experts is None:
                 guarded("dsv3_decode_T64", lambda: sub_layer_record("dsv3", 64, args, device, pk, L=L))
                 guarded("dsv3_decode_T256", lambda: sub_layer_record("dsv3", 256, args, device, pk, L=L))
                 guarded("qwen3_T16384", lambda: sub_layer_record("qwen3", None, args, device, pk))
@@ -724,7 +724,7 @@ def run_gpu(args, wl):
                 e2e=dict(value=tflops_e2e, unit="TFLOP/s", h2d_bytes_per_step=x_host.numel() * 2, d2h_bytes_per_step=out_host.numel() * 2,
                          ms_per_step=ms_e2e / args.steps),
                 gpu_launches=launches * args.steps, device_status=status, clocks=clocks,
-                frac_of_nominal_fp4=tflops / FP4_NOMINAL_TFLOPS)
+                frac_of_nominal_fp4_per_gpu=tflops / world / FP4_NOMINAL_TFLOPS)
     if graph_ms is not None:
         line["graph_replay"] = dict(ms_per_step=graph_ms, tokens_per_s=t / (graph_ms * 1e-3))
     if ep_stage:
@@ -887,6 +887,7 @@ def main():
     ap.add_argument("--workload", default="dsv3", choices=sorted(WORKLOADS))
     ap.add_argument("--zipf", type=float, default=None, help="override the workload's Zipf exponent of the router bias (0 = uniform)")
     ap.add_argument("--tokens", type=int, default=None, help="override the workload's tokens per GPU (e.g. 64 or 256 for decode)")
+    ap.add_argument("--experts", type=int, default=None, help="override the workload's number of routed experts (small profiler cases)")
     ap.add_argument("--graph", action="store_true", help="also time the step replayed from a CUDA graph (always done up to 2048 tokens)")
     ap.add_argument("--dense", default=None, metavar="M,N,K", help="time the dense NVFP4 GEMM of this shape instead of the layer")
     ap.add_argument("--a-bf16", action="store_true", help="with --dense: keep A in bf16 (the bf16 x NVFP4 operator) instead of quantising it")
@@ -903,6 +904,9 @@ def main():
     if args.zipf is not None:
         wl["zipf"] = args.zipf
         wl["label"] += f"_zipf{args.zipf:g}_override"
+    if args.experts is not None:
+        wl["e"] = args.experts
+        wl["label"] = re.sub(r"_E\d+", f"_E{args.experts}", wl["label"])
     if args.impl == "reference-gpu":
         run_reference_gpu(args, wl)
     elif args.impl == "reference":

@@ -22,7 +22,7 @@
 extern "C" {
 #endif
 
-#define B200MOE_ABI_VERSION 2
+#define B200MOE_ABI_VERSION 3
 
 /* Scale-factor layouts. */
 #define B200MOE_SF_ROW_MAJOR 0 /* [rows, cols/16]                                   */
@@ -200,6 +200,47 @@ int b200moe_route_map_noalloc(const int32_t* topk_ids, const float* topk_weights
                               int32_t num_shared_experts, int32_t num_experts, int32_t local_expert_offset, int32_t* counts,
                               int32_t* seg_start, int32_t* tile_expert, int32_t* tile_row0, int32_t* tile_rows, int32_t* totals,
                               int32_t* row_of, int32_t* tok_of_row, float* weight_of_row, int64_t row_capacity, void* stream);
+
+/* ---- Expert-parallel exchange over peer memory (NVLink). No counterpart in the reference operator, which has no
+ * multi-GPU path (it only carries local_expert_offset / local_num_experts, NV/candidate/nvfp4_moe.cu:595-596); the
+ * nearest model in the reference catalogue is the in-kernel exchange of OPS/moe/bf16_fused_moe/candidate/kernel.cuh
+ * (:365-395 remote stores, :1072-1168 results into the source rank's buffer, :1224-1259 release/acquire flags).
+ * One process per GPU. Each rank allocates one shared buffer, passes the 64-byte handle to its peers (any host
+ * transport) and opens theirs; kernels of this library then write peers' buffers with plain stores and only ever
+ * read or poll their own. Every device-side wait is bounded (about a second) and reports through the layer status. */
+#define B200MOE_EP_MAX_RANKS 16
+#define B200MOE_EP_CTRL_INTS (4 * B200MOE_EP_MAX_RANKS)   /* int32 words of one control block */
+#define B200MOE_EP_FLAG_DISPATCH (2 * B200MOE_EP_MAX_RANKS) /* word offset of the "rows have landed" step counters */
+#define B200MOE_EP_FLAG_RETURN (3 * B200MOE_EP_MAX_RANKS)   /* word offset of the "results have landed" step counters */
+typedef struct {
+  int32_t world, rank;
+  void* recv[B200MOE_EP_MAX_RANKS];    /* [d]: this rank's region (seg_len rows) inside rank d's receive buffer */
+  int32_t* ctrl[B200MOE_EP_MAX_RANKS]; /* [d]: rank d's control block (B200MOE_EP_CTRL_INTS words, zero before step 1) */
+  void* ret[B200MOE_EP_MAX_RANKS];     /* [s]: rank s's return buffer, bf16 rows of `hidden` elements */
+} b200moe_ep_peers;
+/* cudaMalloc + clear + cudaIpcGetMemHandle (handle: 64 bytes out) / cudaIpcOpenMemHandle / close / free. */
+int b200moe_ep_shared_alloc(int64_t bytes, void** ptr, void* ipc_handle);
+int b200moe_ep_shared_open(const void* ipc_handle, void** ptr);
+int b200moe_ep_shared_close(void* ptr);
+int b200moe_ep_shared_free(void* ptr);
+/* Dispatch of step `epoch` (1, 2, ...): `plan` is a layer whose "experts" are the ranks (plus one shared slot when
+ * shared_slot != 0) and whose route map was built from b200moe_ep_visits output; one message row per (token, rank)
+ * pair goes into the destination's receive region, then the segment size, its base row in this rank's return buffer
+ * and the dispatch flag. With a shared slot, the plan's row_of[t, world] is pointed at row shared_base + t (weight 1).
+ * `counter` is one zero-initialised uint32 in this rank's memory. */
+int b200moe_ep_dispatch(b200moe_handle plan, const void* hidden_states, const void* hidden_states_scale, const int32_t* topk_ids,
+                        const float* topk_weights, int32_t num_tokens, int32_t hidden, int32_t top_k, int32_t experts_per_rank,
+                        int64_t row_bytes, const b200moe_ep_peers* peers, int32_t epoch, int32_t shared_slot, int32_t shared_base,
+                        void* counter, void* stream);
+/* Waits on the device (bounded) until flags[0..n) >= epoch; an expired wait sets status code 301 on `h`. */
+int b200moe_ep_wait(b200moe_handle h, const int32_t* flags, int32_t n, int32_t epoch, void* stream);
+/* After everything enqueued before it on `stream`: flag word `field` + rank of every peer's control block = epoch. */
+int b200moe_ep_post(const b200moe_ep_peers* peers, int32_t field, int32_t epoch, void* stream);
+/* The layer over the world * seg_len token slots of this rank's receive buffer (args->num_tokens = world * seg_len;
+ * slots past ctrl[count of the region] are ignored): as b200moe_run, except that the combine pass writes the row of
+ * slot (s, i) to row ctrl[ret_base of s] + i of rank s's return buffer instead of args->output. */
+int b200moe_run_ep(b200moe_handle h, const b200moe_args* args, const b200moe_ep_peers* peers, const int32_t* ctrl, int32_t seg_len,
+                   void* stream);
 
 /* (3)+(4) Whole layer on `stream`, asynchronous: route map, permute, FC1 + activation + NVFP4 requantise,
  * FC2, routing-weighted combine into args->output. Replaces run_pipeline of NV/candidate/nvfp4_moe.cu:9078-9363

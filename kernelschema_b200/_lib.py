@@ -11,7 +11,7 @@ import os
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libb200moe.so")
 
-ABI_VERSION = 2
+ABI_VERSION = 3
 SF_ROW_MAJOR, SF_TILED = 0, 1
 
 
@@ -31,6 +31,16 @@ class Args(C.Structure):
                 ("local_expert_offset", C.c_int32), ("direct_rows", C.c_int32), ("output", C.c_void_p),
                 ("output_stride", C.c_int64), ("hidden_states_stride", C.c_int64), ("hidden_states_scale_stride", C.c_int64),
                 ("topk_stride", C.c_int64)]
+
+
+EP_MAX_RANKS = 16
+EP_CTRL_INTS = 4 * EP_MAX_RANKS
+EP_FLAG_DISPATCH, EP_FLAG_RETURN = 2 * EP_MAX_RANKS, 3 * EP_MAX_RANKS
+
+
+class EpPeers(C.Structure):
+    _fields_ = [("world", C.c_int32), ("rank", C.c_int32), ("recv", C.c_void_p * EP_MAX_RANKS), ("ctrl", C.c_void_p * EP_MAX_RANKS),
+                ("ret", C.c_void_p * EP_MAX_RANKS)]
 
 
 class WorkspaceView(C.Structure):
@@ -68,6 +78,15 @@ SIGNATURES = {
                                   C.c_void_p]),
     "b200moe_route_map_noalloc": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32]
                                   + [C.c_void_p] * 9 + [C.c_int64, C.c_void_p]),
+    "b200moe_ep_shared_alloc": (C.c_int, [C.c_int64, C.POINTER(C.c_void_p), C.c_void_p]),
+    "b200moe_ep_shared_open": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p)]),
+    "b200moe_ep_shared_close": (C.c_int, [C.c_void_p]),
+    "b200moe_ep_shared_free": (C.c_int, [C.c_void_p]),
+    "b200moe_ep_dispatch": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32,
+                                      C.c_int32, C.c_int64, C.POINTER(EpPeers), C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
+    "b200moe_ep_wait": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p]),
+    "b200moe_ep_post": (C.c_int, [C.POINTER(EpPeers), C.c_int32, C.c_int32, C.c_void_p]),
+    "b200moe_run_ep": (C.c_int, [C.c_void_p, C.POINTER(Args), C.POINTER(EpPeers), C.c_void_p, C.c_int32, C.c_void_p]),
     "b200moe_run": (C.c_int, [C.c_void_p, C.POINTER(Args), C.c_void_p]),
     "b200moe_run_profiled": (C.c_int, [C.c_void_p, C.POINTER(Args), C.c_void_p, C.POINTER(C.c_float)]),
     "b200moe_status": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_int32)]),

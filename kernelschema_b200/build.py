@@ -13,7 +13,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libb200moe.so")
 SHIM = os.path.join(HERE, "_b200moe_shim.so")
-SOURCES = ["quantize.cu", "router.cu", "route_map.cu", "gather.cu", "finalize.cu", "gemm_nvfp4.cu", "gemm_w4a16.cu", "api.cu"]
+SOURCES = ["quantize.cu", "router.cu", "route_map.cu", "gather.cu", "finalize.cu", "gemm_nvfp4.cu", "gemm_w4a16.cu", "ep_exchange.cu", "api.cu"]
 HEADERS = ["kernels.cuh", "ptx.cuh", os.path.join("..", "..", "include", "b200moe.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
               "-Xptxas", "-v"]

@@ -167,7 +167,13 @@ int check_args(const b200moe_layer* h, const b200moe_args* a) {
   return 0;
 }
 
-int run_impl(b200moe_layer* h, const b200moe_args* a, cudaStream_t st, cudaEvent_t* ev) {
+struct EpRun {
+  EpPeers peers;
+  const int32_t* ctrl;     // this rank's control block of the step's parity
+  int seg_len;
+};
+
+int run_impl(b200moe_layer* h, const b200moe_args* a, cudaStream_t st, cudaEvent_t* ev, const EpRun* ep = nullptr) {
   const b200moe_config& c = h->cfg;
   const int T = a->num_tokens;
   if (T == 0) return 0;
@@ -175,7 +181,7 @@ int run_impl(b200moe_layer* h, const b200moe_args* a, cudaStream_t st, cudaEvent
   auto mark = [&](int i) { if (ev) cudaEventRecord(ev[i], st); };
   mark(0);
   rc = launch_route_map(a->topk_ids, a->topk_weights, a->topk_stride, T, c.top_k, c.num_shared_experts, c.num_experts,
-                        a->local_expert_offset, h->rm, st);
+                        a->local_expert_offset, h->rm, st, ep ? ep->seg_len : 0, ep ? ep->ctrl + kEpCount : nullptr);
   if (rc) return cuda_fail(rc, "route map");
   mark(1);
   // rows this call can occupy at most (every routing of T tokens fits), not the layer's capacity: sizes the permute grid
@@ -276,7 +282,10 @@ int run_impl(b200moe_layer* h, const b200moe_args* a, cudaStream_t st, cudaEvent
     mark(5);
     return 0;
   }
-  rc = launch_finalize(h->rout, h->rm.row_of, h->rm.weight_of_row, T, h->kk, c.hidden, a->output, a->output_stride, st);
+  if (ep)
+    rc = launch_finalize_ep(h->rout, h->rm.row_of, h->rm.weight_of_row, T, h->kk, c.hidden, ep->peers, ep->ctrl, ep->seg_len, st);
+  else
+    rc = launch_finalize(h->rout, h->rm.row_of, h->rm.weight_of_row, T, h->kk, c.hidden, a->output, a->output_stride, st);
   if (rc) return cuda_fail(rc, "combine");
   mark(5);
   return 0;
@@ -565,6 +574,102 @@ int b200moe_route_map_noalloc(const int32_t* ids, const float* weights, int32_t 
   b.row_capacity = row_capacity;
   return cuda_fail(launch_route_map_static(ids, weights, T, top_k, num_shared, num_experts, offset, b, (cudaStream_t)stream),
                    "route_map_noalloc");
+}
+
+static int ep_peers_in(const b200moe_ep_peers* in, EpPeers* out, const char* what) {
+  if (!in) return fail(796, "%s: null peers", what);
+  if (in->world < 1 || in->world > kEpMaxRanks || in->rank < 0 || in->rank >= in->world)
+    return fail(796, "%s: world=%d rank=%d outside 1..%d", what, in->world, in->rank, kEpMaxRanks);
+  memset(out, 0, sizeof(*out));
+  out->world = in->world;
+  out->rank = in->rank;
+  for (int i = 0; i < in->world; ++i) {
+    out->recv[i] = (uint8_t*)in->recv[i];
+    out->ctrl[i] = in->ctrl[i];
+    out->ret[i] = in->ret[i];
+  }
+  return 0;
+}
+
+int b200moe_ep_shared_alloc(int64_t bytes, void** ptr, void* ipc_handle) {
+  if (bytes <= 0 || !ptr || !ipc_handle) return fail(797, "ep_shared_alloc: bad arguments");
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size is part of the ABI");
+  void* p = nullptr;
+  cudaError_t e = cudaMalloc(&p, (size_t)bytes);
+  if (e == cudaSuccess) e = cudaMemset(p, 0, (size_t)bytes);
+  if (e == cudaSuccess) e = cudaIpcGetMemHandle((cudaIpcMemHandle_t*)ipc_handle, p);
+  if (e != cudaSuccess) {
+    if (p) cudaFree(p);
+    return cuda_fail((int)e, "ep_shared_alloc");
+  }
+  *ptr = p;
+  return 0;
+}
+
+int b200moe_ep_shared_open(const void* ipc_handle, void** ptr) {
+  if (!ipc_handle || !ptr) return fail(797, "ep_shared_open: bad arguments");
+  cudaIpcMemHandle_t hnd;
+  memcpy(&hnd, ipc_handle, sizeof(hnd));
+  return cuda_fail((int)cudaIpcOpenMemHandle(ptr, hnd, cudaIpcMemLazyEnablePeerAccess), "ep_shared_open");
+}
+
+int b200moe_ep_shared_close(void* ptr) { return ptr ? cuda_fail((int)cudaIpcCloseMemHandle(ptr), "ep_shared_close") : 0; }
+int b200moe_ep_shared_free(void* ptr) { return ptr ? cuda_fail((int)cudaFree(ptr), "ep_shared_free") : 0; }
+
+int b200moe_ep_dispatch(b200moe_handle plan, const void* hidden_states, const void* hidden_states_scale, const int32_t* ids,
+                        const float* weights, int32_t num_tokens, int32_t hidden, int32_t top_k, int32_t experts_per_rank,
+                        int64_t row_bytes, const b200moe_ep_peers* peers, int32_t epoch, int32_t shared_slot, int32_t shared_base,
+                        void* counter, void* stream) {
+  if (!plan) return fail(792, "ep_dispatch: null plan handle");
+  EpPeers pe;
+  int rc = ep_peers_in(peers, &pe, "ep_dispatch");
+  if (rc) return rc;
+  if (hidden <= 0 || hidden % 64 || top_k <= 0 || row_bytes % 16 || row_bytes < hidden / 2 + hidden / 16 + 8 * top_k)
+    return fail(793, "ep_dispatch: row_bytes must be a multiple of 16 and hold payload, scales, ids and weights");
+  if (!hidden_states || !hidden_states_scale || !ids || !weights || !counter) return fail(794, "ep_dispatch: null pointer");
+  if ((uintptr_t)hidden_states & 15) return fail(795, "ep_dispatch: payload must be 16-byte aligned");
+  if (plan->cfg.num_experts != pe.world || plan->cfg.num_shared_experts != (shared_slot ? 1 : 0))
+    return fail(798, "ep_dispatch: the plan layer must have world experts and the shared slot asked for");
+  if (num_tokens < 0 || num_tokens > plan->cfg.max_tokens || epoch < 1) return fail(798, "ep_dispatch: bad num_tokens / epoch");
+  for (int d = 0; d < pe.world; ++d)
+    if (!pe.recv[d] || !pe.ctrl[d] || ((uintptr_t)pe.recv[d] & 15)) return fail(799, "ep_dispatch: peer %d has no (aligned) buffers", d);
+  return cuda_fail(launch_ep_dispatch(hidden_states, hidden_states_scale, ids, weights, plan->rm.tok_of_row, plan->rm.tile_expert,
+                                      plan->rm.tile_rows, plan->rm.seg_start, plan->rm.totals, hidden, top_k, experts_per_rank, row_bytes,
+                                      plan->row_capacity, pe, epoch, num_tokens, shared_slot ? 1 : 0, shared_base, plan->rm.row_of,
+                                      plan->rm.weight_of_row, (unsigned int*)counter, (cudaStream_t)stream),
+                   "ep_dispatch");
+}
+
+int b200moe_ep_wait(b200moe_handle h, const int32_t* flags, int32_t n, int32_t epoch, void* stream) {
+  if (!h || !flags || n < 1 || n > 32) return fail(796, "ep_wait: bad arguments");
+  return cuda_fail(launch_ep_wait(flags, n, epoch, h->status, 301, (cudaStream_t)stream), "ep_wait");
+}
+
+int b200moe_ep_post(const b200moe_ep_peers* peers, int32_t field, int32_t epoch, void* stream) {
+  EpPeers pe;
+  int rc = ep_peers_in(peers, &pe, "ep_post");
+  if (rc) return rc;
+  if (field != kEpFlagDispatch && field != kEpFlagReturn) return fail(796, "ep_post: unknown flag field");
+  for (int d = 0; d < pe.world; ++d)
+    if (!pe.ctrl[d]) return fail(799, "ep_post: peer %d has no control block", d);
+  return cuda_fail(launch_ep_post(pe, field, epoch, (cudaStream_t)stream), "ep_post");
+}
+
+int b200moe_run_ep(b200moe_handle h, const b200moe_args* args, const b200moe_ep_peers* peers, const int32_t* ctrl, int32_t seg_len,
+                   void* stream) {
+  int rc = check_args(h, args);
+  if (rc) return rc;
+  EpRun ep;
+  rc = ep_peers_in(peers, &ep.peers, "run_ep");
+  if (rc) return rc;
+  if (!ctrl || seg_len <= 0 || seg_len % 128 || (int64_t)seg_len * ep.peers.world != args->num_tokens)
+    return fail(798, "run_ep: num_tokens must be world * seg_len with seg_len a multiple of 128");
+  if (args->direct_rows) return fail(798, "run_ep: direct_rows does not apply");
+  for (int s = 0; s < ep.peers.world; ++s)
+    if (!ep.peers.ret[s] || ((uintptr_t)ep.peers.ret[s] & 15)) return fail(799, "run_ep: peer %d has no (aligned) return buffer", s);
+  ep.ctrl = ctrl;
+  ep.seg_len = seg_len;
+  return run_impl(h, args, (cudaStream_t)stream, nullptr, &ep);
 }
 
 int b200moe_run(b200moe_handle h, const b200moe_args* args, void* stream) {

@@ -540,11 +540,16 @@ k_gemm_nvfp4_pair(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       const uint32_t a_lo0 = ((s_a >> 4) & 0x3FFF) | (1u << 16), b_lo0 = ((s_b >> 4) & 0x3FFF) | (1u << 16);
       uint32_t s = 0, ph = 0, it = 0;
       bool ok = true;
+      PROBE_DECL
       for (long long item = first; ok && item < total_items; item += stride, ++it) {
+        PROBE_T(pr_a)
         if (!mbar_wait_cluster(bar_acc_empty, (it & 1) ^ 1)) { report(p.status, 202); break; }
+        PROBE_ADD(pr_acc, pr_a)
         tc_fence_after();
         for (int ks = 0; ks < nk; ++ks) {
+          PROBE_T(pr_b)
           if (!mbar_wait(bar_sf + 8 * s, ph)) { report(p.status, 203); ok = false; break; }
+          PROBE_ADD(pr_sf, pr_b)
           tc_fence_after();
           const uint32_t sf_t = tmem + C::kSfBase + s * C::kSfCols;
           const uint32_t a_lo = a_lo0 + s * (C::kABytes >> 4), b_lo = b_lo0 + s * (C::kBBytes >> 4);
@@ -558,6 +563,7 @@ k_gemm_nvfp4_pair(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         }
         if (ok) mma_commit_pair(bar_acc_full);
       }
+      PROBE_STORE
     }
   } else {
     // ------------------------------------------------------------------ epilogue (both CTAs: own 128 rows x 256 columns)

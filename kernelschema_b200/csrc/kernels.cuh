@@ -106,8 +106,10 @@ int launch_route_topk(const float* logits, const float* bias, int64_t T, int E, 
 int launch_router_logits(const void* x, const void* w, int64_t T, int H, int E, float* logits, cudaStream_t st);
 int launch_router_logits_tc(const void* x, const void* w, int64_t T, int H, int E, float* logits, int32_t* status, cudaStream_t st);
 int launch_router_logits_small(const void* x, const void* w, int64_t T, int H, int E, float* logits, cudaStream_t st);   // T <= 16
+// seg_len > 0: the T token slots are regions of seg_len consecutive slots and only the first seg_valid[slot / seg_len]
+// slots of each region hold a token (the receive buffer of the expert-parallel exchange); the rest count as unrouted.
 int launch_route_map(const int32_t* ids, const float* scores, int64_t id_stride, int64_t T, int K, int S, int E, int expert_offset,
-                     RouteMapBuffers b, cudaStream_t st);
+                     RouteMapBuffers b, cudaStream_t st, int seg_len = 0, const int32_t* seg_valid = nullptr);
 int launch_route_map_static(const int32_t* ids, const float* scores, int64_t T, int K, int S, int E, int expert_offset,
                             RouteMapBuffers b, cudaStream_t st);
 int launch_ep_visits(const int32_t* ids, int64_t T, int K, int experts_per_rank, int world, int32_t* rank_slots, cudaStream_t st);
@@ -126,6 +128,30 @@ int launch_gemm_w4a16(const void* a, int64_t a_stride, const void* b_q, const vo
                       cudaStream_t st);
 int64_t gemm_w4a16_workspace_bytes(int64_t m, int64_t n, int64_t k);
 int make_sf_map(CUtensorMap* map, const void* base, uint64_t n_chunks);
+
+// ---- expert-parallel exchange over peer memory (ep_exchange.cu)
+constexpr int kEpMaxRanks = 16;
+// int32 fields of a rank's control block, each kEpMaxRanks wide and indexed by the peer that writes it
+constexpr int kEpCount = 0;                           // rows the peer sent (its segment, padded to 128)
+constexpr int kEpRetBase = kEpMaxRanks;               // first row of that segment in the peer's return buffer
+constexpr int kEpFlagDispatch = 2 * kEpMaxRanks;      // step counter: the peer's rows and the two fields above have landed
+constexpr int kEpFlagReturn = 3 * kEpMaxRanks;        // step counter: the peer has written its results into my return buffer
+constexpr int kEpCtrlInts = 4 * kEpMaxRanks;
+struct EpPeers {                   // addresses for the current step's parity, passed to kernels by value
+  int32_t world, rank;
+  uint8_t* recv[kEpMaxRanks];      // [d]: this rank's region inside rank d's receive buffer
+  int32_t* ctrl[kEpMaxRanks];      // [d]: rank d's control block
+  void* ret[kEpMaxRanks];          // [s]: rank s's return buffer (bf16 rows)
+};
+int launch_ep_dispatch(const void* hid_q, const void* hid_sf, const int32_t* ids, const float* weights, const int32_t* tok_of_row,
+                       const int32_t* tile_expert, const int32_t* tile_rows, const int32_t* seg_start, const int32_t* totals, int H,
+                       int K, int experts_per_rank, int64_t row_bytes, int64_t row_capacity, const EpPeers& peers, int epoch, int64_t T,
+                       int shared_slots, int shared_base, int32_t* row_of, float* weight_of_row, unsigned int* done_counter,
+                       cudaStream_t st);
+int launch_ep_wait(const int32_t* flags, int n, int epoch, int32_t* status, int code, cudaStream_t st);
+int launch_ep_post(const EpPeers& peers, int field, int epoch, cudaStream_t st);
+int launch_finalize_ep(const void* rout, const int32_t* row_of, const float* weight_of_row, int64_t T, int KK, int H,
+                       const EpPeers& peers, const int32_t* ctrl, int seg_len, cudaStream_t st);
 int launch_gemm_nvfp4_pair(int mode, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tsa, const CUtensorMap& tsb,
                            const GemmParams& p, int n_clusters, cudaStream_t st);
 int launch_gemm_nvfp4(int mode, int bn, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid,

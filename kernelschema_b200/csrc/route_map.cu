@@ -23,13 +23,22 @@ struct RouteView {
   int S;            // shared experts: extra always-selected slots
   int E;            // local routed experts
   int expert_offset;
+  int seg_len;               // > 0: token slots come in regions of seg_len, of which only the first seg_valid[region] hold a token
+  const int32_t* seg_valid;
 };
+
+DEV bool slot_holds_token(const RouteView& r, int64_t t) {
+  if (r.seg_len <= 0) return true;
+  const int64_t s = t / r.seg_len;
+  return t - s * r.seg_len < r.seg_valid[s];
+}
 
 DEV int route_expert(const RouteView& r, int64_t f, int64_t total) {
   if (f >= total) return -1;
   const int kk = r.K + r.S;
   const int64_t t = f / kk;
   const int k = (int)(f - t * kk);
+  if (!slot_holds_token(r, t)) return -1;
   if (k >= r.K) return r.E + (k - r.K);
   const int e = r.ids[t * r.id_stride + k] - r.expert_offset;
   return (e >= 0 && e < r.E) ? e : -1;
@@ -66,6 +75,7 @@ DEV int route_expert32(const RouteView& r, int f, int total) {
   const int kk = r.K + r.S;
   const int t = f / kk;
   const int k = f - t * kk;
+  if (!slot_holds_token(r, t)) return -1;
   if (k >= r.K) return r.E + (k - r.K);
   const int e = r.ids[(int64_t)t * r.id_stride + k] - r.expert_offset;
   return (e >= 0 && e < r.E) ? e : -1;
@@ -383,11 +393,11 @@ __global__ void __launch_bounds__(256) k_route_fused(RouteView r, const float* _
 }
 
 int launch_route_map(const int32_t* ids, const float* scores, int64_t id_stride, int64_t T, int K, int S, int E, int expert_offset,
-                     RouteMapBuffers b, cudaStream_t st) {
+                     RouteMapBuffers b, cudaStream_t st, int seg_len, const int32_t* seg_valid) {
   const int etot = E + S;
   const int64_t total = T * (K + S);
   const int nblk = (int)((total + kRouteChunk - 1) / kRouteChunk);
-  RouteView r{ids, id_stride > 0 ? id_stride : K, T, K, S, E, expert_offset};
+  RouteView r{ids, id_stride > 0 ? id_stride : K, T, K, S, E, expert_offset, seg_valid ? seg_len : 0, seg_valid};
   if (nblk >= 1 && nblk <= kFusedMaxBlocks)
     return (int)launch_chain(k_route_fused, dim3(nblk), dim3(256), sizeof(int) * (kRouteWarps + 2) * (size_t)etot, st, r, scores, etot, b);
   const size_t smem = sizeof(int) * kRouteWarps * (size_t)etot;

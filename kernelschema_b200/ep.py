@@ -108,14 +108,15 @@ class CudaPlanner:
     """`plan_messages_torch` in three launches of the library: `b200moe_ep_visits`, the route map of a "plan" layer
     whose experts are the ranks (plus one shared slot), `b200moe_ep_pack`. Buffers are allocated once."""
 
-    def __init__(self, hidden, top_k, experts_per_rank, world, max_tokens, shared_slot, device):
+    def __init__(self, hidden, top_k, experts_per_rank, world, max_tokens, shared_slot, device, message_buffer=True):
         from .ops import MoELayer
         self.h, self.k, self.e_local, self.world = hidden, top_k, experts_per_rank, world
         # the plan layer's GEMM operands are never used, so it gets the smallest legal sizes
         self.layer = MoELayer(256, 256, world, world, max_tokens, num_shared_experts=1 if shared_slot else 0)
         self.ws = self.layer.workspace()
         self.slots = torch.empty((max_tokens, world), dtype=torch.int32, device=device)
-        self.msg = torch.empty((self.ws["row_capacity"], row_bytes(hidden, top_k)), dtype=torch.uint8, device=device)
+        self.msg = (torch.empty((self.ws["row_capacity"], row_bytes(hidden, top_k)), dtype=torch.uint8, device=device)
+                    if message_buffer else None)     # the peer-memory transport packs straight into the destinations' buffers
 
     def plan(self, ids, weights, hq, hs):
         """Returns (msg buffer, segment rows per rank as a device tensor, row_of [T, world (+1)], row weights (all 1) for
@@ -130,6 +131,76 @@ class CudaPlanner:
         return self.msg, seg_start[1:self.world + 1] - seg_start[:self.world], self.ws["row_of"][:t], self.ws["weight_of_row"]
 
 
+class PeerExchange:
+    """Buffers of the peer-memory exchange of one rank (see csrc/ep_exchange.cu) and the address tables of its peers.
+
+    One allocation per rank, the same layout everywhere, every region twice (step parity): control block | receive buffer
+    of world regions x seg_len message rows | return buffer of world * seg_len (+ tokens_per_rank shared-expert) bf16 rows.
+    The 64-byte handles travel once through `torch.distributed.all_gather_object`; a group of one rank uses its own
+    buffer as its only peer (the whole device path on a single GPU)."""
+
+    def __init__(self, hidden, top_k, tokens_per_rank, shared_rows, group, device):
+        import ctypes as C
+        from . import _lib
+        from .ops import _from_device_ptr
+        self.lib = _lib.load()
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        if self.world > _lib.EP_MAX_RANKS:
+            raise ValueError(f"at most {_lib.EP_MAX_RANKS} ranks")
+        self.h, self.k = hidden, top_k
+        self.seg_len = (tokens_per_rank + SEGMENT_ROWS - 1) // SEGMENT_ROWS * SEGMENT_ROWS
+        self.row_bytes = row_bytes(hidden, top_k)
+        self.slots = self.world * self.seg_len
+        self.shared_base = self.slots
+        self.ret_rows = self.slots + (tokens_per_rank if shared_rows else 0)
+        al = lambda n: (n + 1023) // 1024 * 1024
+        ctrl_b, recv_b, ret_b = al(_lib.EP_CTRL_INTS * 4), al(self.slots * self.row_bytes), al(self.ret_rows * hidden * 2)
+        self.off_ctrl = [0, ctrl_b]
+        self.off_counter = 2 * ctrl_b
+        self.off_recv = [2 * ctrl_b + 1024, 2 * ctrl_b + 1024 + recv_b]
+        self.off_ret = [self.off_recv[1] + recv_b, self.off_recv[1] + recv_b + ret_b]
+        self.bytes = self.off_ret[1] + ret_b
+        base, handle = C.c_void_p(), C.create_string_buffer(64)
+        _lib.check(self.lib.b200moe_ep_shared_alloc(self.bytes, C.byref(base), handle), "b200moe_ep_shared_alloc")
+        self.base = base.value
+        handles = [None] * self.world
+        dist.all_gather_object(handles, (self.rank, handle.raw), group=group)
+        self.peer_base, self._opened = [None] * self.world, []
+        for r, raw in handles:
+            if r == self.rank:
+                self.peer_base[r] = self.base
+            else:
+                ptr = C.c_void_p()
+                _lib.check(self.lib.b200moe_ep_shared_open(C.create_string_buffer(raw, 64), C.byref(ptr)), "b200moe_ep_shared_open")
+                self.peer_base[r] = ptr.value
+                self._opened.append(ptr.value)
+        self.peers = []
+        for p in (0, 1):
+            pe = _lib.EpPeers(world=self.world, rank=self.rank)
+            for r in range(self.world):
+                pe.recv[r] = self.peer_base[r] + self.off_recv[p] + self.rank * self.seg_len * self.row_bytes
+                pe.ctrl[r] = self.peer_base[r] + self.off_ctrl[p]
+                pe.ret[r] = self.peer_base[r] + self.off_ret[p]
+            self.peers.append(pe)
+        dev = device.index if device.index is not None else torch.cuda.current_device()
+        self.recv = [_from_device_ptr(self.base + self.off_recv[p], self.slots * self.row_bytes, torch.uint8, (self.slots, self.row_bytes), dev)
+                     for p in (0, 1)]
+        self.ret = [_from_device_ptr(self.base + self.off_ret[p], self.ret_rows * hidden * 2, torch.bfloat16, (self.ret_rows, hidden), dev)
+                    for p in (0, 1)]
+        self.ctrl_ptr = [self.base + self.off_ctrl[p] for p in (0, 1)]
+        self.counter_ptr = self.base + self.off_counter
+        self.epoch = 0
+        dist.barrier(group=group)          # nobody writes a peer before every rank has mapped every buffer
+
+    def close(self):
+        for ptr in self._opened:
+            self.lib.b200moe_ep_shared_close(ptr)
+        self._opened = []
+        if self.base:
+            self.lib.b200moe_ep_shared_free(self.base)
+            self.base = None
+
+
 class ExpertParallelMoE:
     """Layer instance on one rank. `expert_rows`, `shared_rows` and `combine_rows` are the compute hooks; by default
     they run libb200moe on the current CUDA device. `planner` is "cuda" (library kernels; default on a GPU) or
@@ -137,7 +208,7 @@ class ExpertParallelMoE:
 
     def __init__(self, hidden, intermediate, num_experts, top_k, tokens_per_rank, num_shared_experts=0, group=None,
                  expert_rows=None, combine_rows=None, shared_rows=None, recv_capacity=None, planner=None, micro_batches=None,
-                 sm_margin=None):
+                 sm_margin=None, transport=None):
         self.group = group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
@@ -159,13 +230,19 @@ class ExpertParallelMoE:
         # B200s it does not pay (2 ranks: 3.78 against 3.22 ms; 8 ranks: 5.37 against 5.16 ms per step): every half re-reads
         # this rank's expert weights and the GEMMs lose the SMs they leave free. Off unless asked for.
         self.micro_batches = micro_batches or 1
+        # "p2p": rows and results travel as peer stores of this library's kernels, flags instead of host synchronisation
+        # (CUDA only; the default there when no hook replaces the compute). "collective": torch.distributed all-to-all
+        # (NCCL, or gloo on CPU).
+        self.transport = transport
+        self._px = None
         self.sm_margin = (sm_margin if sm_margin is not None else 16) if self.micro_batches > 1 else 0
         self._routed = self._shared = self._plan = None
         self._plans = {}
         self.profile = False
         # quantise/route launches are the caller's; here: plan (visits + route map + pack), then (route map + permute +
         # FC1 + FC2 + combine) for the received tokens, the same for the shared experts, and the final combine
-        self.launches_per_step = 3 + 5 * (2 if num_shared_experts else 1) + 1
+        # (peer-memory transport: visits + route map + dispatch, two flag waits and one flag post instead of the pack)
+        self.launches_per_step = 3 + 5 * (2 if num_shared_experts else 1) + 1 + 3
 
     # ------------------------------------------------------------------ CUDA hooks
     def _cuda_expert_rows(self, rows_q, rows_sf, local_ids, weights, w1q, w1s, w2q, w2s, out_rows, kw):
@@ -196,6 +273,12 @@ class ExpertParallelMoE:
             self._side = torch.cuda.Stream(device=dev)
         return self._side
 
+    def close(self):
+        """Frees the peer-exchange buffers (every rank must have finished its last step: barrier first)."""
+        if self._px is not None:
+            self._px.close()
+            self._px = None
+
     def status(self) -> int:
         code = 0
         for layer in [self._routed, self._shared, self._plan.layer if self._plan else None] + [p.layer for p in self._plans.values()]:
@@ -210,6 +293,9 @@ class ExpertParallelMoE:
         scale_gate, scale_out) for the same experts. Returns bf16 [T, H]."""
         dev = hq.device
         t = hq.shape[0]
+        transport = self.transport or ("p2p" if dev.type == "cuda" and self.micro_batches == 1 else "collective")
+        if transport == "p2p":
+            return self._forward_p2p(ids, weights, hq, hs, w1q, w1s, w2q, w2s, out, kw)
         if self.micro_batches > 1 and dev.type == "cuda" and t >= 2 * SEGMENT_ROWS:
             return self._forward_pipelined(ids, weights, hq, hs, w1q, w1s, w2q, w2s, out, kw)
         marks = []
@@ -272,6 +358,73 @@ class ExpertParallelMoE:
         if out is None:
             out = torch.empty((t, self.h), dtype=torch.bfloat16, device=dev)
         self._combine_rows(rows_all, row_of, w_rows, out)
+        mark("combine")
+        if marks:
+            self._pending_marks = marks
+        return out
+
+    def _forward_p2p(self, ids, weights, hq, hs, w1q, w1s, w2q, w2s, out, kw):
+        """One step over peer memory: no collective call, no host synchronisation, no allocation after the first step.
+        plan -> dispatch kernel (rows, sizes and flags into the peers' buffers) -> [shared experts on a side stream] ->
+        wait for every source -> the layer over the receive buffer, its combine pass writing into the sources' return
+        buffers -> return flags -> wait for every destination -> slot-ordered combine of the returned rows."""
+        from . import _lib
+        from .ops import MoELayer, _stream, ep_visits
+        dev = hq.device
+        t = hq.shape[0]
+        if t > self.t:
+            raise ValueError(f"{t} tokens, the exchange buffers were sized for {self.t} per rank")
+        if self._px is None:
+            self._px = PeerExchange(self.h, self.k, self.t, bool(self.s), self.group, dev)
+            self._plan = CudaPlanner(self.h, self.k, self.e_local, self.world, self.t, bool(self.s), dev, message_buffer=False)
+            self._routed = MoELayer(self.h, self.i, self.e_local, self.k, self._px.slots, sm_margin=self.sm_margin)
+            self._scratch_out = torch.empty((1, self.h), dtype=torch.bfloat16, device=dev)
+        px, plan, lib = self._px, self._plan, self._px.lib
+        px.epoch += 1
+        epoch, p = px.epoch, px.epoch & 1
+        marks = []
+
+        def mark(name):
+            if self.profile:
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record()
+                marks.append((name, ev))
+
+        mark("start")
+        hq = hq.contiguous()
+        hs8 = hs.contiguous().view(torch.uint8)
+        ids, weights = ids.contiguous(), weights.contiguous()
+        slots = plan.slots[:t]
+        ep_visits(ids, self.e_local, self.world, slots)
+        plan.layer.route_map(slots, None)
+        _lib.check(lib.b200moe_ep_dispatch(plan.layer._h, hq.data_ptr(), hs8.data_ptr(), ids.data_ptr(), weights.data_ptr(), t, self.h,
+                                           self.k, self.e_local, px.row_bytes, px.peers[p], epoch, int(bool(self.s)), px.shared_base,
+                                           px.counter_ptr, _stream()), "b200moe_ep_dispatch")
+        mark("plan+dispatch")
+        ret = px.ret[p]
+        side = None
+        if self.s:
+            side = self._side_stream(dev)
+            side.wait_stream(torch.cuda.current_stream(dev))
+            with torch.cuda.stream(side):
+                self._shared_rows(hq, hs8, w1q, w1s, w2q, w2s, ret[px.shared_base:px.shared_base + t], kw)
+        _lib.check(lib.b200moe_ep_wait(self._routed._h, px.ctrl_ptr[p] + 4 * _lib.EP_FLAG_DISPATCH, self.world, epoch, _stream()),
+                   "b200moe_ep_wait")
+        mark("wait_rows")
+        rows_q, rows_sf, ids_recv, w_recv = message_views(px.recv[p], self.h, self.k)
+        e = self.e_local
+        self._routed.run_ep(px.peers[p], px.ctrl_ptr[p], px.seg_len, ids_recv, w_recv, rows_q, rows_sf, w1q[:e], w1s[:e], w2q[:e],
+                            w2s[:e], self._scratch_out, **{k: (None if v is None else v[:e]) for k, v in kw.items()})
+        _lib.check(lib.b200moe_ep_post(px.peers[p], _lib.EP_FLAG_RETURN, epoch, _stream()), "b200moe_ep_post")
+        mark("experts+return")
+        _lib.check(lib.b200moe_ep_wait(self._routed._h, px.ctrl_ptr[p] + 4 * _lib.EP_FLAG_RETURN, self.world, epoch, _stream()),
+                   "b200moe_ep_wait")
+        if side is not None:
+            torch.cuda.current_stream(dev).wait_stream(side)
+        mark("wait_results")
+        if out is None:
+            out = torch.empty((t, self.h), dtype=torch.bfloat16, device=dev)
+        self._combine_rows(ret, plan.ws["row_of"][:t], plan.ws["weight_of_row"], out)
         mark("combine")
         if marks:
             self._pending_marks = marks

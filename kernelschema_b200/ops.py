@@ -242,7 +242,11 @@ class MoELayer:
                       output1_scale_scalar=_ptr(scale_up), output1_scale_gate_scalar=_ptr(scale_gate),
                       output2_scale_scalar=_ptr(scale_out), local_expert_offset=expert_offset, direct_rows=int(direct_rows),
                       output=_ptr(out),
-                      output_stride=out.stride(0))
+                      output_stride=out.stride(0),
+                      hidden_states_stride=hidden_states.stride(0) * hidden_states.element_size() if hidden_states.dim() == 2 else 0,
+                      hidden_states_scale_stride=(hidden_states_scale.stride(0) * hidden_states_scale.element_size()
+                                                  if (scale_layout == 2 and hidden_states_scale.dim() == 2) else 0),
+                      topk_stride=0 if ids is None else ids.stride(0))
         return a
 
     def run(self, ids, weights, hidden_states, hidden_states_scale, w1, s1, w2, s2, out, *, alpha=None, beta=None, limit=None,
@@ -262,6 +266,15 @@ class MoELayer:
                     if (scale_layout == 2 and hidden_states_scale.dim() == 2) else 0,
                     0 if ids is None else ids.stride(0))
         return out
+
+    def run_ep(self, peers, ctrl_ptr: int, seg_len: int, ids, weights, hidden_states, hidden_states_scale, w1, s1, w2, s2, scratch_out,
+               **kw):
+        """The layer over the token slots of an expert-parallel receive buffer (b200moe_run_ep): `peers` is a
+        ``_lib.EpPeers`` of the step's parity, `ctrl_ptr` the device address of this rank's control block. The combine
+        pass writes into the source ranks' return buffers; `scratch_out` only satisfies the argument checks."""
+        _need_cuda(hidden_states, hidden_states_scale, w1, s1, w2, s2)
+        a = self._args(ids, weights, hidden_states, hidden_states_scale, w1, s1, w2, s2, scratch_out, **kw)
+        _lib.check(_lib.load().b200moe_run_ep(self._h, C.byref(a), C.byref(peers), ctrl_ptr, seg_len, _stream()), "b200moe_run_ep")
 
     def run_profiled(self, ids, weights, hidden_states, hidden_states_scale, w1, s1, w2, s2, out, **kw):
         a = self._args(ids, weights, hidden_states, hidden_states_scale, w1, s1, w2, s2, out, **kw)

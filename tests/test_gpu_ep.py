@@ -18,7 +18,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, results, tokens=T, micro_batches=1):
+def _worker(rank, world, port, results, tokens=T, micro_batches=1, transport=None):
     T = tokens
     import torch.distributed as dist
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
@@ -35,7 +35,7 @@ def _worker(rank, world, port, results, tokens=T, micro_batches=1):
         mine = slice(rank * T, (rank + 1) * T)
         own = list(range(rank * e_local, (rank + 1) * e_local)) + list(range(E, E + S))
         dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
-        ep = ExpertParallelMoE(H, I, E, K, T, num_shared_experts=S, micro_batches=micro_batches)
+        ep = ExpertParallelMoE(H, I, E, K, T, num_shared_experts=S, micro_batches=micro_batches, transport=transport)
         assert ep.micro_batches == micro_batches
         ids, scores = p["topk_ids"]
         out = ep.forward(dev(ids[mine]), dev(scores[mine]), dev(p["hidden_states"][mine]), dev(p["hidden_states_scale"][mine]),
@@ -50,16 +50,20 @@ def _worker(rank, world, port, results, tokens=T, micro_batches=1):
         assert ep.status() == 0
         r = assert_layer_parity(out.float().cpu().numpy(), o.moe_expected(p)[mine], f"rank {rank}", extra_bf16_roundings=world)
         results[rank] = r["rel_l2"]
+        dist.barrier()
+        ep.close()
     finally:
         dist.destroy_process_group()
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_expert_parallel_two_gpus():
+@pytest.mark.parametrize("transport", ["p2p", "collective"])
+def test_expert_parallel_two_gpus(transport):
+    """`p2p`: rows and results as peer stores of the library's kernels with flags; `collective`: NCCL all-to-all."""
     import torch.multiprocessing as mp
     with mp.Manager() as mgr:
         results = mgr.dict()
-        mp.spawn(_worker, args=(2, _free_port(), results), nprocs=2, join=True)
+        mp.spawn(_worker, args=(2, _free_port(), results, T, 1, transport), nprocs=2, join=True)
         assert sorted(results.keys()) == [0, 1]
 
 
@@ -69,7 +73,7 @@ def test_expert_parallel_two_gpus_pipelined():
     import torch.multiprocessing as mp
     with mp.Manager() as mgr:
         results = mgr.dict()
-        mp.spawn(_worker, args=(2, _free_port(), results, 384, 2), nprocs=2, join=True)
+        mp.spawn(_worker, args=(2, _free_port(), results, 384, 2, "collective"), nprocs=2, join=True)
         assert sorted(results.keys()) == [0, 1]
 
 

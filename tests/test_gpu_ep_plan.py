@@ -6,6 +6,7 @@ import pytest
 import torch
 
 from helpers import make_moe_case
+from oracle import nvfp4_oracle as o
 
 pytestmark = pytest.mark.gpu
 
@@ -67,3 +68,39 @@ def test_layer_runs_on_strided_message_views():
     odd = torch.zeros((msg.shape[0], h // 2 + 8), dtype=torch.uint8, device="cuda")[:, :h // 2]     # row stride not % 16
     with pytest.raises((RuntimeError, ValueError), match="stride"):
         layer.run(m_ids, m_w, odd, m_sf, *wt, out_strided, **kw)
+
+
+@pytest.mark.parametrize("shared,tokens", [(1, 200), (0, 128), (1, 1)])
+def test_peer_memory_exchange_single_rank_loop(shared, tokens):
+    """The whole peer-memory path (dispatch kernel, flags, layer over the receive buffer with its combine pass writing
+    into the return buffer, final combine) on ONE GPU: a group of one rank is its own peer. Two steps with different
+    tokens, so both buffer parities and the reuse of flags and counters are exercised; against the CPU oracle."""
+    import torch.distributed as dist
+    from helpers import assert_layer_parity, make_moe_case
+    from kernelschema_b200.ep import ExpertParallelMoE
+    h, i, e, k = 512, 256, 8, 4
+    own = not dist.is_initialized()
+    if own:
+        import socket
+        with socket.socket() as sock:
+            sock.bind(("127.0.0.1", 0))
+            port = sock.getsockname()[1]
+        dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=0, world_size=1)
+    try:
+        ep = ExpertParallelMoE(h, i, e, k, 256, num_shared_experts=shared, transport="p2p")
+        dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+        for step, seed in enumerate((3, 4, 5)):
+            p = make_moe_case(seed, tokens, h, i, e, k, shared=shared, global_scales=True, routing="zipf", masked=(step == 1))
+            ids, scores = p["topk_ids"]
+            out = ep.forward(dev(ids), dev(scores), dev(p["hidden_states"]), dev(p["hidden_states_scale"]), dev(p["gemm1_weights"]),
+                             dev(p["gemm1_weights_scale"]), dev(p["gemm2_weights"]), dev(p["gemm2_weights_scale"]),
+                             scale_up=dev(p["output1_scale_scalar"]), scale_gate=dev(p["output1_scale_gate_scalar"]),
+                             scale_out=dev(p["output2_scale_scalar"]))
+            torch.cuda.synchronize()
+            assert ep.status() == 0
+            assert_layer_parity(out.float().cpu().numpy(), o.moe_expected(p), f"step {step}", extra_bf16_roundings=1)
+        assert ep._px.epoch == 3
+        ep.close()
+    finally:
+        if own:
+            dist.destroy_process_group()
