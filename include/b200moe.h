@@ -41,7 +41,10 @@ typedef struct {
   int32_t max_tokens;         /* largest T a run may pass */
   int32_t tile_n;             /* GEMM tile: 0 = default; 128 or 256 = one CTA per 128 x tile_n tile; 512 = CTA pair per 256 x 256 tile */
   int32_t sm_margin;          /* SMs the persistent GEMM grids leave free (0 = use all): room for a collective that runs beside them */
-  int32_t reserved[7];
+  int32_t graph_cache;        /* 1 = b200moe_run replays a CUDA graph when it is called again with an identical argument block
+                                 on the same stream (captured on the second such call, as the reference's moe_run does,
+                                 NV/candidate/nvfp4_moe.cu:9513-9517); 0 = always launch the kernel chain */
+  int32_t reserved[6];
 } b200moe_config;
 
 /* One forward call. Field names follow the reference operator's forward() arguments
@@ -249,6 +252,18 @@ int b200moe_run(b200moe_handle h, const b200moe_args* args, void* stream);
 /* Same, recording CUDA events between stages and returning their durations in milliseconds (synchronises).
  * stage_ms[0..4] = route map, permute, FC1, FC2, combine. Counterpart of moe_profile, NV/candidate/nvfp4_moe.cu:9678. */
 int b200moe_run_profiled(b200moe_handle h, const b200moe_args* args, void* stream, float* stage_ms);
+/* Host-side counters of a layer (counterpart of the reference's graph_status() / nvfp4_fast.stats(),
+ * NV/candidate/nvfp4_moe.cu:9618-9702, NV/candidate/nvfp4_fast.c:139-145). */
+typedef struct {
+  int64_t runs;             /* b200moe_run calls that launched work */
+  int64_t graph_replays;    /* ... of which replayed a cached graph */
+  int64_t graph_captures;   /* graphs captured (second identical call) */
+  int64_t graph_evictions;  /* cached graphs dropped to make room (the cache holds 4) */
+  int64_t eager_in_capture; /* calls made while the caller was capturing `stream` itself: launched into that capture */
+  int64_t workspace_bytes;
+} b200moe_stats;
+int b200moe_get_stats(b200moe_handle h, b200moe_stats* out);
+
 /* Synchronises `stream` and returns the device status word of the layer (0 = no bounded wait expired). */
 int b200moe_status(b200moe_handle h, void* stream, int32_t* code);
 

@@ -18,7 +18,7 @@ SF_ROW_MAJOR, SF_TILED = 0, 1
 class Config(C.Structure):
     _fields_ = [("struct_size", C.c_int32), ("hidden", C.c_int32), ("intermediate", C.c_int32), ("num_experts", C.c_int32),
                 ("top_k", C.c_int32), ("num_shared_experts", C.c_int32), ("max_tokens", C.c_int32), ("tile_n", C.c_int32),
-                ("sm_margin", C.c_int32), ("reserved", C.c_int32 * 7)]
+                ("sm_margin", C.c_int32), ("graph_cache", C.c_int32), ("reserved", C.c_int32 * 6)]
 
 
 class Args(C.Structure):
@@ -41,6 +41,11 @@ EP_FLAG_DISPATCH, EP_FLAG_RETURN = 2 * EP_MAX_RANKS, 3 * EP_MAX_RANKS
 class EpPeers(C.Structure):
     _fields_ = [("world", C.c_int32), ("rank", C.c_int32), ("recv", C.c_void_p * EP_MAX_RANKS), ("ctrl", C.c_void_p * EP_MAX_RANKS),
                 ("ret", C.c_void_p * EP_MAX_RANKS)]
+
+
+class Stats(C.Structure):
+    _fields_ = [("runs", C.c_int64), ("graph_replays", C.c_int64), ("graph_captures", C.c_int64), ("graph_evictions", C.c_int64),
+                ("eager_in_capture", C.c_int64), ("workspace_bytes", C.c_int64)]
 
 
 class WorkspaceView(C.Structure):
@@ -90,6 +95,7 @@ SIGNATURES = {
     "b200moe_run": (C.c_int, [C.c_void_p, C.POINTER(Args), C.c_void_p]),
     "b200moe_run_profiled": (C.c_int, [C.c_void_p, C.POINTER(Args), C.c_void_p, C.POINTER(C.c_float)]),
     "b200moe_status": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_int32)]),
+    "b200moe_get_stats": (C.c_int, [C.c_void_p, C.POINTER(Stats)]),
 }
 
 _lib = None

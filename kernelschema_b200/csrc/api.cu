@@ -71,6 +71,16 @@ struct b200moe_layer {
   const void* b2_ptr;
   const void* s1_ptr;
   const void* s2_ptr;
+  // graph cache of b200moe_run (cfg.graph_cache): entries keyed on the whole argument block and the stream
+  struct Cached {
+    b200moe_args key;
+    cudaStream_t stream;
+    cudaGraphExec_t exec;     // null: the key was seen once, the next identical call captures
+    uint64_t last_use;
+  } cache[4];
+  uint64_t tick;
+  cudaStream_t capture_stream;   // only ever captured on, never executed on: the caller's stream may be the legacy default
+  b200moe_stats stats;
 };
 
 namespace {
@@ -96,6 +106,7 @@ int check_cfg(const b200moe_config* c) {
   if (c->sm_margin < 0 || c->sm_margin > 64) return fail(708, "config: sm_margin must be in 0..64");
   if (c->tile_n != 0 && c->tile_n != 128 && c->tile_n != 256 && c->tile_n != 512)
     return fail(716, "config: tile_n must be 0, 128, 256 or 512");
+  if (c->graph_cache != 0 && c->graph_cache != 1) return fail(709, "config: graph_cache must be 0 or 1");
   return 0;
 }
 
@@ -475,6 +486,9 @@ int b200moe_create(const b200moe_config* cfg, b200moe_handle* out) {
 
 int b200moe_destroy(b200moe_handle h) {
   if (!h) return 0;
+  for (auto& c : h->cache)
+    if (c.exec) cudaGraphExecDestroy(c.exec);
+  if (h->capture_stream) cudaStreamDestroy(h->capture_stream);
   cudaError_t e = cudaFree(h->base);
   delete h;
   return cuda_fail((int)e, "destroy");
@@ -672,10 +686,96 @@ int b200moe_run_ep(b200moe_handle h, const b200moe_args* args, const b200moe_ep_
   return run_impl(h, args, (cudaStream_t)stream, nullptr, &ep);
 }
 
+// Replay of the layer's launch chain from a CUDA graph. An entry is keyed on the bytes of the argument block and the
+// stream: same pointers, sizes and strides mean the same launches (routing and data are read from memory by the
+// kernels, tensor maps depend on addresses only). First sighting of a key runs the chain and remembers the key, the
+// second captures the chain on the caller's stream and launches the graph, later ones only launch it.
+static int run_cached(b200moe_layer* h, const b200moe_args* in, cudaStream_t st) {
+  // the key is compared as bytes: copy the fields into a zeroed block so that padding never takes part
+  b200moe_args key;
+  memset(&key, 0, sizeof(key));
+#define B200MOE_COPY(f) key.f = in->f
+  B200MOE_COPY(struct_size); B200MOE_COPY(num_tokens); B200MOE_COPY(topk_ids); B200MOE_COPY(topk_weights); B200MOE_COPY(hidden_states);
+  B200MOE_COPY(hidden_states_scale); B200MOE_COPY(hidden_states_scale_layout); B200MOE_COPY(activation_type); B200MOE_COPY(gemm1_weights);
+  B200MOE_COPY(gemm1_weights_scale); B200MOE_COPY(gemm2_weights); B200MOE_COPY(gemm2_weights_scale); B200MOE_COPY(gemm1_alpha);
+  B200MOE_COPY(gemm1_beta); B200MOE_COPY(gemm1_clamp_limit); B200MOE_COPY(output1_scale_scalar); B200MOE_COPY(output1_scale_gate_scalar);
+  B200MOE_COPY(output2_scale_scalar); B200MOE_COPY(local_expert_offset); B200MOE_COPY(direct_rows); B200MOE_COPY(output);
+  B200MOE_COPY(output_stride); B200MOE_COPY(hidden_states_stride); B200MOE_COPY(hidden_states_scale_stride); B200MOE_COPY(topk_stride);
+#undef B200MOE_COPY
+  const b200moe_args* a = &key;
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(st, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) {
+    cudaGetLastError();
+    h->stats.eager_in_capture++;
+    return run_impl(h, a, st, nullptr);          // the caller is capturing: our launches become part of its graph
+  }
+  b200moe_layer::Cached* hit = nullptr;
+  b200moe_layer::Cached* victim = &h->cache[0];
+  for (auto& c : h->cache) {
+    if (c.last_use && c.stream == st && memcmp(&c.key, a, sizeof(*a)) == 0) hit = &c;
+    if (c.last_use < victim->last_use) victim = &c;
+  }
+  ++h->tick;
+  if (hit && hit->exec) {
+    hit->last_use = h->tick;
+    h->stats.graph_replays++;
+    return cuda_fail((int)cudaGraphLaunch(hit->exec, st), "graph replay");
+  }
+  if (!hit) {                                    // first sighting: eager, remember the key
+    if (victim->exec) {
+      cudaGraphExecDestroy(victim->exec);
+      h->stats.graph_evictions++;
+    }
+    victim->key = *a;
+    victim->stream = st;
+    victim->exec = nullptr;
+    victim->last_use = h->tick;
+    return run_impl(h, a, st, nullptr);
+  }
+  hit->last_use = h->tick;
+  // The chain is captured on a stream of the layer's own (nothing ever executes there) and the graph is launched on
+  // the caller's stream, which may be the legacy default stream that cannot be captured itself.
+  cudaError_t e = cudaSuccess;
+  if (!h->capture_stream) e = cudaStreamCreateWithFlags(&h->capture_stream, cudaStreamNonBlocking);
+  if (e == cudaSuccess) e = cudaStreamBeginCapture(h->capture_stream, cudaStreamCaptureModeThreadLocal);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return run_impl(h, a, st, nullptr);
+  }
+  const int rc = run_impl(h, a, h->capture_stream, nullptr);
+  cudaGraph_t graph = nullptr;
+  e = cudaStreamEndCapture(h->capture_stream, &graph);
+  if (rc || e != cudaSuccess || !graph) {
+    if (graph) cudaGraphDestroy(graph);
+    cudaGetLastError();
+    return rc ? rc : run_impl(h, a, st, nullptr);
+  }
+  cudaGraphExec_t exec = nullptr;
+  e = cudaGraphInstantiate(&exec, graph, 0);
+  cudaGraphDestroy(graph);
+  if (e != cudaSuccess || !exec) {
+    cudaGetLastError();
+    return run_impl(h, a, st, nullptr);
+  }
+  hit->exec = exec;
+  h->stats.graph_captures++;
+  return cuda_fail((int)cudaGraphLaunch(exec, st), "graph launch");
+}
+
 int b200moe_run(b200moe_handle h, const b200moe_args* args, void* stream) {
   int rc = check_args(h, args);
   if (rc) return rc;
+  if (args->num_tokens == 0) return 0;
+  h->stats.runs++;
+  if (h->cfg.graph_cache) return run_cached(h, args, (cudaStream_t)stream);
   return run_impl(h, args, (cudaStream_t)stream, nullptr);
+}
+
+int b200moe_get_stats(b200moe_handle h, b200moe_stats* out) {
+  if (!h || !out) return fail(719, "get_stats: null argument");
+  *out = h->stats;
+  out->workspace_bytes = h->bytes;
+  return 0;
 }
 
 int b200moe_run_profiled(b200moe_handle h, const b200moe_args* args, void* stream, float* stage_ms) {

@@ -24,11 +24,12 @@ static T* ptr(uintptr_t v) { return reinterpret_cast<T*>(v); }
 PYBIND11_MODULE(_b200moe_shim, m) {
   m.doc() = "pybind11 binding of libb200moe's layer entry points";
   m.def("abi_version", &b200moe_abi_version);
-  m.def("create", [](int hidden, int intermediate, int num_experts, int top_k, int num_shared_experts, int max_tokens, int tile_n) {
+  m.def("create", [](int hidden, int intermediate, int num_experts, int top_k, int num_shared_experts, int max_tokens, int tile_n,
+                     int graph_cache) {
     b200moe_config c{};
     c.struct_size = (int32_t)sizeof(c);
     c.hidden = hidden; c.intermediate = intermediate; c.num_experts = num_experts; c.top_k = top_k;
-    c.num_shared_experts = num_shared_experts; c.max_tokens = max_tokens; c.tile_n = tile_n;
+    c.num_shared_experts = num_shared_experts; c.max_tokens = max_tokens; c.tile_n = tile_n; c.graph_cache = graph_cache;
     b200moe_handle h = nullptr;
     check(b200moe_create(&c, &h), "b200moe_create");
     return reinterpret_cast<uintptr_t>(h);
@@ -72,6 +73,10 @@ PYBIND11_MODULE(_b200moe_shim, m) {
      py::arg("beta"), py::arg("limit"), py::arg("scale_up"), py::arg("scale_gate"), py::arg("scale_out"), py::arg("expert_offset"),
      py::arg("direct_rows"), py::arg("output"), py::arg("output_stride"), py::arg("stream"), py::arg("hidden_states_stride") = 0,
      py::arg("hidden_states_scale_stride") = 0, py::arg("topk_stride") = 0);
+  // Repeat call with an argument block the caller keeps alive (address of a b200moe_args): no marshalling at all.
+  m.def("run_packed", [](uintptr_t h, uintptr_t args, uintptr_t stream) {
+    check(b200moe_run(ptr<b200moe_layer>(h), ptr<const b200moe_args>(args), ptr<void>(stream)), "b200moe_run");
+  });
   m.def("handle_null", []() { return (uintptr_t)0; });
   m.def("status", [](uintptr_t h, uintptr_t stream) {
     int32_t code = 0;

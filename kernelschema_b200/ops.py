@@ -207,13 +207,13 @@ class MoELayer:
     """One layer instance: owns the library workspace for a geometry (b200moe_create / b200moe_destroy)."""
 
     def __init__(self, hidden: int, intermediate: int, num_experts: int, top_k: int, max_tokens: int,
-                 num_shared_experts: int = 0, tile_n: int = 0, sm_margin: int = 0):
+                 num_shared_experts: int = 0, tile_n: int = 0, sm_margin: int = 0, graph_cache: bool = False):
         lib = _lib.load()
         if not torch.cuda.is_available():
             raise RuntimeError("libb200moe needs a CUDA device (sm_100a); there is no CPU path")
         self.cfg = _lib.Config(struct_size=C.sizeof(_lib.Config), hidden=hidden, intermediate=intermediate,
                                num_experts=num_experts, top_k=top_k, num_shared_experts=num_shared_experts,
-                               max_tokens=max_tokens, tile_n=tile_n, sm_margin=sm_margin)
+                               max_tokens=max_tokens, tile_n=tile_n, sm_margin=sm_margin, graph_cache=int(bool(graph_cache)))
         self._h = C.c_void_p()
         _lib.check(lib.b200moe_create(C.byref(self.cfg), C.byref(self._h)), "b200moe_create")
         self.device = torch.cuda.current_device()
@@ -286,6 +286,12 @@ class MoELayer:
         t = ids.shape[0]
         _lib.check(_lib.load().b200moe_route_map(self._h, _ptr(ids), _ptr(weights), t, expert_offset, _stream()),
                    "b200moe_route_map")
+
+    def stats(self) -> dict:
+        """Host-side counters of the layer (calls, graph replays / captures / evictions)."""
+        st = _lib.Stats()
+        _lib.check(_lib.load().b200moe_get_stats(self._h, C.byref(st)), "b200moe_get_stats")
+        return {name: int(getattr(st, name)) for name, _ in _lib.Stats._fields_}
 
     def status(self) -> int:
         code = C.c_int32(0)

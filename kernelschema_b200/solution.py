@@ -14,15 +14,26 @@ the weight tensors which every token visits with weight 1.
 """
 from __future__ import annotations
 
+import ctypes as C
+
 import torch
 
-from .ops import MoELayer
+from .ops import MoELayer, _shim
+
+_raw_stream = torch._C._cuda_getCurrentRawStream
 
 
 class Model(torch.nn.Module):
-    def __init__(self):
+    """Host side of the drop-in. Two things keep the per-call host cost low, as in the reference host (its id-keyed hot path
+    and C fast call, candidate/solution.py:1054-1109, candidate/nvfp4_fast.c:153-295): a repeat call with the very same
+    tensor objects skips validation and marshalling and hands the cached argument block to the library, and the
+    library replays a CUDA graph from the second call with an identical argument block on (b200moe_config.graph_cache)."""
+
+    def __init__(self, graph_cache: bool = True):
         super().__init__()
         self._layers = {}
+        self._graph_cache = graph_cache
+        self._hot = None            # (key, handle, address of the argument block, [output], device index, keep-alive)
 
     def _layer(self, hidden, intermediate, experts, top_k, shared, tokens, tune_max):
         cap = max(int(tokens), int(tune_max or 0), 1)
@@ -31,7 +42,8 @@ class Model(torch.nn.Module):
         if layer is None or layer.cfg.max_tokens < tokens:
             if layer is not None:
                 layer.close()
-            layer = MoELayer(hidden, intermediate, experts, top_k, cap, num_shared_experts=shared)
+            layer = MoELayer(hidden, intermediate, experts, top_k, cap, num_shared_experts=shared, graph_cache=self._graph_cache)
+            self._hot = None
             self._layers[key] = layer
         return layer
 
@@ -43,6 +55,17 @@ class Model(torch.nn.Module):
                 output=None, tune_max_num_tokens=8192, gemm1_lora_delta=None, valid_hidden_size=None,
                 valid_intermediate_size=None, num_fused_shared_experts=None, hidden_states_scale_layout=None):
         ids, scores = topk_ids
+        hot = self._hot
+        if hot is not None and output is not None:
+            key = (id(ids), id(scores), id(hidden_states), id(hidden_states_scale), id(gemm1_weights), id(gemm1_weights_scale),
+                   id(gemm1_alpha), id(gemm1_beta), id(gemm1_clamp_limit), id(gemm2_weights), id(gemm2_weights_scale),
+                   id(output1_scale_scalar), id(output1_scale_gate_scalar), id(output2_scale_scalar), id(output), activation_type,
+                   local_expert_offset, top_k, intermediate_size, num_fused_shared_experts, local_num_experts, do_finalize,
+                   routed_scaling_factor, hidden_states.data_ptr(), output.data_ptr())
+            if key == hot[0]:
+                # same objects (kept alive here, so the ids cannot have been recycled) at the same addresses: same launches
+                _shim().run_packed(hot[1], hot[2], _raw_stream(hot[4]))
+                return hot[3]
         if output is None:
             raise ValueError("output tensor is required (the operator writes in place)")
         if not hidden_states.is_cuda:
@@ -90,11 +113,27 @@ class Model(torch.nn.Module):
                 gemm1_weights_scale.contiguous().view(torch.uint8), gemm2_weights.contiguous(),
                 gemm2_weights_scale.contiguous().view(torch.uint8), f32(gemm1_alpha), f32(gemm1_beta), f32(gemm1_clamp_limit),
                 f32(output1_scale_scalar), f32(output1_scale_gate_scalar), f32(output2_scale_scalar)]
-        layer.run(keep[0], keep[1], keep[2], keep[3], keep[4], keep[5], keep[6], keep[7], output, alpha=keep[8], beta=keep[9],
-                  limit=keep[10], scale_up=keep[11], scale_gate=keep[12], scale_out=keep[13],
-                  activation_type=int(activation_type), expert_offset=int(local_expert_offset or 0))
+        args = layer._args(keep[0], keep[1], keep[2], keep[3], keep[4], keep[5], keep[6], keep[7], output, alpha=keep[8], beta=keep[9],
+                           limit=keep[10], scale_up=keep[11], scale_gate=keep[12], scale_out=keep[13],
+                           activation_type=int(activation_type), expert_offset=int(local_expert_offset or 0))
+        dev = hidden_states.device.index
+        _shim().run_packed(layer._h.value, C.addressof(args), _raw_stream(dev))
         self._last_inputs = keep   # keep converted temporaries alive until the stream has consumed them
-        return [output]
+        result = [output]
+        originals = (ids, scores, hidden_states, hidden_states_scale, gemm1_weights, gemm1_weights_scale, gemm2_weights,
+                     gemm2_weights_scale, gemm1_alpha, gemm1_beta, gemm1_clamp_limit, output1_scale_scalar, output1_scale_gate_scalar,
+                     output2_scale_scalar)
+        no_copies = all(k is None or k.data_ptr() == o.data_ptr() for k, o in zip(keep, originals))
+        if no_copies:      # only then does the cached argument block keep reading the caller's own memory
+            key = (id(ids), id(scores), id(hidden_states), id(hidden_states_scale), id(gemm1_weights), id(gemm1_weights_scale),
+                   id(gemm1_alpha), id(gemm1_beta), id(gemm1_clamp_limit), id(gemm2_weights), id(gemm2_weights_scale),
+                   id(output1_scale_scalar), id(output1_scale_gate_scalar), id(output2_scale_scalar), id(output), activation_type,
+                   local_expert_offset, top_k, intermediate_size, num_fused_shared_experts, local_num_experts, do_finalize,
+                   routed_scaling_factor, hidden_states.data_ptr(), output.data_ptr())
+            self._hot = (key, layer._h.value, C.addressof(args), result, dev, (args, originals, output, topk_ids, layer))
+        else:
+            self._hot = None
+        return result
 
 
 class DenseModel(torch.nn.Module):

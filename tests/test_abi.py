@@ -80,7 +80,7 @@ def test_pybind_shim_loads_and_maps_errors(lib):
     shim = _shim()
     assert shim.abi_version() == _lib.ABI_VERSION
     with pytest.raises(ValueError):
-        shim.create(100, 256, 4, 2, 0, 8, 0)
+        shim.create(100, 256, 4, 2, 0, 8, 0, 0)
     with pytest.raises(ValueError):
         shim.run(0, 1, *([0] * 21))
 

@@ -209,3 +209,75 @@ def test_layer_is_cuda_graph_capturable():
     assert torch.equal(out, eager)
     assert_layer_parity(out.float().cpu().numpy(), o.moe_expected(p), "graph replay")
     layer.close()
+
+
+def test_library_graph_cache_and_hot_call():
+    """b200moe_config.graph_cache: the second call with an identical argument block captures the launch chain, later ones
+    replay it; routing and activations are read from memory at replay time, another argument block misses. The drop-in
+    Model's repeat-call path (same tensor objects) goes through the same cache."""
+    import kernelschema_b200 as ks
+    from gpu_util import to_dev
+    p = make_moe_case(21, 200, 512, 256, 16, 4, shared=1, global_scales=True)
+    ids, scores = p["topk_ids"]
+    dev = dict(ids=to_dev(ids.astype(np.int32)), w=to_dev(scores.astype(np.float32)), hq=to_dev(p["hidden_states"]),
+               hs=to_dev(p["hidden_states_scale"]), w1=to_dev(p["gemm1_weights"]), s1=to_dev(p["gemm1_weights_scale"]),
+               w2=to_dev(p["gemm2_weights"]), s2=to_dev(p["gemm2_weights_scale"]))
+    kw = dict(scale_up=to_dev(p["output1_scale_scalar"]), scale_gate=to_dev(p["output1_scale_gate_scalar"]),
+              scale_out=to_dev(p["output2_scale_scalar"]))
+    eager = ks.MoELayer(512, 256, 16, 4, 200, num_shared_experts=1)
+    cached = ks.MoELayer(512, 256, 16, 4, 200, num_shared_experts=1, graph_cache=True)
+    out_e = torch.empty((200, 512), dtype=torch.bfloat16, device="cuda")
+    out_c = torch.empty_like(out_e)
+    run = lambda layer, out: layer.run(dev["ids"], dev["w"], dev["hq"], dev["hs"], dev["w1"], dev["s1"], dev["w2"], dev["s2"], out, **kw)
+    run(eager, out_e)
+    for _ in range(4):
+        out_c.fill_(-3)
+        run(cached, out_c)
+        assert torch.equal(out_c, out_e)
+    st = cached.stats()
+    assert (st["runs"], st["graph_captures"], st["graph_replays"]) == (4, 1, 2), st
+    # new routing and activations in the same buffers: the replayed graph reads them
+    p2 = make_moe_case(22, 200, 512, 256, 16, 4, shared=1, global_scales=True)
+    dev["ids"].copy_(to_dev(p2["topk_ids"][0].astype(np.int32)))
+    dev["w"].copy_(to_dev(p2["topk_ids"][1].astype(np.float32)))
+    dev["hq"].copy_(to_dev(p2["hidden_states"]))
+    dev["hs"].copy_(to_dev(p2["hidden_states_scale"]))
+    run(eager, out_e)
+    run(cached, out_c)
+    assert torch.equal(out_c, out_e) and cached.stats()["graph_replays"] == 3
+    # another output buffer is another argument block: eager first, then its own graph
+    out_d = torch.empty_like(out_e)
+    for _ in range(3):
+        run(cached, out_d)
+    assert torch.equal(out_d, out_e)
+    st = cached.stats()
+    assert st["graph_captures"] == 2 and st["graph_replays"] == 4 and st["graph_evictions"] == 0, st
+    # inside the caller's own stream capture the library launches into that capture instead of nesting one
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        run(cached, out_c)
+    torch.cuda.current_stream().wait_stream(side)
+    with torch.cuda.graph(g):
+        run(cached, out_c)
+    out_c.zero_()
+    g.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(out_c, out_e) and cached.stats()["eager_in_capture"] >= 1
+    assert cached.status() == 0
+    # the drop-in Model: three calls with the same objects -> validation once, then the cached argument block
+    from gpu_util import run_model
+    model = ks.Model()
+    got, kwm, model = run_model(p2, model)
+    ref = got.copy()
+    for _ in range(3):
+        kwm["output"].zero_()
+        res = model(**kwm)
+        torch.cuda.synchronize()
+        assert res[0] is kwm["output"]
+        assert np.array_equal(kwm["output"].float().cpu().numpy(), ref)
+    layer = next(iter(model._layers.values()))
+    assert layer.stats()["graph_replays"] >= 2
+    eager.close()
+    cached.close()
