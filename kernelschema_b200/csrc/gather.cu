@@ -46,18 +46,92 @@ __global__ void __launch_bounds__(256) k_gather_rows(const uint8_t* __restrict__
   }
 }
 
+// Tile form of the permute for row-major token scales: one block per 128-row tile of the permuted buffer. The tile's
+// scale image ([H/64] chunks of 512 bytes, the layout tcgen05.cp consumes) is assembled in shared memory - thread r
+// walks the scale bytes of row r's token with 16-byte loads - and leaves with full 16-byte coalesced stores; written
+// word by word from the rows it would cost one 32-byte sector per 4 bytes. Payload rows are copied by the warps, two rows
+// in flight per warp. Padding rows (past the tile's count) get zero scales and keep whatever payload they had.
+__global__ void __launch_bounds__(256) k_gather_tiles(const uint8_t* __restrict__ hid_q, const uint8_t* __restrict__ hid_sf,
+                                                      int64_t q_stride, int64_t sf_stride, const int32_t* __restrict__ tok_of_row,
+                                                      const int32_t* __restrict__ tile_rows, const int32_t* __restrict__ totals, int H,
+                                                      uint8_t* __restrict__ a_q, uint8_t* __restrict__ a_sf) {
+  extern __shared__ uint4 s_img4[];                 // [H/64][512 B]
+  uint32_t* s_img = reinterpret_cast<uint32_t*>(s_img4);
+  __shared__ int s_tok[128];
+  pdl_trigger();
+  pdl_wait();
+  const int n_tiles = totals[0];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int chunks = H >> 6;                        // 512-byte scale chunks per tile = 4-byte scale words per row
+  const int vec_per_row = H >> 5;                   // 16-byte vectors of payload per row
+  for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+    const int rows = tile_rows[tile];
+    const int row0 = tile << 7;
+    if (threadIdx.x < 128) s_tok[threadIdx.x] = threadIdx.x < rows ? tok_of_row[row0 + threadIdx.x] : -1;
+    __syncthreads();
+    if (threadIdx.x < 128) {
+      const int r = threadIdx.x;
+      const int tok = s_tok[r];
+      uint32_t* dst = s_img + (r & 31) * 4 + (r >> 5);          // word (row, chunk j) lives at j * 128 + (r % 32) * 4 + r / 32
+      if (tok >= 0) {
+        const uint4* src = reinterpret_cast<const uint4*>(hid_sf + (size_t)tok * sf_stride);
+        for (int j4 = 0; j4 < (chunks >> 2); ++j4) {
+          const uint4 v = __ldg(src + j4);
+          dst[(4 * j4 + 0) * 128] = v.x;
+          dst[(4 * j4 + 1) * 128] = v.y;
+          dst[(4 * j4 + 2) * 128] = v.z;
+          dst[(4 * j4 + 3) * 128] = v.w;
+        }
+      } else {
+        for (int j = 0; j < chunks; ++j) dst[j * 128] = 0u;
+      }
+    } else {
+      // the other four warps start on the payload meanwhile: rows 0, 4, 8, ... of the tile (the rest follows below)
+      for (int r = warp - 4; r < rows; r += 8) {
+        const uint4* src = reinterpret_cast<const uint4*>(hid_q + (size_t)s_tok[r] * q_stride);
+        uint4* dst = reinterpret_cast<uint4*>(a_q + (size_t)(row0 + r) * (H >> 1));
+        for (int v = lane; v < vec_per_row; v += 32) dst[v] = __ldg(src + v);
+      }
+    }
+    __syncthreads();
+    {
+      uint4* out = reinterpret_cast<uint4*>(a_sf + (size_t)tile * chunks * 512);
+      for (int i = threadIdx.x; i < chunks * 32; i += blockDim.x) out[i] = s_img4[i];
+    }
+    // payload rows 4..7 (mod 8) by warps 0..3, the other half by warps 4..7 above; two rows in flight per warp
+    if (warp < 4) {
+      for (int r = warp + 4; r < rows; r += 8) {
+        const uint4* src = reinterpret_cast<const uint4*>(hid_q + (size_t)s_tok[r] * q_stride);
+        uint4* dst = reinterpret_cast<uint4*>(a_q + (size_t)(row0 + r) * (H >> 1));
+        for (int v = lane; v < vec_per_row; v += 32) dst[v] = __ldg(src + v);
+      }
+    }
+    __syncthreads();                                  // s_tok and the image are reused by the next tile
+  }
+}
+
 int launch_gather_rows(const void* hid_q, const void* hid_sf, int hid_sf_tiled, int64_t q_stride, int64_t sf_stride,
                        const int32_t* tok_of_row, const int32_t* tile_rows, const int32_t* totals,
                        int H, int64_t row_capacity, void* a_q, void* a_sf, cudaStream_t st) {
   if (row_capacity == 0) return 0;
-  // Short rows (H <= 4096): a resident grid of 8 blocks per SM walks the rows (5.8 TB/s on 1 KB rows). Long rows: one warp
-  // per row of the capacity, so that every row's index -> source -> copy chain is in flight at once (DeepSeek-V3 geometry,
-  // 3.5 KB rows: 112 us against 128 us); rows past the count in `totals` exit at once.
+  const int64_t qs = q_stride > 0 ? q_stride : (int64_t)(H / 2), ss = sf_stride > 0 ? sf_stride : (int64_t)(H / 16);
+  const size_t img = (size_t)(H >> 6) * 512;
+  if (!hid_sf_tiled && H % 256 == 0 && ss % 16 == 0 && ((uintptr_t)hid_sf & 15) == 0 && img <= 96 * 1024) {
+    static SmemOptIn opt_in;
+    if (int e = opt_in.ensure(k_gather_tiles, (int)(96 * 1024))) return e;
+    int64_t blocks = row_capacity / 128;
+    const int64_t resident = (int64_t)sm_count() * (img > 48 * 1024 ? 3 : 6);
+    if (blocks > resident) blocks = resident;
+    if (blocks < 1) blocks = 1;
+    return (int)launch_chain(k_gather_tiles, dim3((unsigned)blocks), dim3(256), img, st, (const uint8_t*)hid_q, (const uint8_t*)hid_sf,
+                             qs, ss, tok_of_row, tile_rows, totals, H, (uint8_t*)a_q, (uint8_t*)a_sf);
+  }
+  // Tiled token scales (or odd strides): one warp per permuted row. Short rows (H <= 4096): a resident grid of 8 blocks per
+  // SM walks the rows. Long rows: one warp per row of the capacity; rows past the count in `totals` exit at once.
   int64_t blocks = (row_capacity + 7) / 8;
   if (H <= 4096 && blocks > (int64_t)sm_count() * 8) blocks = (int64_t)sm_count() * 8;
   return (int)launch_chain(k_gather_rows, dim3((unsigned)blocks), dim3(256), 0, st, (const uint8_t*)hid_q, (const uint8_t*)hid_sf,
-                           hid_sf_tiled, q_stride > 0 ? q_stride : (int64_t)(H / 2), sf_stride > 0 ? sf_stride : (int64_t)(H / 16),
-                           tok_of_row, tile_rows, totals, H, (uint8_t*)a_q, (uint8_t*)a_sf);
+                           hid_sf_tiled, qs, ss, tok_of_row, tile_rows, totals, H, (uint8_t*)a_q, (uint8_t*)a_sf);
 }
 
 // ----------------------------------------------------------------------------- expert-parallel dispatch packing

@@ -30,7 +30,8 @@ namespace b200 {
 constexpr int kBM = 128;
 constexpr int kStageK = 256;             // FP4 elements of K per pipeline stage (128 payload bytes per row)
 constexpr int kSfChunk = 512;            // bytes of one (128 rows x 64 K) scale-factor chunk
-constexpr int kCopiers = 2;              // warps that issue the scale-factor copies of a stage, half of them each
+constexpr int kCopiers = 2;              // warps that issue the scale-factor copies of a stage, round-robin (a third would make
+                                         // 13 or 21 warps: one more warp on an SM sub-partition costs the epilogue its registers)
 
 template <int BN>
 struct GemmCfg {
@@ -47,7 +48,6 @@ struct GemmCfg {
   // one TMEM scale-factor buffer per pipeline stage: a copier can run as far ahead of the MMA thread as the stage ring lets it
   static_assert(kSfBase + kStages * kSfCols <= 512, "TMEM budget");
   static constexpr int kSfCopies = 4 + 4 * (BN / 128);           // tcgen05.cp per stage
-  static_assert(kSfCopies % kCopiers == 0, "copies split evenly over the copier warps");
 };
 
 // Cycle accounting of the MMA thread (where it waits), compiled only into experiment builds (-DB200MOE_PROBE).
@@ -194,7 +194,7 @@ DEV void epilogue_cols(const GemmParams& p, uint32_t taddr, int e, size_t row, b
 // TMEM), then 4 * BN/EC epilogue warps; epilogue warp w owns TMEM lane quadrant w & 3 and the EC-column group
 // (w - kFirstEpiWarp) / 4.
 constexpr int kFirstEpiWarp = 2 + kCopiers;
-static_assert(kFirstEpiWarp % 4 == 0, "epilogue warp w must own lane quadrant w & 3 with groups of four consecutive warps");
+// any four consecutive warps own the four TMEM lane quadrants (quadrant = warp & 3), so the epilogue groups may start anywhere
 template <int BN, int EC>
 constexpr int gemm_threads() { return 32 * (kFirstEpiWarp + 4 * BN / EC); }
 
@@ -211,12 +211,11 @@ DEV void sf_copy(int j, uint32_t sf_t, uint32_t sfa_lo, uint32_t sfb_lo) {
   }
 }
 
-// The scale-factor copies of copier warp C: copies [C * n, (C + 1) * n) of every stage, n = kSfCopies / kCopiers.
+// The scale-factor copies of copier warp C: copies C, C + kCopiers, C + 2 * kCopiers, ... of every stage.
 template <int BN, int C>
 DEV void copier_loop(const GemmParams& p, uint32_t tmem, uint32_t s_sfa, uint32_t s_sfb, uint32_t bar_full, uint32_t bar_sf,
                      long long total_items, int nk) {
   using Cfg = GemmCfg<BN>;
-  constexpr int kPer = Cfg::kSfCopies / kCopiers;
   const uint32_t sfa_lo0 = (s_sfa >> 4) & 0x3FFF, sfb_lo0 = (s_sfb >> 4) & 0x3FFF;
   uint32_t s = 0, ph = 0;
   for (long long item = blockIdx.x; item < total_items; item += gridDim.x) {
@@ -226,7 +225,7 @@ DEV void copier_loop(const GemmParams& p, uint32_t tmem, uint32_t s_sfa, uint32_
       const uint32_t sf_t = tmem + Cfg::kSfBase + s * Cfg::kSfCols;
       const uint32_t sfa_lo = sfa_lo0 + s * (Cfg::kSfaBytes >> 4), sfb_lo = sfb_lo0 + s * (Cfg::kSfbBytes >> 4);
 #pragma unroll
-      for (int j = C * kPer; j < (C + 1) * kPer; ++j) sf_copy<BN>(j, sf_t, sfa_lo, sfb_lo);
+      for (int j = C; j < Cfg::kSfCopies; j += kCopiers) sf_copy<BN>(j, sf_t, sfa_lo, sfb_lo);
       mma_commit(bar_sf + 8 * s);                      // arrives once this thread's copies have landed
       if (++s == Cfg::kStages) { s = 0; ph ^= 1; }
     }
@@ -328,7 +327,8 @@ k_gemm_nvfp4(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
     // ------------------------------------------------------------------ scale-factor copiers: shared memory -> TMEM
     if (lane == 0) {
       if (warp == 2) copier_loop<BN, 0>(p, tmem, s_sfa, s_sfb, bar_full, bar_sf, total_items, nk);
-      else copier_loop<BN, kCopiers - 1>(p, tmem, s_sfa, s_sfb, bar_full, bar_sf, total_items, nk);
+      else if (warp == 3) copier_loop<BN, 1 % kCopiers>(p, tmem, s_sfa, s_sfb, bar_full, bar_sf, total_items, nk);
+      else copier_loop<BN, 2 % kCopiers>(p, tmem, s_sfa, s_sfb, bar_full, bar_sf, total_items, nk);
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
@@ -506,8 +506,7 @@ k_gemm_nvfp4_pair(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     // ------------------------------------------------------------------ scale-factor copiers (leader; every copy acts on both CTAs)
     if (leader && lane == 0) {
       constexpr uint32_t kHiSf = (128u >> 4) | (1u << 14);
-      constexpr int kPer = 12 / kCopiers;
-      const int j0 = (warp - 2) * kPer;
+      const int j0 = warp - 2;
       const uint32_t sfa_lo0 = (s_sfa >> 4) & 0x3FFF, sfb_lo0 = (s_sfb >> 4) & 0x3FFF;
       uint32_t s = 0, ph = 0;
       bool ok = true;
@@ -517,9 +516,7 @@ k_gemm_nvfp4_pair(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
           tc_fence_after();
           const uint32_t sf_t = tmem + C::kSfBase + s * C::kSfCols;
           const uint32_t sfa_lo = sfa_lo0 + s * (C::kSfaBytes >> 4), sfb_lo = sfb_lo0 + s * (C::kSfbBytes >> 4);
-#pragma unroll
-          for (int jj = 0; jj < kPer; ++jj) {
-            const int j = j0 + jj;                       // copy j of the stage: 0..3 A scales, then B scales (half h, k-block q)
+          for (int j = j0; j < 12; j += kCopiers) {    // copy j of the stage: 0..3 A scales, then B scales (half h, k-block q)
             if (j < 4) {
               tmem_cp_sf_pair(sf_t + 4 * j, ((uint64_t)kHiSf << 32) | (sfa_lo + j * (kSfChunk >> 4)));
             } else {
