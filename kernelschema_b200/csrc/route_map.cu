@@ -126,25 +126,28 @@ __global__ void __launch_bounds__(1024) k_route_scan(int etot, int nblk, int32_t
   pdl_trigger();
   pdl_wait();
   if (threadIdx.x < 4) carry[threadIdx.x] = 0;
+  // Exclusive prefix over the blocks, one WARP per expert: lanes take blocks lane, lane + 32, ... (all loads of a round in
+  // flight at once), a shuffle scan orders them; the fixed order keeps every output reproducible.
+  for (int e = warp; e < etot; e += (int)(blockDim.x >> 5)) {
+    int run = 0;
+    for (int b0 = 0; b0 < nblk; b0 += 32) {
+      const int b = b0 + lane;
+      const int v = b < nblk ? block_hist[(int64_t)b * etot + e] : 0;
+      int inc = v;
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const int a = __shfl_up_sync(0xFFFFFFFFu, inc, off);
+        if (lane >= off) inc += a;
+      }
+      if (b < nblk) block_hist[(int64_t)b * etot + e] = run + inc - v;
+      run += __shfl_sync(0xFFFFFFFFu, inc, 31);
+    }
+    if (lane == 0) counts[e] = run;
+  }
   __syncthreads();
   for (int e0 = 0; e0 < etot; e0 += blockDim.x) {
     const int e = e0 + threadIdx.x;
-    int cnt = 0;
-    if (e < etot) {
-      // exclusive prefix over the blocks; loads run 8 ahead of the stores so their latencies overlap
-      for (int b0 = 0; b0 < nblk; b0 += 8) {
-        int v[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) v[j] = (b0 + j < nblk) ? block_hist[(int64_t)(b0 + j) * etot + e] : 0;
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-          if (b0 + j < nblk) {
-            block_hist[(int64_t)(b0 + j) * etot + e] = cnt;
-            cnt += v[j];
-          }
-      }
-      counts[e] = cnt;
-    }
+    const int cnt = e < etot ? counts[e] : 0;
     const int ntile = (cnt + 127) >> 7;
     const int pad = ntile << 7;
     const int npair = (ntile + 1) >> 1;        // 256-row work items of the CTA-pair GEMM

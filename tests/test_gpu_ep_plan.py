@@ -104,3 +104,30 @@ def test_peer_memory_exchange_single_rank_loop(shared, tokens):
     finally:
         if own:
             dist.destroy_process_group()
+
+
+def test_ep_wait_is_bounded_and_reports():
+    """A flag that nobody sets: the device-side wait gives up after its poll limit (a few seconds), records status code 301
+    on the layer and returns; the context stays usable and a later wait on a flag that IS set succeeds."""
+    import time
+    import kernelschema_b200 as ks
+    from kernelschema_b200 import _lib
+    lib = _lib.load()
+    layer = ks.MoELayer(256, 256, 2, 2, 128)
+    flags = torch.zeros(4, dtype=torch.int32, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    assert layer.status() == 0
+    t0 = time.perf_counter()
+    _lib.check(lib.b200moe_ep_wait(layer._h, flags.data_ptr(), 2, 7, stream), "b200moe_ep_wait")
+    torch.cuda.synchronize()
+    waited = time.perf_counter() - t0
+    assert 0.2 < waited < 30.0, waited
+    assert layer.status() == 301
+    flags.fill_(7)
+    t0 = time.perf_counter()
+    _lib.check(lib.b200moe_ep_wait(layer._h, flags.data_ptr(), 4, 7, stream), "b200moe_ep_wait")
+    torch.cuda.synchronize()
+    assert time.perf_counter() - t0 < 0.2
+    x = torch.ones(8, device="cuda")
+    assert float((x * 2).sum()) == 16.0
+    layer.close()

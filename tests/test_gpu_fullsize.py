@@ -100,3 +100,34 @@ def test_full_size_properties_and_samples(name, n_sample):
     ref = _oracle_for_tokens(wl, L, ids, w, hq, hs, tokens)
     assert_layer_parity(base[torch.as_tensor(tokens, device=ids.device)].float().cpu().numpy(), ref, f"{name} sampled tokens")
     layer.close()
+
+
+def test_peer_memory_exchange_full_size_single_rank():
+    """The expert-parallel peer-memory path at the benchmark's size on ONE GPU (a group of one rank is its own peer): 8192
+    tokens, 256 + 1 experts. Its result may differ from the plain layer's only by the one extra bf16 rounding of the partial
+    row that travels (exactly reproduced here: round the routed part to bf16, add the shared row, round again is NOT what
+    the layer does, so compare with the parity rule instead)."""
+    import socket
+    import torch.distributed as dist
+    from kernelschema_b200.ep import ExpertParallelMoE
+    wl, L, (ids, w, hq, hs), run, layer = _setup("dsv3")
+    base = run(ids, w, hq, hs)
+    own = not dist.is_initialized()
+    if own:
+        with socket.socket() as sock:
+            sock.bind(("127.0.0.1", 0))
+            port = sock.getsockname()[1]
+        dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=0, world_size=1)
+    try:
+        ep = ExpertParallelMoE(wl["h"], wl["i"], wl["e"], wl["k"], wl["t"], num_shared_experts=wl["s"], transport="p2p")
+        for _ in range(2):
+            out = ep.forward(ids, w, hq, hs.view(torch.uint8), L["w1q"], L["w1s"], L["w2q"], L["w2s"], scale_up=L["scale_fc1"],
+                             scale_gate=L["scale_fc1"], scale_out=L["scale_fc2"])
+        torch.cuda.synchronize()
+        assert ep.status() == 0
+        assert_layer_parity(out.float().cpu().numpy(), base.float().cpu().numpy(), "p2p world=1 at full size", extra_bf16_roundings=1)
+        ep.close()
+    finally:
+        if own:
+            dist.destroy_process_group()
+    layer.close()
