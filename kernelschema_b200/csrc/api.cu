@@ -65,6 +65,7 @@ struct b200moe_layer {
   __nv_bfloat16* rout;
   int32_t* status;
   CUtensorMap tm_a1, tm_a2, tm_b1, tm_b2;
+  CUtensorMap tm_b1_narrow, tm_b2_narrow;             // weight maps with 128-row boxes: small batches run 128 x 128 tiles
   CUtensorMap tm_sfa1, tm_sfa2, tm_sfb1, tm_sfb2;   // scale-factor maps of the CTA-pair GEMM
   int n_clusters;                                    // CTA pairs that can be co-resident
   const void* b1_ptr;
@@ -204,6 +205,7 @@ int run_impl(b200moe_layer* h, const b200moe_args* a, cudaStream_t st, cudaEvent
   mark(2);
   if (h->b1_ptr != a->gemm1_weights || h->s1_ptr != a->gemm1_weights_scale) {
     rc = make_operand_map(&h->tm_b1, a->gemm1_weights, (uint64_t)h->etot * 2 * c.intermediate, c.hidden / 2, h->bn == 512 ? 128 : h->bn);
+    if (!rc) rc = make_operand_map(&h->tm_b1_narrow, a->gemm1_weights, (uint64_t)h->etot * 2 * c.intermediate, c.hidden / 2, 128);
     if (!rc && h->bn == 512)
       rc = make_sf_map(&h->tm_sfb1, a->gemm1_weights_scale, (uint64_t)h->etot * 2 * c.intermediate / 128 * (c.hidden / 64));
     if (rc) return cuda_fail(rc, "FC1 weight tensor map");
@@ -212,6 +214,7 @@ int run_impl(b200moe_layer* h, const b200moe_args* a, cudaStream_t st, cudaEvent
   }
   if (h->b2_ptr != a->gemm2_weights || h->s2_ptr != a->gemm2_weights_scale) {
     rc = make_operand_map(&h->tm_b2, a->gemm2_weights, (uint64_t)h->etot * c.hidden, c.intermediate / 2, h->bn == 512 ? 128 : h->bn);
+    if (!rc) rc = make_operand_map(&h->tm_b2_narrow, a->gemm2_weights, (uint64_t)h->etot * c.hidden, c.intermediate / 2, 128);
     if (!rc && h->bn == 512)
       rc = make_sf_map(&h->tm_sfb2, a->gemm2_weights_scale, (uint64_t)h->etot * c.hidden / 128 * (c.intermediate / 64));
     if (rc) return cuda_fail(rc, "FC2 weight tensor map");
@@ -238,21 +241,29 @@ int run_impl(b200moe_layer* h, const b200moe_args* a, cudaStream_t st, cudaEvent
   g.beta = a->gemm1_beta;
   g.limit = a->gemm1_clamp_limit;
   g.act_type = a->activation_type;
+  // m-tiles of this call at most: an expert with c routes owns ceil(c / 128) tiles, and no more experts are touched than
+  // there are routes. Small batches (decode) are bound by how fast ONE SM can pull its item's weights: when 256-wide
+  // tiles would leave half of the SMs without an item, 128-wide tiles double the number of SMs that stream.
+  const int64_t routes = (int64_t)T * h->kk;
+  const int64_t worst_tiles = routes / 128 + (routes < h->etot ? routes : (int64_t)h->etot);
+  auto tile_n_for = [&](int n_cols) {
+    if (h->bn != 256 || c.tile_n != 0) return h->bn;
+    return worst_tiles * (n_cols / 256) * 2 <= h->sm_count ? 128 : 256;
+  };
   {
-    const int64_t worst_tiles = (int64_t)T * h->kk / 128 + h->etot;
-    const int64_t items = worst_tiles * (g.N / h->bn);
+    const int bn = tile_n_for(g.N);
+    const int64_t items = worst_tiles * (g.N / (bn == 512 ? 256 : bn));
     const int grid = (int)(items < h->sm_count ? items : h->sm_count);
-    if (h->bn == 512) {
+    if (bn == 512) {
       GemmParams gp = g;
       gp.tile_expert = h->rm.pair_expert;
       gp.tile_row0 = h->rm.pair_row0;
       gp.tile_rows = h->rm.pair_rows;
       gp.n_tiles_ptr = h->rm.totals + 3;
-      const int64_t pair_items = worst_tiles * (g.N / 256);
       rc = launch_gemm_nvfp4_pair(kGemmFc1, h->tm_a1, h->tm_b1, h->tm_sfa1, h->tm_sfb1, gp,
-                                  (int)(pair_items < h->n_clusters ? pair_items : h->n_clusters), st);
+                                  (int)(items < h->n_clusters ? items : h->n_clusters), st);
     } else {
-      rc = launch_gemm_nvfp4(kGemmFc1, h->bn, h->tm_a1, h->tm_b1, g, grid, st);
+      rc = launch_gemm_nvfp4(kGemmFc1, bn, h->tm_a1, bn == h->bn ? h->tm_b1 : h->tm_b1_narrow, g, grid, st);
     }
     if (rc) return cuda_fail(rc, "FC1");
   }
@@ -271,20 +282,19 @@ int run_impl(b200moe_layer* h, const b200moe_args* a, cudaStream_t st, cudaEvent
     g.out_row_index = h->rm.tok_of_row;
   }
   {
-    const int64_t worst_tiles = (int64_t)T * h->kk / 128 + h->etot;
-    const int64_t items = worst_tiles * (g.N / h->bn);
+    const int bn = tile_n_for(g.N);
+    const int64_t items = worst_tiles * (g.N / (bn == 512 ? 256 : bn));
     const int grid = (int)(items < h->sm_count ? items : h->sm_count);
-    if (h->bn == 512) {
+    if (bn == 512) {
       GemmParams gp = g;
       gp.tile_expert = h->rm.pair_expert;
       gp.tile_row0 = h->rm.pair_row0;
       gp.tile_rows = h->rm.pair_rows;
       gp.n_tiles_ptr = h->rm.totals + 3;
-      const int64_t pair_items = worst_tiles * (g.N / 256);
       rc = launch_gemm_nvfp4_pair(kGemmFc2, h->tm_a2, h->tm_b2, h->tm_sfa2, h->tm_sfb2, gp,
-                                  (int)(pair_items < h->n_clusters ? pair_items : h->n_clusters), st);
+                                  (int)(items < h->n_clusters ? items : h->n_clusters), st);
     } else {
-      rc = launch_gemm_nvfp4(kGemmFc2, h->bn, h->tm_a2, h->tm_b2, g, grid, st);
+      rc = launch_gemm_nvfp4(kGemmFc2, bn, h->tm_a2, bn == h->bn ? h->tm_b2 : h->tm_b2_narrow, g, grid, st);
     }
     if (rc) return cuda_fail(rc, "FC2");
   }

@@ -89,6 +89,7 @@ DEV void chunk_histogram(const int (&e)[kRouteSteps], int etot, int* hist) {
   __syncthreads();
 #pragma unroll
   for (int step = 0; step < kRouteSteps; ++step) {
+    if (!__any_sync(0xFFFFFFFFu, e[step] >= 0)) continue;      // a step without a route (decode sizes: most of them)
     const unsigned m = same_expert_lanes(e[step], bits);
     if (e[step] >= 0 && lane == (__ffs(m) - 1)) hist[warp * etot + e[step]] += __popc(m);
     __syncwarp();
@@ -239,8 +240,9 @@ __global__ void __launch_bounds__(256) k_route_scatter(RouteView r, const float*
 #pragma unroll
   for (int step = 0; step < kRouteSteps; ++step) {
     const int e = ex[step];
-    const unsigned m = same_expert_lanes(e, expert_bits(etot));
     pos[step] = -1;
+    if (!__any_sync(0xFFFFFFFFu, e >= 0)) continue;
+    const unsigned m = same_expert_lanes(e, expert_bits(etot));
     if (e >= 0) pos[step] = hist[warp * etot + e] + __popc(m & ((1u << lane) - 1u));
     __syncwarp();
     if (e >= 0 && lane == (__ffs(m) - 1)) hist[warp * etot + e] += __popc(m);
@@ -375,8 +377,9 @@ __global__ void __launch_bounds__(256) k_route_fused(RouteView r, const float* _
 #pragma unroll
   for (int step = 0; step < kRouteSteps; ++step) {
     const int e = ex[step];
-    const unsigned m = same_expert_lanes(e, expert_bits(etot));
     pos[step] = -1;
+    if (!__any_sync(0xFFFFFFFFu, e >= 0)) continue;
+    const unsigned m = same_expert_lanes(e, expert_bits(etot));
     if (e >= 0) pos[step] = hist[warp * etot + e] + __popc(m & ((1u << lane) - 1u));
     __syncwarp();
     if (e >= 0 && lane == (__ffs(m) - 1)) hist[warp * etot + e] += __popc(m);
