@@ -45,7 +45,7 @@ ACT_GLOBAL_SCALE = 5.7 / (6.0 * 448.0)
 FP4_NOMINAL_TFLOPS = 9000.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one FC1 launch, from the ncu captures summarised in
 # profiles/bench_dsv3_T8192_launch_list.md and profiles/layer_kernels_qwen3_T16384_ncu_full.md (workload -> bytes).
-FC1_DRAM_TRAFFIC = {"dsv3": 4966850048 + 79877632, "qwen3": 386940416 + 49309952}
+FC1_DRAM_TRAFFIC = {"dsv3": 4823125760 + 80460288, "qwen3": 386940416 + 49309952}
 REF_DIR = os.path.join(ROOT, "oracle", "_ref")
 
 

@@ -36,6 +36,8 @@ def test_struct_sizes_match_header(lib):
     assert C.sizeof(_lib.Config) == 16 * 4
     assert C.sizeof(_lib.Args) == 8 + 8 * 4 + 8 + 8 * 10 + 8 + 16 + 24
     assert C.sizeof(_lib.WorkspaceView) == 14 * 8 + 16 + 24
+    assert C.sizeof(_lib.EpPeers) == 8 + 3 * 16 * 8
+    assert C.sizeof(_lib.Stats) == 6 * 8
 
 
 def test_bad_config_is_refused_without_a_device(lib):
@@ -58,6 +60,18 @@ def test_argument_checks_precede_launches(lib):
     assert lib.b200moe_route_topk(None, None, 4, 8, 9, None, None, None) == 750
     assert lib.b200moe_gemm_nvfp4(None, None, None, None, 1.0, None, 4, 128, 100, 128, 0, None, None) == 761
     assert lib.b200moe_run(None, None, None) == 720
+    # expert-parallel exchange and diagnostics
+    assert lib.b200moe_run_ep(None, None, None, None, 128, None) == 720
+    assert lib.b200moe_ep_wait(None, None, 2, 1, None) == 796
+    assert lib.b200moe_ep_post(None, 32, 1, None) == 796
+    assert lib.b200moe_ep_dispatch(None, None, None, None, None, 4, 256, 2, 2, 4096, None, 1, 0, 0, None, None) == 792
+    assert lib.b200moe_ep_shared_alloc(0, None, None) == 797
+    assert lib.b200moe_ep_shared_open(None, None) == 797
+    assert lib.b200moe_ep_shared_close(None) == 0 and lib.b200moe_ep_shared_free(None) == 0
+    assert lib.b200moe_get_stats(None, None) == 719
+    from kernelschema_b200 import _lib
+    bad = _lib.EpPeers(world=99, rank=0)
+    assert lib.b200moe_ep_post(C.byref(bad), _lib.EP_FLAG_RETURN, 1, None) == 796 and b"world" in lib.b200moe_last_error()
 
 
 def test_model_refuses_cpu_tensors():
