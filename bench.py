@@ -184,14 +184,16 @@ def make_step(wl, L, world, device, tokens=None):
         return hq[:n], hs[:n], ids[:n], w[:n]
 
     if world == 1:
-        layer = ks.MoELayer(h, i, L["e_local"], k, t, num_shared_experts=s)
+        # one library call per step (b200moe_step: quantiser, router logits, top-k / softmax, layer), replayed from the
+        # library's own CUDA graph after the second call with the same buffers
+        layer = ks.MoELayer(h, i, L["e_local"], k, t, num_shared_experts=s, graph_cache=True)
+        ids_view = layer.step_outputs(t)["ids"]
 
         def step(x, out=None):
             out = out_own[:x.shape[0]] if out is None else out
-            q, sf, ids_, w_ = front(x)
-            layer.run(ids_, w_, q, sf, L["w1q"], L["w1s"], L["w2q"], L["w2s"], out, scale_up=L["scale_fc1"],
-                      scale_gate=L["scale_fc1"], scale_out=L["scale_fc2"])
-            return out, ids_
+            layer.step(x, L["gate_w"], L["bias"], ACT_GLOBAL_SCALE, L["w1q"], L["w1s"], L["w2q"], L["w2s"], out,
+                       scale_up=L["scale_fc1"], scale_gate=L["scale_fc1"], scale_out=L["scale_fc2"])
+            return out, ids_view[:x.shape[0]]
 
         step.front = front
         return step, layer, 10

@@ -102,6 +102,8 @@ typedef struct {
   int32_t* pair_expert;   /* [tile_capacity] 256-row work items of the CTA-pair GEMM: expert, */
   int32_t* pair_row0;     /*                 first permuted row,                               */
   int32_t* pair_rows;     /*                 valid rows (1..256)                               */
+  int32_t* step_ids;      /* [max_tokens, top_k] experts selected by the last b200moe_step */
+  float* step_weights;    /* [max_tokens, top_k] and their routing weights */
 } b200moe_workspace_view;
 
 int b200moe_abi_version(void);
@@ -252,6 +254,35 @@ int b200moe_run(b200moe_handle h, const b200moe_args* args, void* stream);
 /* Same, recording CUDA events between stages and returning their durations in milliseconds (synchronises).
  * stage_ms[0..4] = route map, permute, FC1, FC2, combine. Counterpart of moe_profile, NV/candidate/nvfp4_moe.cu:9678. */
 int b200moe_run_profiled(b200moe_handle h, const b200moe_args* args, void* stream, float* stage_ms);
+/* The whole step in one call, from bf16 tokens: (2) NVFP4 quantiser with a global scale, (1) router logits x * gate^T,
+ * top-k / softmax (optional logit bias), then (3)+(4) the layer as b200moe_run with local_expert_offset 0. The quantised
+ * tokens, logits, ids and weights live in the layer's workspace. With b200moe_config.graph_cache the chain of ~10 launches
+ * is replayed as one graph from the second identical call on. No counterpart in the reference, whose operator starts from
+ * routed NVFP4 inputs (NV/problem/input.py:101-112 generates them on the host side of its boundary). */
+typedef struct {
+  int32_t struct_size;               /* sizeof(b200moe_step_args) */
+  int32_t num_tokens;
+  const void* x;                     /* bf16 [T, H] */
+  int64_t x_stride;                  /* elements between rows of x (>= H, multiple of 8) */
+  const void* gate_weight;           /* bf16 [E, H] router matrix (E = num_experts of the layer) */
+  const float* gate_bias;            /* fp32 [E] added to the logits before selection, or NULL */
+  float activation_global_scale;     /* global scale of the activation quantiser (> 0) */
+  int32_t activation_type;           /* as b200moe_args */
+  const void* gemm1_weights;
+  const void* gemm1_weights_scale;
+  const void* gemm2_weights;
+  const void* gemm2_weights_scale;
+  const float* gemm1_alpha;
+  const float* gemm1_beta;
+  const float* gemm1_clamp_limit;
+  const float* output1_scale_scalar;
+  const float* output1_scale_gate_scalar;
+  const float* output2_scale_scalar;
+  void* output;                      /* bf16 [T, H] */
+  int64_t output_stride;
+} b200moe_step_args;
+int b200moe_step(b200moe_handle h, const b200moe_step_args* args, void* stream);
+
 /* Host-side counters of a layer (counterpart of the reference's graph_status() / nvfp4_fast.stats(),
  * NV/candidate/nvfp4_moe.cu:9618-9702, NV/candidate/nvfp4_fast.c:139-145). */
 typedef struct {

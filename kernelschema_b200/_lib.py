@@ -43,6 +43,16 @@ class EpPeers(C.Structure):
                 ("ret", C.c_void_p * EP_MAX_RANKS)]
 
 
+class StepArgs(C.Structure):
+    _fields_ = [("struct_size", C.c_int32), ("num_tokens", C.c_int32), ("x", C.c_void_p), ("x_stride", C.c_int64),
+                ("gate_weight", C.c_void_p), ("gate_bias", C.c_void_p), ("activation_global_scale", C.c_float),
+                ("activation_type", C.c_int32), ("gemm1_weights", C.c_void_p), ("gemm1_weights_scale", C.c_void_p),
+                ("gemm2_weights", C.c_void_p), ("gemm2_weights_scale", C.c_void_p), ("gemm1_alpha", C.c_void_p),
+                ("gemm1_beta", C.c_void_p), ("gemm1_clamp_limit", C.c_void_p), ("output1_scale_scalar", C.c_void_p),
+                ("output1_scale_gate_scalar", C.c_void_p), ("output2_scale_scalar", C.c_void_p), ("output", C.c_void_p),
+                ("output_stride", C.c_int64)]
+
+
 class Stats(C.Structure):
     _fields_ = [("runs", C.c_int64), ("graph_replays", C.c_int64), ("graph_captures", C.c_int64), ("graph_evictions", C.c_int64),
                 ("eager_in_capture", C.c_int64), ("workspace_bytes", C.c_int64)]
@@ -53,7 +63,8 @@ class WorkspaceView(C.Structure):
                 ("tile_rows", C.c_void_p), ("totals", C.c_void_p), ("row_of", C.c_void_p), ("tok_of_row", C.c_void_p),
                 ("weight_of_row", C.c_void_p), ("a_q", C.c_void_p), ("a_sf", C.c_void_p), ("act_q", C.c_void_p),
                 ("act_sf", C.c_void_p), ("rout", C.c_void_p), ("row_capacity", C.c_int64), ("tile_capacity", C.c_int64),
-                ("pair_expert", C.c_void_p), ("pair_row0", C.c_void_p), ("pair_rows", C.c_void_p)]
+                ("pair_expert", C.c_void_p), ("pair_row0", C.c_void_p), ("pair_rows", C.c_void_p), ("step_ids", C.c_void_p),
+                ("step_weights", C.c_void_p)]
 
 
 #: every exported symbol with (restype, argtypes); the CPU test checks the library exports exactly these
@@ -96,6 +107,7 @@ SIGNATURES = {
     "b200moe_run_profiled": (C.c_int, [C.c_void_p, C.POINTER(Args), C.c_void_p, C.POINTER(C.c_float)]),
     "b200moe_status": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_int32)]),
     "b200moe_get_stats": (C.c_int, [C.c_void_p, C.POINTER(Stats)]),
+    "b200moe_step": (C.c_int, [C.c_void_p, C.POINTER(StepArgs), C.c_void_p]),
 }
 
 _lib = None

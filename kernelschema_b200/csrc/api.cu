@@ -65,7 +65,11 @@ struct b200moe_layer {
   __nv_bfloat16* rout;
   int32_t* status;
   CUtensorMap tm_a1, tm_a2, tm_b1, tm_b2;
-  CUtensorMap tm_b1_narrow, tm_b2_narrow;             // weight maps with 128-row boxes: small batches run 128 x 128 tiles
+  CUtensorMap tm_b1_narrow, tm_b2_narrow;
+  uint8_t *step_hq, *step_hs;                         // b200moe_step: quantised tokens,
+  float* step_logits;                                 //               router logits,
+  int32_t* step_ids;                                  //               selected experts
+  float* step_w;                                      //               and their weights             // weight maps with 128-row boxes: small batches run 128 x 128 tiles
   CUtensorMap tm_sfa1, tm_sfa2, tm_sfb1, tm_sfb2;   // scale-factor maps of the CTA-pair GEMM
   int n_clusters;                                    // CTA pairs that can be co-resident
   const void* b1_ptr;
@@ -74,7 +78,8 @@ struct b200moe_layer {
   const void* s2_ptr;
   // graph cache of b200moe_run (cfg.graph_cache): entries keyed on the whole argument block and the stream
   struct Cached {
-    b200moe_args key;
+    uint8_t key[320];         // the argument block of b200moe_run or b200moe_step, fields copied into a zeroed buffer
+    int key_bytes;
     cudaStream_t stream;
     cudaGraphExec_t exec;     // null: the key was seen once, the next identical call captures
     uint64_t last_use;
@@ -91,7 +96,7 @@ int64_t align_up(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
 struct Plan {
   int64_t row_capacity, tile_capacity, nblk;
   int64_t off_block_hist, off_counts, off_seg, off_texp, off_trow0, off_trows, off_pexp, off_prow0, off_prows, off_totals, off_row_of, off_tok, off_w, off_aq,
-      off_asf, off_actq, off_actsf, off_rout, off_status, total;
+      off_asf, off_actq, off_actsf, off_rout, off_status, off_step_hq, off_step_hs, off_step_logits, off_step_ids, off_step_w, total;
 };
 
 int check_cfg(const b200moe_config* c) {
@@ -140,6 +145,12 @@ Plan make_plan(const b200moe_config& c) {
   p.off_actsf = take(p.row_capacity * (c.intermediate / 16));
   p.off_rout = take(p.row_capacity * c.hidden * 2);
   p.off_status = take(16);
+  // buffers of b200moe_step (bf16 tokens in): NVFP4 tokens, router logits over the routed experts, top-k ids and weights
+  p.off_step_hq = take((int64_t)c.max_tokens * (c.hidden / 2));
+  p.off_step_hs = take((int64_t)c.max_tokens * (c.hidden / 16));
+  p.off_step_logits = take((int64_t)c.max_tokens * (c.num_experts > 0 ? c.num_experts : 1) * 4);
+  p.off_step_ids = take((int64_t)c.max_tokens * (c.top_k > 0 ? c.top_k : 1) * 4);
+  p.off_step_w = take((int64_t)c.max_tokens * (c.top_k > 0 ? c.top_k : 1) * 4);
   p.total = o;
   return p;
 }
@@ -345,16 +356,19 @@ int b200moe_route_topk(const float* logits, const float* bias, int64_t T, int32_
   return cuda_fail(launch_route_topk(logits, bias, T, E, K, ids, weights, (cudaStream_t)stream), "route_topk");
 }
 
+static int router_logits_any(const void* x, const void* w, int64_t T, int H, int E, float* logits, cudaStream_t st) {
+  if (T <= 16)      // decode sizes: stream the gate matrix over the whole device
+    return launch_router_logits_small(x, w, T, H, E, logits, st);
+  // tensor-core path: whole gate matrix as one B tile (E <= 256), K in 64-element stages, 16-byte aligned rows
+  if (E <= 256 && H % 64 == 0 && E % 8 == 0) return launch_router_logits_tc(x, w, T, H, E, logits, nullptr, st);
+  return launch_router_logits(x, w, T, H, E, logits, st);
+}
+
 int b200moe_router_logits(const void* x, const void* w, int64_t T, int32_t H, int32_t E, float* logits, void* stream) {
   if (T < 0 || H <= 0 || H % 8 || E <= 0) return fail(752, "router_logits: hidden must be a positive multiple of 8");
   if (T && (!x || !w || !logits)) return fail(753, "router_logits: null pointer");
   if (((uintptr_t)x | (uintptr_t)w) & 15) return fail(754, "router_logits: operands must be 16-byte aligned");
-  if (T <= 16)      // decode sizes: stream the gate matrix over the whole device
-    return cuda_fail(launch_router_logits_small(x, w, T, H, E, logits, (cudaStream_t)stream), "router_logits");
-  // tensor-core path: whole gate matrix as one B tile (E <= 256), K in 64-element stages, 16-byte aligned rows
-  if (E <= 256 && H % 64 == 0 && E % 8 == 0)
-    return cuda_fail(launch_router_logits_tc(x, w, T, H, E, logits, nullptr, (cudaStream_t)stream), "router_logits");
-  return cuda_fail(launch_router_logits(x, w, T, H, E, logits, (cudaStream_t)stream), "router_logits");
+  return cuda_fail(router_logits_any(x, w, T, H, E, logits, (cudaStream_t)stream), "router_logits");
 }
 
 int b200moe_gemm_nvfp4(const void* a_q, const void* a_sf, const void* b_q, const void* b_sf, float alpha, void* out, int64_t m,
@@ -473,6 +487,11 @@ int b200moe_create(const b200moe_config* cfg, b200moe_handle* out) {
   h->act_sf = b + p.off_actsf;
   h->rout = (__nv_bfloat16*)(b + p.off_rout);
   h->status = (int32_t*)(b + p.off_status);
+  h->step_hq = b + p.off_step_hq;
+  h->step_hs = b + p.off_step_hs;
+  h->step_logits = (float*)(b + p.off_step_logits);
+  h->step_ids = (int32_t*)(b + p.off_step_ids);
+  h->step_w = (float*)(b + p.off_step_w);
   e = cudaMemset(h->base, 0, (size_t)p.off_aq);   // index tables and status start at zero
   if (e == cudaSuccess) e = cudaMemset(h->status, 0, 16);
   if (e != cudaSuccess) {
@@ -525,6 +544,8 @@ int b200moe_workspace(b200moe_handle h, b200moe_workspace_view* v) {
   v->pair_expert = h->rm.pair_expert;
   v->pair_row0 = h->rm.pair_row0;
   v->pair_rows = h->rm.pair_rows;
+  v->step_ids = h->step_ids;
+  v->step_weights = h->step_w;
   return 0;
 }
 
@@ -700,29 +721,21 @@ int b200moe_run_ep(b200moe_handle h, const b200moe_args* args, const b200moe_ep_
 // stream: same pointers, sizes and strides mean the same launches (routing and data are read from memory by the
 // kernels, tensor maps depend on addresses only). First sighting of a key runs the chain and remembers the key, the
 // second captures the chain on the caller's stream and launches the graph, later ones only launch it.
-static int run_cached(b200moe_layer* h, const b200moe_args* in, cudaStream_t st) {
-  // the key is compared as bytes: copy the fields into a zeroed block so that padding never takes part
-  b200moe_args key;
-  memset(&key, 0, sizeof(key));
-#define B200MOE_COPY(f) key.f = in->f
-  B200MOE_COPY(struct_size); B200MOE_COPY(num_tokens); B200MOE_COPY(topk_ids); B200MOE_COPY(topk_weights); B200MOE_COPY(hidden_states);
-  B200MOE_COPY(hidden_states_scale); B200MOE_COPY(hidden_states_scale_layout); B200MOE_COPY(activation_type); B200MOE_COPY(gemm1_weights);
-  B200MOE_COPY(gemm1_weights_scale); B200MOE_COPY(gemm2_weights); B200MOE_COPY(gemm2_weights_scale); B200MOE_COPY(gemm1_alpha);
-  B200MOE_COPY(gemm1_beta); B200MOE_COPY(gemm1_clamp_limit); B200MOE_COPY(output1_scale_scalar); B200MOE_COPY(output1_scale_gate_scalar);
-  B200MOE_COPY(output2_scale_scalar); B200MOE_COPY(local_expert_offset); B200MOE_COPY(direct_rows); B200MOE_COPY(output);
-  B200MOE_COPY(output_stride); B200MOE_COPY(hidden_states_stride); B200MOE_COPY(hidden_states_scale_stride); B200MOE_COPY(topk_stride);
-#undef B200MOE_COPY
-  const b200moe_args* a = &key;
+}  // extern "C"
+
+template <class Launch>
+static int launch_cached(b200moe_layer* h, const void* key, int key_bytes, cudaStream_t st, Launch launch) {
+  static_assert(sizeof(b200moe_args) <= sizeof(h->cache[0].key) && sizeof(b200moe_step_args) <= sizeof(h->cache[0].key), "key buffer");
   cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
   if (cudaStreamIsCapturing(st, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) {
     cudaGetLastError();
     h->stats.eager_in_capture++;
-    return run_impl(h, a, st, nullptr);          // the caller is capturing: our launches become part of its graph
+    return launch(st);                           // the caller is capturing: our launches become part of its graph
   }
   b200moe_layer::Cached* hit = nullptr;
   b200moe_layer::Cached* victim = &h->cache[0];
   for (auto& c : h->cache) {
-    if (c.last_use && c.stream == st && memcmp(&c.key, a, sizeof(*a)) == 0) hit = &c;
+    if (c.last_use && c.stream == st && c.key_bytes == key_bytes && memcmp(c.key, key, key_bytes) == 0) hit = &c;
     if (c.last_use < victim->last_use) victim = &c;
   }
   ++h->tick;
@@ -736,11 +749,12 @@ static int run_cached(b200moe_layer* h, const b200moe_args* in, cudaStream_t st)
       cudaGraphExecDestroy(victim->exec);
       h->stats.graph_evictions++;
     }
-    victim->key = *a;
+    memcpy(victim->key, key, key_bytes);
+    victim->key_bytes = key_bytes;
     victim->stream = st;
     victim->exec = nullptr;
     victim->last_use = h->tick;
-    return run_impl(h, a, st, nullptr);
+    return launch(st);
   }
   hit->last_use = h->tick;
   // The chain is captured on a stream of the layer's own (nothing ever executes there) and the graph is launched on
@@ -750,26 +764,114 @@ static int run_cached(b200moe_layer* h, const b200moe_args* in, cudaStream_t st)
   if (e == cudaSuccess) e = cudaStreamBeginCapture(h->capture_stream, cudaStreamCaptureModeThreadLocal);
   if (e != cudaSuccess) {
     cudaGetLastError();
-    return run_impl(h, a, st, nullptr);
+    return launch(st);
   }
-  const int rc = run_impl(h, a, h->capture_stream, nullptr);
+  const int rc = launch(h->capture_stream);
   cudaGraph_t graph = nullptr;
   e = cudaStreamEndCapture(h->capture_stream, &graph);
   if (rc || e != cudaSuccess || !graph) {
     if (graph) cudaGraphDestroy(graph);
     cudaGetLastError();
-    return rc ? rc : run_impl(h, a, st, nullptr);
+    return rc ? rc : launch(st);
   }
   cudaGraphExec_t exec = nullptr;
   e = cudaGraphInstantiate(&exec, graph, 0);
   cudaGraphDestroy(graph);
   if (e != cudaSuccess || !exec) {
     cudaGetLastError();
-    return run_impl(h, a, st, nullptr);
+    return launch(st);
   }
   hit->exec = exec;
   h->stats.graph_captures++;
   return cuda_fail((int)cudaGraphLaunch(exec, st), "graph launch");
+}
+
+static int run_cached(b200moe_layer* h, const b200moe_args* in, cudaStream_t st) {
+  // the key is compared as bytes: copy the fields into a zeroed block so that padding never takes part
+  b200moe_args key;
+  memset(&key, 0, sizeof(key));
+#define B200MOE_COPY(f) key.f = in->f
+  B200MOE_COPY(struct_size); B200MOE_COPY(num_tokens); B200MOE_COPY(topk_ids); B200MOE_COPY(topk_weights); B200MOE_COPY(hidden_states);
+  B200MOE_COPY(hidden_states_scale); B200MOE_COPY(hidden_states_scale_layout); B200MOE_COPY(activation_type); B200MOE_COPY(gemm1_weights);
+  B200MOE_COPY(gemm1_weights_scale); B200MOE_COPY(gemm2_weights); B200MOE_COPY(gemm2_weights_scale); B200MOE_COPY(gemm1_alpha);
+  B200MOE_COPY(gemm1_beta); B200MOE_COPY(gemm1_clamp_limit); B200MOE_COPY(output1_scale_scalar); B200MOE_COPY(output1_scale_gate_scalar);
+  B200MOE_COPY(output2_scale_scalar); B200MOE_COPY(local_expert_offset); B200MOE_COPY(direct_rows); B200MOE_COPY(output);
+  B200MOE_COPY(output_stride); B200MOE_COPY(hidden_states_stride); B200MOE_COPY(hidden_states_scale_stride); B200MOE_COPY(topk_stride);
+#undef B200MOE_COPY
+  return launch_cached(h, &key, (int)sizeof(key), st, [&](cudaStream_t s2) { return run_impl(h, &key, s2, nullptr); });
+}
+
+// Whole step from bf16 tokens: quantiser, router logits, top-k / softmax into the layer's own buffers, then the layer.
+static int step_impl(b200moe_layer* h, const b200moe_step_args* a, cudaStream_t st) {
+  const b200moe_config& c = h->cfg;
+  const int T = a->num_tokens;
+  int rc = launch_quantize_nvfp4(a->x, T, c.hidden, a->x_stride, a->activation_global_scale, h->step_hq, h->step_hs,
+                                 B200MOE_SF_ROW_MAJOR, st);
+  if (rc) return cuda_fail(rc, "step: quantise");
+  if (c.top_k > 0) {
+    rc = router_logits_any(a->x, a->gate_weight, T, c.hidden, c.num_experts, h->step_logits, st);
+    if (rc) return cuda_fail(rc, "step: router logits");
+    rc = launch_route_topk(h->step_logits, a->gate_bias, T, c.num_experts, c.top_k, h->step_ids, h->step_w, st);
+    if (rc) return cuda_fail(rc, "step: top-k");
+  }
+  b200moe_args r;
+  memset(&r, 0, sizeof(r));
+  r.struct_size = (int32_t)sizeof(r);
+  r.num_tokens = T;
+  r.topk_ids = h->step_ids;
+  r.topk_weights = h->step_w;
+  r.hidden_states = h->step_hq;
+  r.hidden_states_scale = h->step_hs;
+  r.hidden_states_scale_layout = 2;
+  r.activation_type = a->activation_type;
+  r.gemm1_weights = a->gemm1_weights;
+  r.gemm1_weights_scale = a->gemm1_weights_scale;
+  r.gemm2_weights = a->gemm2_weights;
+  r.gemm2_weights_scale = a->gemm2_weights_scale;
+  r.gemm1_alpha = a->gemm1_alpha;
+  r.gemm1_beta = a->gemm1_beta;
+  r.gemm1_clamp_limit = a->gemm1_clamp_limit;
+  r.output1_scale_scalar = a->output1_scale_scalar;
+  r.output1_scale_gate_scalar = a->output1_scale_gate_scalar;
+  r.output2_scale_scalar = a->output2_scale_scalar;
+  r.output = a->output;
+  r.output_stride = a->output_stride;
+  return run_impl(h, &r, st, nullptr);
+}
+
+extern "C" {
+
+int b200moe_step(b200moe_handle h, const b200moe_step_args* a, void* stream) {
+  if (!h) return fail(720, "step: null handle");
+  if (!a || a->struct_size != (int32_t)sizeof(b200moe_step_args)) return fail(721, "step: bad args struct_size");
+  const b200moe_config& c = h->cfg;
+  if (a->num_tokens < 0 || a->num_tokens > c.max_tokens)
+    return fail(722, "step: num_tokens=%d outside 0..max_tokens=%d", a->num_tokens, c.max_tokens);
+  if (a->num_tokens == 0) return 0;
+  if (!a->x || ((uintptr_t)a->x & 15) || a->x_stride < c.hidden || a->x_stride % 8)
+    return fail(724, "step: x must be 16-byte aligned bf16 rows with x_stride >= hidden and a multiple of 8");
+  if (c.top_k > 0 && (!a->gate_weight || ((uintptr_t)a->gate_weight & 15) || c.top_k > c.num_experts))
+    return fail(723, "step: gate_weight is null or misaligned, or top_k > num_experts");
+  if (!(a->activation_global_scale > 0.f)) return fail(744, "step: activation_global_scale must be positive");
+  if (c.hidden % 64) return fail(711, "step: hidden must be a multiple of 64");
+  if (!a->gemm1_weights || !a->gemm1_weights_scale || !a->gemm2_weights || !a->gemm2_weights_scale) return fail(726, "step: weight pointers are null");
+  if (a->activation_type != 3 && a->activation_type != 10) return fail(727, "step: activation_type=%d, expected 3 or 10", a->activation_type);
+  if (!a->output || ((uintptr_t)a->output & 15) || a->output_stride < c.hidden || a->output_stride % 8)
+    return fail(728, "step: output must be 16-byte aligned with output_stride >= hidden and a multiple of 8");
+  if (((uintptr_t)a->gemm1_weights | (uintptr_t)a->gemm2_weights | (uintptr_t)a->gemm1_weights_scale | (uintptr_t)a->gemm2_weights_scale) & 15)
+    return fail(730, "step: tensors must be 16-byte aligned");
+  h->stats.runs++;
+  if (!c.graph_cache) return step_impl(h, a, (cudaStream_t)stream);
+  b200moe_step_args key;
+  memset(&key, 0, sizeof(key));
+#define B200MOE_COPY(f) key.f = a->f
+  B200MOE_COPY(struct_size); B200MOE_COPY(num_tokens); B200MOE_COPY(x); B200MOE_COPY(x_stride); B200MOE_COPY(gate_weight);
+  B200MOE_COPY(gate_bias); B200MOE_COPY(activation_global_scale); B200MOE_COPY(activation_type); B200MOE_COPY(gemm1_weights);
+  B200MOE_COPY(gemm1_weights_scale); B200MOE_COPY(gemm2_weights); B200MOE_COPY(gemm2_weights_scale); B200MOE_COPY(gemm1_alpha);
+  B200MOE_COPY(gemm1_beta); B200MOE_COPY(gemm1_clamp_limit); B200MOE_COPY(output1_scale_scalar); B200MOE_COPY(output1_scale_gate_scalar);
+  B200MOE_COPY(output2_scale_scalar); B200MOE_COPY(output); B200MOE_COPY(output_stride);
+#undef B200MOE_COPY
+  return launch_cached(h, &key, (int)sizeof(key), (cudaStream_t)stream, [&](cudaStream_t s2) { return step_impl(h, &key, s2); });
 }
 
 int b200moe_run(b200moe_handle h, const b200moe_args* args, void* stream) {

@@ -256,10 +256,14 @@ class ExpertParallelMoE:
         self._routed.run(local_ids, weights, rows_q, rows_sf, w1q[:e], w1s[:e], w2q[:e], w2s[:e], out_rows,
                          **{k: (None if v is None else v[:e]) for k, v in kw.items()})
 
-    def _cuda_shared_rows(self, hq, hs, w1q, w1s, w2q, w2s, out_rows, kw):
+    def _cuda_shared_layer(self):
         from .ops import MoELayer
         if self._shared is None:
             self._shared = MoELayer(self.h, self.i, 0, 0, self.t, num_shared_experts=self.s, sm_margin=self.sm_margin)
+        return self._shared
+
+    def _cuda_shared_rows(self, hq, hs, w1q, w1s, w2q, w2s, out_rows, kw):
+        self._cuda_shared_layer()
         e = self.e_local
         self._shared.run(None, None, hq, hs, w1q[e:], w1s[e:], w2q[e:], w2s[e:], out_rows,
                          **{k: (None if v is None else v[e:]) for k, v in kw.items()})
@@ -375,10 +379,17 @@ class ExpertParallelMoE:
         if t > self.t:
             raise ValueError(f"{t} tokens, the exchange buffers were sized for {self.t} per rank")
         if self._px is None:
-            self._px = PeerExchange(self.h, self.k, self.t, bool(self.s), self.group, dev)
+            # every allocation of the step first, the exchange buffers last: their set-up ends with a barrier, so all ranks
+            # enter their first step together and the bounded flag waits only ever cover the step itself
+            seg_len = (self.t + SEGMENT_ROWS - 1) // SEGMENT_ROWS * SEGMENT_ROWS
             self._plan = CudaPlanner(self.h, self.k, self.e_local, self.world, self.t, bool(self.s), dev, message_buffer=False)
-            self._routed = MoELayer(self.h, self.i, self.e_local, self.k, self._px.slots, sm_margin=self.sm_margin)
+            self._routed = MoELayer(self.h, self.i, self.e_local, self.k, self.world * seg_len, sm_margin=self.sm_margin)
             self._scratch_out = torch.empty((1, self.h), dtype=torch.bfloat16, device=dev)
+            if self.s:
+                self._cuda_shared_layer()
+            torch.cuda.synchronize(dev)
+            self._px = PeerExchange(self.h, self.k, self.t, bool(self.s), self.group, dev)
+            assert self._px.slots == self.world * seg_len
         px, plan, lib = self._px, self._plan, self._px.lib
         px.epoch += 1
         epoch, p = px.epoch, px.epoch & 1

@@ -267,6 +267,40 @@ class MoELayer:
                     0 if ids is None else ids.stride(0))
         return out
 
+    def step(self, x, gate_weight, gate_bias, global_scale, w1, s1, w2, s2, out, *, alpha=None, beta=None, limit=None,
+             scale_up=None, scale_gate=None, scale_out=None, activation_type=3):
+        """The whole step from bf16 tokens in one library call (b200moe_step): quantiser, router logits, top-k / softmax,
+        layer. The argument block is cached per (tensors, sizes): a repeat call only hands its address to the library,
+        which replays its graph when the layer was created with ``graph_cache``."""
+        key = (x.data_ptr(), x.shape[0], x.stride(0), gate_weight.data_ptr(), _ptr(gate_bias), float(global_scale), w1.data_ptr(),
+               s1.data_ptr(), w2.data_ptr(), s2.data_ptr(), _ptr(alpha), _ptr(beta), _ptr(limit), _ptr(scale_up), _ptr(scale_gate),
+               _ptr(scale_out), out.data_ptr(), out.stride(0), activation_type)
+        cached = getattr(self, "_step_cache", None)
+        if cached is None or cached[0] != key:
+            _need_cuda(x, gate_weight, gate_bias, w1, s1, w2, s2, out)
+            if x.dtype != torch.bfloat16 or gate_weight.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+                raise ValueError("x, gate_weight and out must be bfloat16")
+            if x.stride(1) != 1 or not gate_weight.is_contiguous() or out.stride(1) != 1:
+                raise ValueError("x and out need unit inner stride, gate_weight must be contiguous")
+            a = _lib.StepArgs(struct_size=C.sizeof(_lib.StepArgs), num_tokens=x.shape[0], x=x.data_ptr(), x_stride=x.stride(0),
+                              gate_weight=gate_weight.data_ptr(), gate_bias=_ptr(gate_bias), activation_global_scale=float(global_scale),
+                              activation_type=activation_type, gemm1_weights=w1.data_ptr(), gemm1_weights_scale=s1.data_ptr(),
+                              gemm2_weights=w2.data_ptr(), gemm2_weights_scale=s2.data_ptr(), gemm1_alpha=_ptr(alpha),
+                              gemm1_beta=_ptr(beta), gemm1_clamp_limit=_ptr(limit), output1_scale_scalar=_ptr(scale_up),
+                              output1_scale_gate_scalar=_ptr(scale_gate), output2_scale_scalar=_ptr(scale_out), output=out.data_ptr(),
+                              output_stride=out.stride(0))
+            cached = self._step_cache = (key, a)
+        _lib.check(_lib.load().b200moe_step(self._h, C.byref(cached[1]), _stream()), "b200moe_step")
+        return out
+
+    def step_outputs(self, num_tokens: int) -> dict:
+        """Views of what the last `step` left in the workspace: ids int32 [T, K], weights fp32 [T, K] (for accounting)."""
+        v = _lib.WorkspaceView()
+        _lib.check(_lib.load().b200moe_workspace(self._h, C.byref(v)), "b200moe_workspace")
+        k = max(1, self.cfg.top_k)
+        return dict(ids=_from_device_ptr(v.step_ids, 4 * num_tokens * k, torch.int32, (num_tokens, k), self.device),
+                    weights=_from_device_ptr(v.step_weights, 4 * num_tokens * k, torch.float32, (num_tokens, k), self.device))
+
     def run_ep(self, peers, ctrl_ptr: int, seg_len: int, ids, weights, hidden_states, hidden_states_scale, w1, s1, w2, s2, scratch_out,
                **kw):
         """The layer over the token slots of an expert-parallel receive buffer (b200moe_run_ep): `peers` is a

@@ -35,7 +35,8 @@ def test_struct_sizes_match_header(lib):
     from kernelschema_b200 import _lib
     assert C.sizeof(_lib.Config) == 16 * 4
     assert C.sizeof(_lib.Args) == 8 + 8 * 4 + 8 + 8 * 10 + 8 + 16 + 24
-    assert C.sizeof(_lib.WorkspaceView) == 14 * 8 + 16 + 24
+    assert C.sizeof(_lib.WorkspaceView) == 14 * 8 + 16 + 24 + 16
+    assert C.sizeof(_lib.StepArgs) == 8 + 8 * 4 + 8 + 8 * 10 + 16
     assert C.sizeof(_lib.EpPeers) == 8 + 3 * 16 * 8
     assert C.sizeof(_lib.Stats) == 6 * 8
 
@@ -69,6 +70,7 @@ def test_argument_checks_precede_launches(lib):
     assert lib.b200moe_ep_shared_open(None, None) == 797
     assert lib.b200moe_ep_shared_close(None) == 0 and lib.b200moe_ep_shared_free(None) == 0
     assert lib.b200moe_get_stats(None, None) == 719
+    assert lib.b200moe_step(None, None, None) == 720
     from kernelschema_b200 import _lib
     bad = _lib.EpPeers(world=99, rank=0)
     assert lib.b200moe_ep_post(C.byref(bad), _lib.EP_FLAG_RETURN, 1, None) == 796 and b"world" in lib.b200moe_last_error()

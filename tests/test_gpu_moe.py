@@ -281,3 +281,48 @@ def test_library_graph_cache_and_hot_call():
     assert layer.stats()["graph_replays"] >= 2
     eager.close()
     cached.close()
+
+
+@pytest.mark.parametrize("t,graph", [(200, False), (200, True), (1, True), (16, True)])
+def test_whole_step_entry_equals_separate_calls(t, graph):
+    """b200moe_step (bf16 tokens -> quantiser -> router logits -> top-k -> layer in one library call) against the same
+    kernels called one by one; with the graph cache the second call captures and the later ones replay."""
+    import kernelschema_b200 as ks
+    from gpu_util import to_dev
+    h, i, e, k, s = 512, 256, 16, 4, 1
+    p = make_moe_case(31, t, h, i, e, k, shared=s, global_scales=True)
+    gen = torch.Generator(device="cuda").manual_seed(5)
+    x = torch.randn((t, h), device="cuda", generator=gen).to(torch.bfloat16)
+    gate = (torch.randn((e, h), device="cuda", generator=gen) * 0.05).to(torch.bfloat16)
+    bias = torch.randn(e, device="cuda", generator=gen) * 0.1
+    gs = 0.0021
+    w = dict(w1=to_dev(p["gemm1_weights"]), s1=to_dev(p["gemm1_weights_scale"]), w2=to_dev(p["gemm2_weights"]),
+             s2=to_dev(p["gemm2_weights_scale"]))
+    kw = dict(scale_up=to_dev(p["output1_scale_scalar"]), scale_gate=to_dev(p["output1_scale_gate_scalar"]),
+              scale_out=to_dev(p["output2_scale_scalar"]))
+    ref_layer = ks.MoELayer(h, i, e, k, t, num_shared_experts=s)
+    hq, hs = ks.nvfp4_quantize(x, gs)
+    ids, wt = ks.route_topk(ks.router_logits(x, gate), k, bias)
+    want = torch.empty((t, h), dtype=torch.bfloat16, device="cuda")
+    ref_layer.run(ids, wt, hq, hs.view(torch.uint8), w["w1"], w["s1"], w["w2"], w["s2"], want, **kw)
+    layer = ks.MoELayer(h, i, e, k, t, num_shared_experts=s, graph_cache=graph)
+    out = torch.empty_like(want)
+    for _ in range(4):
+        out.fill_(-5)
+        layer.step(x, gate, bias, gs, w["w1"], w["s1"], w["w2"], w["s2"], out, **kw)
+        torch.cuda.synchronize()
+        assert torch.equal(out, want)
+    got = layer.step_outputs(t)
+    assert torch.equal(got["ids"], ids) and torch.equal(got["weights"], wt)
+    st = layer.stats()
+    assert st["runs"] == 4 and st["graph_replays"] == (2 if graph else 0) and st["graph_captures"] == (1 if graph else 0), st
+    # new tokens in the same buffer: the replayed chain re-quantises and re-routes them
+    x.copy_(torch.randn((t, h), device="cuda", generator=gen).to(torch.bfloat16))
+    hq, hs = ks.nvfp4_quantize(x, gs)
+    ids, wt = ks.route_topk(ks.router_logits(x, gate), k, bias)
+    ref_layer.run(ids, wt, hq, hs.view(torch.uint8), w["w1"], w["s1"], w["w2"], w["s2"], want, **kw)
+    layer.step(x, gate, bias, gs, w["w1"], w["s1"], w["w2"], w["s2"], out, **kw)
+    torch.cuda.synchronize()
+    assert torch.equal(out, want) and layer.status() == 0
+    ref_layer.close()
+    layer.close()
