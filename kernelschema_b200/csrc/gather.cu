@@ -46,6 +46,19 @@ __global__ void __launch_bounds__(256) k_gather_rows(const uint8_t* __restrict__
   }
 }
 
+// One payload row by one warp, eight 16-byte vectors per lane in flight (all loads of a batch before its stores).
+DEV void copy_row_batched(const uint4* __restrict__ src, uint4* __restrict__ dst, int vecs, int lane) {
+  for (int v0 = lane; v0 < vecs; v0 += 32 * 8) {
+    uint4 t[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      if (v0 + 32 * i < vecs) t[i] = __ldg(src + v0 + 32 * i);
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      if (v0 + 32 * i < vecs) dst[v0 + 32 * i] = t[i];
+  }
+}
+
 // Tile form of the permute for row-major token scales: one block per 128-row tile of the permuted buffer. The tile's
 // scale image ([H/64] chunks of 512 bytes, the layout tcgen05.cp consumes) is assembled in shared memory - thread r
 // walks the scale bytes of row r's token with 16-byte loads - and leaves with full 16-byte coalesced stores; written
@@ -75,23 +88,29 @@ __global__ void __launch_bounds__(256) k_gather_tiles(const uint8_t* __restrict_
       uint32_t* dst = s_img + (r & 31) * 4 + (r >> 5);          // word (row, chunk j) lives at j * 128 + (r % 32) * 4 + r / 32
       if (tok >= 0) {
         const uint4* src = reinterpret_cast<const uint4*>(hid_sf + (size_t)tok * sf_stride);
-        for (int j4 = 0; j4 < (chunks >> 2); ++j4) {
-          const uint4 v = __ldg(src + j4);
-          dst[(4 * j4 + 0) * 128] = v.x;
-          dst[(4 * j4 + 1) * 128] = v.y;
-          dst[(4 * j4 + 2) * 128] = v.z;
-          dst[(4 * j4 + 3) * 128] = v.w;
+        for (int j0 = 0; j0 < (chunks >> 2); j0 += 8) {          // eight 16-byte loads in flight, then their 32 words
+          uint4 v[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            if (j0 + i < (chunks >> 2)) v[i] = __ldg(src + j0 + i);
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            if (j0 + i < (chunks >> 2)) {
+              const int j4 = j0 + i;
+              dst[(4 * j4 + 0) * 128] = v[i].x;
+              dst[(4 * j4 + 1) * 128] = v[i].y;
+              dst[(4 * j4 + 2) * 128] = v[i].z;
+              dst[(4 * j4 + 3) * 128] = v[i].w;
+            }
         }
       } else {
         for (int j = 0; j < chunks; ++j) dst[j * 128] = 0u;
       }
     } else {
       // the other four warps start on the payload meanwhile: rows 0, 4, 8, ... of the tile (the rest follows below)
-      for (int r = warp - 4; r < rows; r += 8) {
-        const uint4* src = reinterpret_cast<const uint4*>(hid_q + (size_t)s_tok[r] * q_stride);
-        uint4* dst = reinterpret_cast<uint4*>(a_q + (size_t)(row0 + r) * (H >> 1));
-        for (int v = lane; v < vec_per_row; v += 32) dst[v] = __ldg(src + v);
-      }
+      for (int r = warp - 4; r < rows; r += 8)
+        copy_row_batched(reinterpret_cast<const uint4*>(hid_q + (size_t)s_tok[r] * q_stride),
+                         reinterpret_cast<uint4*>(a_q + (size_t)(row0 + r) * (H >> 1)), vec_per_row, lane);
     }
     __syncthreads();
     {
@@ -100,11 +119,9 @@ __global__ void __launch_bounds__(256) k_gather_tiles(const uint8_t* __restrict_
     }
     // payload rows 4..7 (mod 8) by warps 0..3, the other half by warps 4..7 above; two rows in flight per warp
     if (warp < 4) {
-      for (int r = warp + 4; r < rows; r += 8) {
-        const uint4* src = reinterpret_cast<const uint4*>(hid_q + (size_t)s_tok[r] * q_stride);
-        uint4* dst = reinterpret_cast<uint4*>(a_q + (size_t)(row0 + r) * (H >> 1));
-        for (int v = lane; v < vec_per_row; v += 32) dst[v] = __ldg(src + v);
-      }
+      for (int r = warp + 4; r < rows; r += 8)
+        copy_row_batched(reinterpret_cast<const uint4*>(hid_q + (size_t)s_tok[r] * q_stride),
+                         reinterpret_cast<uint4*>(a_q + (size_t)(row0 + r) * (H >> 1)), vec_per_row, lane);
     }
     __syncthreads();                                  // s_tok and the image are reused by the next tile
   }

@@ -127,23 +127,45 @@ __global__ void __launch_bounds__(1024) k_route_scan(int etot, int nblk, int32_t
   pdl_trigger();
   pdl_wait();
   if (threadIdx.x < 4) carry[threadIdx.x] = 0;
-  // Exclusive prefix over the blocks, one WARP per expert: lanes take blocks lane, lane + 32, ... (all loads of a round in
-  // flight at once), a shuffle scan orders them; the fixed order keeps every output reproducible.
-  for (int e = warp; e < etot; e += (int)(blockDim.x >> 5)) {
-    int run = 0;
-    for (int b0 = 0; b0 < nblk; b0 += 32) {
-      const int b = b0 + lane;
-      const int v = b < nblk ? block_hist[(int64_t)b * etot + e] : 0;
-      int inc = v;
+  // Exclusive prefix over the blocks, per expert, in a fixed order (reproducible). Two forms, by the number of dependent
+  // load rounds: one THREAD per expert with eight loads in flight (ceil(nblk / 8) rounds: many experts, few blocks), or one
+  // WARP per expert, lanes on blocks lane, lane + 32, ... and a shuffle scan (ceil(etot / 32) * ceil(nblk / 32) rounds: the
+  // receive buffer of an expert-parallel rank, few experts and hundreds of blocks).
+  const int rounds_thread = ((nblk + 7) >> 3) * ((etot + (int)blockDim.x - 1) / (int)blockDim.x);
+  const int rounds_warp = ((etot + 31) >> 5) * ((nblk + 31) >> 5);
+  if (rounds_thread <= rounds_warp) {
+    for (int e = threadIdx.x; e < etot; e += blockDim.x) {
+      int cnt = 0;
+      for (int b0 = 0; b0 < nblk; b0 += 8) {
+        int v[8];
 #pragma unroll
-      for (int off = 1; off < 32; off <<= 1) {
-        const int a = __shfl_up_sync(0xFFFFFFFFu, inc, off);
-        if (lane >= off) inc += a;
+        for (int j = 0; j < 8; ++j) v[j] = (b0 + j < nblk) ? block_hist[(int64_t)(b0 + j) * etot + e] : 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (b0 + j < nblk) {
+            block_hist[(int64_t)(b0 + j) * etot + e] = cnt;
+            cnt += v[j];
+          }
       }
-      if (b < nblk) block_hist[(int64_t)b * etot + e] = run + inc - v;
-      run += __shfl_sync(0xFFFFFFFFu, inc, 31);
+      counts[e] = cnt;
     }
-    if (lane == 0) counts[e] = run;
+  } else {
+    for (int e = warp; e < etot; e += (int)(blockDim.x >> 5)) {
+      int run = 0;
+      for (int b0 = 0; b0 < nblk; b0 += 32) {
+        const int b = b0 + lane;
+        const int v = b < nblk ? block_hist[(int64_t)b * etot + e] : 0;
+        int inc = v;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+          const int a = __shfl_up_sync(0xFFFFFFFFu, inc, off);
+          if (lane >= off) inc += a;
+        }
+        if (b < nblk) block_hist[(int64_t)b * etot + e] = run + inc - v;
+        run += __shfl_sync(0xFFFFFFFFu, inc, 31);
+      }
+      if (lane == 0) counts[e] = run;
+    }
   }
   __syncthreads();
   for (int e0 = 0; e0 < etot; e0 += blockDim.x) {
