@@ -203,17 +203,28 @@ int run_impl(b200moe_layer* h, const b200moe_args* a, cudaStream_t st, cudaEvent
   int rc;
   auto mark = [&](int i) { if (ev) cudaEventRecord(ev[i], st); };
   mark(0);
-  rc = launch_route_map(a->topk_ids, a->topk_weights, a->topk_stride, T, c.top_k, c.num_shared_experts, c.num_experts,
-                        a->local_expert_offset, h->rm, st, ep ? ep->seg_len : 0, ep ? ep->ctrl + kEpCount : nullptr);
-  if (rc) return cuda_fail(rc, "route map");
-  mark(1);
-  // rows this call can occupy at most (every routing of T tokens fits), not the layer's capacity: sizes the permute grid
-  int64_t call_rows = ((int64_t)T * h->kk / 128 + h->etot + 1) * 128;
-  if (call_rows > h->row_capacity) call_rows = h->row_capacity;
-  rc = launch_gather_rows(a->hidden_states, a->hidden_states_scale, a->hidden_states_scale_layout == 1, a->hidden_states_stride,
-                          a->hidden_states_scale_stride, h->rm.tok_of_row, h->rm.tile_rows, h->rm.totals, c.hidden, call_rows, h->a_q, h->a_sf, st);
-  if (rc) return cuda_fail(rc, "permute");
-  mark(2);
+  if (a->hidden_states_scale_layout == 2 && route_gather_fits(T, c.top_k, c.num_shared_experts, c.num_experts, c.hidden)) {
+    // decode-sized batch: the route map and the permute are one launch
+    rc = launch_route_gather(a->topk_ids, a->topk_weights, a->topk_stride, T, c.top_k, c.num_shared_experts, c.num_experts,
+                             a->local_expert_offset, h->rm, a->hidden_states, a->hidden_states_scale, a->hidden_states_stride,
+                             a->hidden_states_scale_stride, c.hidden, h->a_q, h->a_sf, st, ep ? ep->seg_len : 0,
+                             ep ? ep->ctrl + kEpCount : nullptr);
+    if (rc) return cuda_fail(rc, "route map + permute");
+    mark(1);
+    mark(2);
+  } else {
+    rc = launch_route_map(a->topk_ids, a->topk_weights, a->topk_stride, T, c.top_k, c.num_shared_experts, c.num_experts,
+                          a->local_expert_offset, h->rm, st, ep ? ep->seg_len : 0, ep ? ep->ctrl + kEpCount : nullptr);
+    if (rc) return cuda_fail(rc, "route map");
+    mark(1);
+    // rows this call can occupy at most (every routing of T tokens fits), not the layer's capacity: sizes the permute grid
+    int64_t call_rows = ((int64_t)T * h->kk / 128 + h->etot + 1) * 128;
+    if (call_rows > h->row_capacity) call_rows = h->row_capacity;
+    rc = launch_gather_rows(a->hidden_states, a->hidden_states_scale, a->hidden_states_scale_layout == 1, a->hidden_states_stride,
+                            a->hidden_states_scale_stride, h->rm.tok_of_row, h->rm.tile_rows, h->rm.totals, c.hidden, call_rows, h->a_q, h->a_sf, st);
+    if (rc) return cuda_fail(rc, "permute");
+    mark(2);
+  }
   if (h->b1_ptr != a->gemm1_weights || h->s1_ptr != a->gemm1_weights_scale) {
     rc = make_operand_map(&h->tm_b1, a->gemm1_weights, (uint64_t)h->etot * 2 * c.intermediate, c.hidden / 2, h->bn == 512 ? 128 : h->bn);
     if (!rc) rc = make_operand_map(&h->tm_b1_narrow, a->gemm1_weights, (uint64_t)h->etot * 2 * c.intermediate, c.hidden / 2, 128);

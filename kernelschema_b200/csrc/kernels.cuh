@@ -110,6 +110,12 @@ int launch_router_logits_small(const void* x, const void* w, int64_t T, int H, i
 // slots of each region hold a token (the receive buffer of the expert-parallel exchange); the rest count as unrouted.
 int launch_route_map(const int32_t* ids, const float* scores, int64_t id_stride, int64_t T, int K, int S, int E, int expert_offset,
                      RouteMapBuffers b, cudaStream_t st, int seg_len = 0, const int32_t* seg_valid = nullptr);
+// Route map and permute in ONE launch for batches of at most 4096 routes with row-major token scales (decode sizes):
+// `route_gather_fits` says whether a call qualifies.
+bool route_gather_fits(int64_t T, int K, int S, int E, int H);
+int launch_route_gather(const int32_t* ids, const float* scores, int64_t id_stride, int64_t T, int K, int S, int E, int expert_offset,
+                        RouteMapBuffers b, const void* hid_q, const void* hid_sf, int64_t q_stride, int64_t sf_stride, int H, void* a_q,
+                        void* a_sf, cudaStream_t st, int seg_len = 0, const int32_t* seg_valid = nullptr);
 int launch_route_map_static(const int32_t* ids, const float* scores, int64_t T, int K, int S, int E, int expert_offset,
                             RouteMapBuffers b, cudaStream_t st);
 int launch_ep_visits(const int32_t* ids, int64_t T, int K, int experts_per_rank, int world, int32_t* rank_slots, cudaStream_t st);

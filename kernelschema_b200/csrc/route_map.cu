@@ -82,13 +82,14 @@ DEV int route_expert32(const RouteView& r, int f, int total) {
 }
 
 // Per-warp histograms of this block's chunk into hist[warp][e]; each warp owns its row, so no atomics.
-DEV void chunk_histogram(const int (&e)[kRouteSteps], int etot, int* hist) {
+template <int STEPS>
+DEV void chunk_histogram(const int (&e)[STEPS], int etot, int* hist) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int bits = expert_bits(etot);
   for (int i = threadIdx.x; i < (int)(blockDim.x >> 5) * etot; i += blockDim.x) hist[i] = 0;
   __syncthreads();
 #pragma unroll
-  for (int step = 0; step < kRouteSteps; ++step) {
+  for (int step = 0; step < STEPS; ++step) {
     if (!__any_sync(0xFFFFFFFFu, e[step] >= 0)) continue;      // a step without a route (decode sizes: most of them)
     const unsigned m = same_expert_lanes(e[step], bits);
     if (e[step] >= 0 && lane == (__ffs(m) - 1)) hist[warp * etot + e[step]] += __popc(m);
@@ -289,47 +290,58 @@ __global__ void __launch_bounds__(256) k_route_scatter(RouteView r, const float*
 // the segment). The counts of foreign chunks are accumulated with shared-memory atomics; a count does not depend on the
 // order of the additions, so every output stays reproducible. Block 0 also writes the per-expert tables.
 constexpr int kFusedMaxBlocks = 8;
+constexpr int kGatherMaxRoutes = 4096;           // the fused form that also permutes the rows: 16 routes per lane of ONE chunk
 
-__global__ void __launch_bounds__(256) k_route_fused(RouteView r, const float* __restrict__ scores, int etot, RouteMapBuffers b) {
-  extern __shared__ int hist[];                    // own chunk [kRouteWarps][etot] | all chunks [etot] | chunks before [etot]
-  __shared__ int warp_pad[8], warp_tiles[8], warp_pairs[8], warp_cnt[8];
-  __shared__ int carry[4];
-  int* others = hist + kRouteWarps * etot;         // routes of expert e in the other chunks
-  int* before = others + etot;                     // ... in the chunks before this block's
-  const int kk = r.K + r.S;
-  const int total = (int)(r.T * kk);
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const bool writer = blockIdx.x == 0;
-  pdl_trigger();
-  pdl_wait();
-  for (int i = threadIdx.x; i < 2 * etot; i += blockDim.x) others[i] = 0;
-  __syncthreads();
-  int ex[kRouteSteps];
-  float wt[kRouteSteps];                           // routing weight of each own route: fetched with the ids, before any store
+// The permute of one routed row from inside the route-map kernel (small batches): payload with 16-byte vectors, the row's
+// scale words straight into the 128x4-tiled image. Scales of padding rows are left as they are: the GEMMs neither store
+// nor read across rows, so whatever a padding row computes is dropped.
+struct GatherView {
+  const uint8_t* hid_q;
+  const uint8_t* hid_sf;      // row-major [T, H/16]
+  int64_t q_stride, sf_stride;
+  int H;
+  uint8_t* a_q;
+  uint8_t* a_sf;
+};
+
+DEV void gather_row(const GatherView& g, int tok, int pos, int lane) {
+  const int vecs = g.H >> 5, words = g.H >> 6;
+  const uint4* src = reinterpret_cast<const uint4*>(g.hid_q + (size_t)tok * g.q_stride);
+  uint4* dst = reinterpret_cast<uint4*>(g.a_q + (size_t)pos * (g.H >> 1));
+  const uint32_t* sf_src = reinterpret_cast<const uint32_t*>(g.hid_sf + (size_t)tok * g.sf_stride);
+  uint32_t* sf_dst = reinterpret_cast<uint32_t*>(g.a_sf + (size_t)(pos >> 7) * words * 512 + (size_t)(pos & 31) * 16 +
+                                                 (size_t)((pos >> 5) & 3) * 4);
+  for (int v0 = lane; v0 < vecs; v0 += 32 * 8) {
+    uint4 t[8];
 #pragma unroll
-  for (int step = 0; step < kRouteSteps; ++step) {
-    const int f = (int)blockIdx.x * kRouteChunk + warp * kRoutesPerWarp + step * 32 + lane;
-    ex[step] = route_expert32(r, f, total);
-    wt[step] = 1.0f;
-    if (scores && ex[step] >= 0 && ex[step] < r.E) {
-      const int t = f / kk;
-      wt[step] = scores[(int64_t)t * r.id_stride + (f - t * kk)];
+    for (int i = 0; i < 8; ++i)
+      if (v0 + 32 * i < vecs) t[i] = __ldg(src + v0 + 32 * i);
+    uint32_t sw[4];
+    if (v0 == lane) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        if (lane + 32 * i < words) sw[i] = __ldg(sf_src + lane + 32 * i);
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      if (v0 + 32 * i < vecs) dst[v0 + 32 * i] = t[i];
+    if (v0 == lane) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        if (lane + 32 * i < words) sf_dst[(size_t)(lane + 32 * i) * 128] = sw[i];
     }
   }
-  for (int c = 0; c < (int)gridDim.x; ++c) {
-    if (c == (int)blockIdx.x) continue;
-    int eo[kRouteSteps];
-#pragma unroll
-    for (int step = 0; step < kRouteSteps; ++step)
-      eo[step] = route_expert32(r, c * kRouteChunk + warp * kRoutesPerWarp + step * 32 + lane, total);
-#pragma unroll
-    for (int step = 0; step < kRouteSteps; ++step)
-      if (eo[step] >= 0) {
-        atomicAdd(&others[eo[step]], 1);
-        if (c < (int)blockIdx.x) atomicAdd(&before[eo[step]], 1);
-      }
-  }
-  chunk_histogram(ex, etot, hist);                 // own chunk, per warp; its barriers also publish others/before
+  for (int w = lane + 128; w < words; w += 32) sf_dst[(size_t)w * 128] = __ldg(sf_src + w);     // H > 8192
+}
+
+// Block-wide scan over the experts, shared by the one-launch kernels. In: hist[w][e] = routes of expert e that warp w of
+// this block owns, others[e] = routes of e owned by other blocks, before[e] = those of them that precede this block's.
+// Out: segment starts, tile and pair tables and totals (stored by the `writer` block only), and hist[w][e] turned into
+// the permuted row of warp w's first route of expert e. Ends with a block barrier.
+DEV void scan_experts(int etot, const int* others, const int* before, int* hist, bool writer, const RouteMapBuffers& b) {
+  __shared__ int warp_pad[8], warp_tiles[8], warp_pairs[8], warp_cnt[8];
+  __shared__ int carry[4];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   if (threadIdx.x < 4) carry[threadIdx.x] = 0;
   __syncthreads();
   for (int e0 = 0; e0 < etot; e0 += blockDim.x) {
@@ -395,6 +407,52 @@ __global__ void __launch_bounds__(256) k_route_fused(RouteView r, const float* _
     b.totals[2] = carry[2];
     b.totals[3] = carry[3];
   }
+}
+
+// A chunk's routes are dealt to the 8 warps in runs of `rpw` (a multiple of 32, just enough for the chunk), so that a
+// small chunk occupies every warp with one step instead of one warp with eight; positions stay in ascending route order.
+DEV int routes_per_warp(int chunk_total) { return max(32, (((chunk_total + kRouteWarps - 1) / kRouteWarps) + 31) & ~31); }
+
+__global__ void __launch_bounds__(256) k_route_fused(RouteView r, const float* __restrict__ scores, int etot, RouteMapBuffers b) {
+  extern __shared__ int hist[];                    // own chunk [kRouteWarps][etot] | all chunks [etot] | chunks before [etot]
+  int* others = hist + kRouteWarps * etot;         // routes of expert e in the other chunks
+  int* before = others + etot;                     // ... in the chunks before this block's
+  const int kk = r.K + r.S;
+  const int total = (int)(r.T * kk);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const bool writer = blockIdx.x == 0;
+  const int rpw = routes_per_warp(min(kRouteChunk, total - (int)blockIdx.x * kRouteChunk));
+  pdl_trigger();
+  pdl_wait();
+  for (int i = threadIdx.x; i < 2 * etot; i += blockDim.x) others[i] = 0;
+  __syncthreads();
+  int ex[kRouteSteps];
+  float wt[kRouteSteps];                           // routing weight of each own route: fetched with the ids, before any store
+#pragma unroll
+  for (int step = 0; step < kRouteSteps; ++step) {
+    const int f = (int)blockIdx.x * kRouteChunk + warp * rpw + step * 32 + lane;
+    ex[step] = step * 32 < rpw ? route_expert32(r, f, total) : -1;
+    wt[step] = 1.0f;
+    if (scores && ex[step] >= 0 && ex[step] < r.E) {
+      const int t = f / kk;
+      wt[step] = scores[(int64_t)t * r.id_stride + (f - t * kk)];
+    }
+  }
+  for (int c = 0; c < (int)gridDim.x; ++c) {
+    if (c == (int)blockIdx.x) continue;
+    int eo[kRouteSteps];
+#pragma unroll
+    for (int step = 0; step < kRouteSteps; ++step)
+      eo[step] = route_expert32(r, c * kRouteChunk + warp * kRoutesPerWarp + step * 32 + lane, total);
+#pragma unroll
+    for (int step = 0; step < kRouteSteps; ++step)
+      if (eo[step] >= 0) {
+        atomicAdd(&others[eo[step]], 1);
+        if (c < (int)blockIdx.x) atomicAdd(&before[eo[step]], 1);
+      }
+  }
+  chunk_histogram(ex, etot, hist);                 // own chunk, per warp; its barriers also publish others/before
+  scan_experts(etot, others, before, hist, writer, b);
   int pos[kRouteSteps];
 #pragma unroll
   for (int step = 0; step < kRouteSteps; ++step) {
@@ -409,14 +467,81 @@ __global__ void __launch_bounds__(256) k_route_fused(RouteView r, const float* _
   }
 #pragma unroll
   for (int step = 0; step < kRouteSteps; ++step) {
-    const int f = (int)blockIdx.x * kRouteChunk + warp * kRoutesPerWarp + step * 32 + lane;
-    if (f < total) {
+    const int f = (int)blockIdx.x * kRouteChunk + warp * rpw + step * 32 + lane;
+    if (step * 32 < rpw && f < total) {
       b.row_of[f] = pos[step];
       if (pos[step] >= 0) {
         b.tok_of_row[pos[step]] = f / kk;
         b.weight_of_row[pos[step]] = wt[step];
       }
     }
+  }
+}
+
+// Route map AND permute of a decode-sized batch (at most kGatherMaxRoutes routes) in one launch: every block builds the
+// whole map for itself in shared memory (a few thousand integer operations), block 0 stores it, and the blocks share the
+// row copies, one warp per routed row. The step loops are rolled: a one-wave, latency-bound kernel pays for every
+// instruction-cache line it touches, and a decode batch takes one step.
+__global__ void __launch_bounds__(256) k_route_gather(RouteView r, const float* __restrict__ scores, int etot, RouteMapBuffers b,
+                                                      GatherView gv) {
+  extern __shared__ int hist[];                    // [kRouteWarps][etot] | zeros [etot] | zeros [etot] | expert, then row, of every route
+  int* zeros = hist + kRouteWarps * etot;
+  int* s_pos = zeros + 2 * etot;
+  const int kk = r.K + r.S;
+  const int total = (int)(r.T * kk);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const bool writer = blockIdx.x == 0;
+  const int rpw = routes_per_warp(total), nsteps = rpw >> 5;
+  const int bits = expert_bits(etot);
+  pdl_trigger();
+  pdl_wait();
+  for (int i = threadIdx.x; i < (kRouteWarps + 2) * etot; i += blockDim.x) hist[i] = 0;
+#pragma unroll 4
+  for (int step = 0; step < nsteps; ++step) {
+    const int f = warp * rpw + step * 32 + lane;
+    if (f < total) s_pos[f] = route_expert32(r, f, total);
+  }
+  __syncthreads();
+#pragma unroll 1
+  for (int step = 0; step < nsteps; ++step) {
+    const int f = warp * rpw + step * 32 + lane;
+    const int e = f < total ? s_pos[f] : -1;
+    if (!__any_sync(0xFFFFFFFFu, e >= 0)) continue;
+    const unsigned m = same_expert_lanes(e, bits);
+    if (e >= 0 && lane == (__ffs(m) - 1)) hist[warp * etot + e] += __popc(m);
+    __syncwarp();
+  }
+  __syncthreads();
+  scan_experts(etot, zeros, zeros + etot, hist, writer, b);
+#pragma unroll 1
+  for (int step = 0; step < nsteps; ++step) {
+    const int f = warp * rpw + step * 32 + lane;
+    const int e = f < total ? s_pos[f] : -1;
+    int at = -1;
+    if (__any_sync(0xFFFFFFFFu, e >= 0)) {
+      const unsigned m = same_expert_lanes(e, bits);
+      if (e >= 0) at = hist[warp * etot + e] + __popc(m & ((1u << lane) - 1u));
+      __syncwarp();
+      if (e >= 0 && lane == (__ffs(m) - 1)) hist[warp * etot + e] += __popc(m);
+      __syncwarp();
+    }
+    if (f < total) {
+      s_pos[f] = at;
+      if (writer) {
+        b.row_of[f] = at;
+        if (at >= 0) {
+          const int t = f / kk, k = f - t * kk;
+          b.tok_of_row[at] = t;
+          b.weight_of_row[at] = (scores && k < r.K) ? scores[(int64_t)t * r.id_stride + k] : 1.0f;
+        }
+      }
+    }
+  }
+  __syncthreads();
+  const int warps = (int)gridDim.x * kRouteWarps;
+  for (int f = (int)blockIdx.x * kRouteWarps + warp; f < total; f += warps) {
+    const int at = s_pos[f];
+    if (at >= 0) gather_row(gv, f / kk, at, lane);
   }
 }
 
@@ -438,6 +563,26 @@ int launch_route_map(const int32_t* ids, const float* scores, int64_t id_stride,
     err = launch_chain(k_route_scatter, dim3(nblk), dim3(256), smem, st, r, scores, etot, (const int32_t*)b.block_hist,
                        (const int32_t*)b.seg_start, b.row_of, b.tok_of_row, b.weight_of_row);
   return (int)err;
+}
+
+bool route_gather_fits(int64_t T, int K, int S, int E, int H) {
+  const int64_t total = T * (K + S);
+  return total >= 1 && total <= kGatherMaxRoutes && sizeof(int) * ((kRouteWarps + 2) * (size_t)(E + S) + kGatherMaxRoutes) <= 48 * 1024 &&
+         H % 256 == 0;
+}
+
+int launch_route_gather(const int32_t* ids, const float* scores, int64_t id_stride, int64_t T, int K, int S, int E, int expert_offset,
+                        RouteMapBuffers b, const void* hid_q, const void* hid_sf, int64_t q_stride, int64_t sf_stride, int H, void* a_q,
+                        void* a_sf, cudaStream_t st, int seg_len, const int32_t* seg_valid) {
+  const int etot = E + S;
+  const int64_t total = T * (K + S);
+  RouteView r{ids, id_stride > 0 ? id_stride : K, T, K, S, E, expert_offset, seg_valid ? seg_len : 0, seg_valid};
+  GatherView gv{(const uint8_t*)hid_q, (const uint8_t*)hid_sf, q_stride > 0 ? q_stride : (int64_t)(H / 2),
+                sf_stride > 0 ? sf_stride : (int64_t)(H / 16), H, (uint8_t*)a_q, (uint8_t*)a_sf};
+  int64_t blocks = (total + kRouteWarps - 1) / kRouteWarps;     // one row per warp while the SMs last
+  if (blocks > sm_count()) blocks = sm_count();
+  return (int)launch_chain(k_route_gather, dim3((unsigned)blocks), dim3(256),
+                           sizeof(int) * ((kRouteWarps + 2) * (size_t)etot + kGatherMaxRoutes), st, r, scores, etot, b, gv);
 }
 
 // ----------------------------------------------------------------------------- allocation-free variant
