@@ -134,28 +134,8 @@ __global__ void __launch_bounds__(128) k_finalize_ep(const __nv_bfloat16* __rest
     __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(peers.ret[s]) + (size_t)(ctrl[kEpRetBase + s] + i) * H;
     for (int v = blockIdx.y * blockDim.x + threadIdx.x; v < vecs; v += gridDim.y * blockDim.x) {
       float acc[8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-      for (int k = 0; k < KK; ++k) {
-        const int row = row_of[t * KK + k];
-        if (row < 0) continue;
-        const float w = weight_of_row[row];
-        const uint4 raw = __ldg(reinterpret_cast<const uint4*>(rout + (size_t)row * H) + v);
-        const uint32_t* u = reinterpret_cast<const uint32_t*>(&raw);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          acc[2 * j] = fmaf(__uint_as_float(u[j] << 16), w, acc[2 * j]);
-          acc[2 * j + 1] = fmaf(__uint_as_float(u[j] & 0xFFFF0000u), w, acc[2 * j + 1]);
-        }
-      }
-      uint4 o;
-      uint32_t* ou = reinterpret_cast<uint32_t*>(&o);
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const __nv_bfloat162 pr = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
-        ou[j] = *reinterpret_cast<const uint32_t*>(&pr);
-      }
-      *(reinterpret_cast<uint4*>(out) + v) = o;
+      combine_slots(rout, row_of + t * KK, weight_of_row, KK, H, v, acc);
+      *(reinterpret_cast<uint4*>(out) + v) = pack_bf16x8(acc);
     }
   }
 }

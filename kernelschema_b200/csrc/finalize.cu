@@ -17,28 +17,8 @@ __global__ void __launch_bounds__(128) k_finalize(const __nv_bfloat16* __restric
   for (int64_t t = blockIdx.x; t < T; t += gridDim.x) {
     for (int v = blockIdx.y * blockDim.x + threadIdx.x; v < vecs; v += gridDim.y * blockDim.x) {
       float acc[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-      for (int k = 0; k < KK; ++k) {
-        const int row = row_of[t * KK + k];
-        if (row < 0) continue;
-        const float w = weight_of_row[row];
-        const uint4 raw = __ldg(reinterpret_cast<const uint4*>(rout + (size_t)row * H) + v);
-        const uint32_t* u = reinterpret_cast<const uint32_t*>(&raw);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          acc[2 * i] = fmaf(__uint_as_float(u[i] << 16), w, acc[2 * i]);
-          acc[2 * i + 1] = fmaf(__uint_as_float(u[i] & 0xFFFF0000u), w, acc[2 * i + 1]);
-        }
-      }
-      uint4 o;
-      uint32_t* ou = reinterpret_cast<uint32_t*>(&o);
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const __nv_bfloat162 p = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
-        ou[i] = *reinterpret_cast<const uint32_t*>(&p);
-      }
-      *(reinterpret_cast<uint4*>(out + t * out_stride) + v) = o;
+      combine_slots(rout, row_of + t * KK, weight_of_row, KK, H, v, acc);
+      *(reinterpret_cast<uint4*>(out + t * out_stride) + v) = pack_bf16x8(acc);
     }
   }
 }

@@ -240,4 +240,46 @@ DEV float e4m3_to_f32(uint32_t b) {
   return __half2float(__ushort_as_half((unsigned short)(h & 0xFFFF)));
 }
 
+// Routing-weighted sum of one 16-byte vector (8 bf16 columns) over a token's KK slots, fp32, slots in ascending order
+// (slots without a row are skipped). Eight slots at a time: their row indices, then their weights, then their vectors are
+// each fetched as one batch, so a token costs three dependent memory round trips per eight slots instead of two per slot.
+DEV void combine_slots(const __nv_bfloat16* __restrict__ rout, const int32_t* __restrict__ slots, const float* __restrict__ weight_of_row,
+                       int KK, int H, int v, float (&acc)[8]) {
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+  for (int k0 = 0; k0 < KK; k0 += 8) {
+    int row[8];
+    float w[8];
+    uint4 raw[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) row[j] = k0 + j < KK ? slots[k0 + j] : -1;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) w[j] = row[j] >= 0 ? weight_of_row[row[j]] : 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (row[j] >= 0) raw[j] = __ldg(reinterpret_cast<const uint4*>(rout + (size_t)row[j] * H) + v);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (row[j] < 0) continue;
+      const uint32_t* u = reinterpret_cast<const uint32_t*>(&raw[j]);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        acc[2 * i] = fmaf(__uint_as_float(u[i] << 16), w[j], acc[2 * i]);
+        acc[2 * i + 1] = fmaf(__uint_as_float(u[i] & 0xFFFF0000u), w[j], acc[2 * i + 1]);
+      }
+    }
+  }
+}
+
+DEV uint4 pack_bf16x8(const float (&acc)[8]) {
+  uint4 o;
+  uint32_t* ou = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const __nv_bfloat162 p = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+    ou[i] = *reinterpret_cast<const uint32_t*>(&p);
+  }
+  return o;
+}
+
 }  // namespace b200
