@@ -18,7 +18,8 @@ SF_ROW_MAJOR, SF_TILED = 0, 1
 class Config(C.Structure):
     _fields_ = [("struct_size", C.c_int32), ("hidden", C.c_int32), ("intermediate", C.c_int32), ("num_experts", C.c_int32),
                 ("top_k", C.c_int32), ("num_shared_experts", C.c_int32), ("max_tokens", C.c_int32), ("tile_n", C.c_int32),
-                ("sm_margin", C.c_int32), ("graph_cache", C.c_int32), ("reserved", C.c_int32 * 6)]
+                ("sm_margin", C.c_int32), ("graph_cache", C.c_int32), ("tma_gather", C.c_int32),
+                ("reserved", C.c_int32 * 5)]
 
 
 class Args(C.Structure):

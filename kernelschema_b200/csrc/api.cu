@@ -66,6 +66,9 @@ struct b200moe_layer {
   int32_t* status;
   CUtensorMap tm_a1, tm_a2, tm_b1, tm_b2;
   CUtensorMap tm_b1_narrow, tm_b2_narrow;
+  CUtensorMap tm_hid;                                 // the caller's token rows as FC1's A operand (TMA gather), box {128, 1}
+  const void* hid_ptr;
+  int64_t hid_stride;
   uint8_t *step_hq, *step_hs;                         // b200moe_step: quantised tokens,
   float* step_logits;                                 //               router logits,
   int32_t* step_ids;                                  //               selected experts
@@ -113,6 +116,7 @@ int check_cfg(const b200moe_config* c) {
   if (c->tile_n != 0 && c->tile_n != 128 && c->tile_n != 256 && c->tile_n != 512)
     return fail(716, "config: tile_n must be 0, 128, 256 or 512");
   if (c->graph_cache != 0 && c->graph_cache != 1) return fail(709, "config: graph_cache must be 0 or 1");
+  if (c->tma_gather != 0 && c->tma_gather != 1) return fail(707, "config: tma_gather must be 0 or 1");
   return 0;
 }
 
@@ -202,12 +206,16 @@ int run_impl(b200moe_layer* h, const b200moe_args* a, cudaStream_t st, cudaEvent
   if (T == 0) return 0;
   int rc;
   auto mark = [&](int i) { if (ev) cudaEventRecord(ev[i], st); };
+  // cfg.tma_gather: FC1 fetches its A rows from the caller's token matrix by TMA gather and the permute moves only the
+  // scale rows; otherwise (and always for the CTA-pair GEMM) the permute also copies the payload rows.
+  const bool gather_a = c.tma_gather && h->bn != 512;
+  uint8_t* const a_q = gather_a ? nullptr : h->a_q;
   mark(0);
   if (a->hidden_states_scale_layout == 2 && route_gather_fits(T, c.top_k, c.num_shared_experts, c.num_experts, c.hidden)) {
     // decode-sized batch: the route map and the permute are one launch
     rc = launch_route_gather(a->topk_ids, a->topk_weights, a->topk_stride, T, c.top_k, c.num_shared_experts, c.num_experts,
                              a->local_expert_offset, h->rm, a->hidden_states, a->hidden_states_scale, a->hidden_states_stride,
-                             a->hidden_states_scale_stride, c.hidden, h->a_q, h->a_sf, st, ep ? ep->seg_len : 0,
+                             a->hidden_states_scale_stride, c.hidden, a_q, h->a_sf, st, ep ? ep->seg_len : 0,
                              ep ? ep->ctrl + kEpCount : nullptr);
     if (rc) return cuda_fail(rc, "route map + permute");
     mark(1);
@@ -221,9 +229,15 @@ int run_impl(b200moe_layer* h, const b200moe_args* a, cudaStream_t st, cudaEvent
     int64_t call_rows = ((int64_t)T * h->kk / 128 + h->etot + 1) * 128;
     if (call_rows > h->row_capacity) call_rows = h->row_capacity;
     rc = launch_gather_rows(a->hidden_states, a->hidden_states_scale, a->hidden_states_scale_layout == 1, a->hidden_states_stride,
-                            a->hidden_states_scale_stride, h->rm.tok_of_row, h->rm.tile_rows, h->rm.totals, c.hidden, call_rows, h->a_q, h->a_sf, st);
+                            a->hidden_states_scale_stride, h->rm.tok_of_row, h->rm.tile_rows, h->rm.totals, c.hidden, call_rows, a_q, h->a_sf, st);
     if (rc) return cuda_fail(rc, "permute");
     mark(2);
+  }
+  if (gather_a && (h->hid_ptr != a->hidden_states || h->hid_stride != a->hidden_states_stride)) {
+    rc = make_operand_map(&h->tm_hid, a->hidden_states, (uint64_t)c.max_tokens, c.hidden / 2, 1, (uint64_t)a->hidden_states_stride);
+    if (rc) return cuda_fail(rc, "token tensor map");
+    h->hid_ptr = a->hidden_states;
+    h->hid_stride = a->hidden_states_stride;
   }
   if (h->b1_ptr != a->gemm1_weights || h->s1_ptr != a->gemm1_weights_scale) {
     rc = make_operand_map(&h->tm_b1, a->gemm1_weights, (uint64_t)h->etot * 2 * c.intermediate, c.hidden / 2, h->bn == 512 ? 128 : h->bn);
@@ -254,6 +268,7 @@ int run_impl(b200moe_layer* h, const b200moe_args* a, cudaStream_t st, cudaEvent
   g.N = 2 * c.intermediate;
   g.K = c.hidden;
   g.sfa = h->a_sf;
+  g.a_tok = gather_a ? h->rm.tok_of_row : nullptr;
   g.sfb = (const uint8_t*)a->gemm1_weights_scale;
   g.act_q = h->act_q;
   g.act_sf = h->act_sf;
@@ -285,12 +300,13 @@ int run_impl(b200moe_layer* h, const b200moe_args* a, cudaStream_t st, cudaEvent
       rc = launch_gemm_nvfp4_pair(kGemmFc1, h->tm_a1, h->tm_b1, h->tm_sfa1, h->tm_sfb1, gp,
                                   (int)(items < h->n_clusters ? items : h->n_clusters), st);
     } else {
-      rc = launch_gemm_nvfp4(kGemmFc1, bn, h->tm_a1, bn == h->bn ? h->tm_b1 : h->tm_b1_narrow, g, grid, st);
+      rc = launch_gemm_nvfp4(kGemmFc1, bn, gather_a ? h->tm_hid : h->tm_a1, bn == h->bn ? h->tm_b1 : h->tm_b1_narrow, g, grid, st);
     }
     if (rc) return cuda_fail(rc, "FC1");
   }
   mark(3);
   // FC2: [rows, I] x [H, I]^T -> bf16 [rows, H]
+  g.a_tok = nullptr;
   g.N = c.hidden;
   g.K = c.intermediate;
   g.sfa = h->act_sf;

@@ -32,9 +32,11 @@ __global__ void __launch_bounds__(256) k_gather_rows(const uint8_t* __restrict__
       for (int w = lane; w < words_per_row; w += 32) sf_dst[(size_t)w * 128] = 0u;
       continue;
     }
-    const uint4* src = reinterpret_cast<const uint4*>(hid_q + (size_t)tok * q_stride);
-    uint4* dst = reinterpret_cast<uint4*>(a_q + (size_t)r * (H >> 1));
-    for (int v = lane; v < vec_per_row; v += 32) dst[v] = __ldg(src + v);
+    if (a_q) {                           // null: the GEMM gathers the payload rows itself, only the scales are permuted
+      const uint4* src = reinterpret_cast<const uint4*>(hid_q + (size_t)tok * q_stride);
+      uint4* dst = reinterpret_cast<uint4*>(a_q + (size_t)r * (H >> 1));
+      for (int v = lane; v < vec_per_row; v += 32) dst[v] = __ldg(src + v);
+    }
     if (hid_sf_tiled) {
       const uint32_t* sf_src = reinterpret_cast<const uint32_t*>(hid_sf + (size_t)(tok >> 7) * words_per_row * 512 +
                                                                  (size_t)(tok & 31) * 16 + (size_t)((tok >> 5) & 3) * 4);
@@ -64,6 +66,7 @@ DEV void copy_row_batched(const uint4* __restrict__ src, uint4* __restrict__ dst
 // walks the scale bytes of row r's token with 16-byte loads - and leaves with full 16-byte coalesced stores; written
 // word by word from the rows it would cost one 32-byte sector per 4 bytes. Payload rows are copied by the warps, two rows
 // in flight per warp. Padding rows (past the tile's count) get zero scales and keep whatever payload they had.
+// a_q == null: scales only (the GEMM fetches the payload rows of the tokens itself).
 __global__ void __launch_bounds__(256) k_gather_tiles(const uint8_t* __restrict__ hid_q, const uint8_t* __restrict__ hid_sf,
                                                       int64_t q_stride, int64_t sf_stride, const int32_t* __restrict__ tok_of_row,
                                                       const int32_t* __restrict__ tile_rows, const int32_t* __restrict__ totals, int H,
@@ -106,7 +109,7 @@ __global__ void __launch_bounds__(256) k_gather_tiles(const uint8_t* __restrict_
       } else {
         for (int j = 0; j < chunks; ++j) dst[j * 128] = 0u;
       }
-    } else {
+    } else if (a_q) {
       // the other four warps start on the payload meanwhile: rows 0, 4, 8, ... of the tile (the rest follows below)
       for (int r = warp - 4; r < rows; r += 8)
         copy_row_batched(reinterpret_cast<const uint4*>(hid_q + (size_t)s_tok[r] * q_stride),
@@ -118,7 +121,7 @@ __global__ void __launch_bounds__(256) k_gather_tiles(const uint8_t* __restrict_
       for (int i = threadIdx.x; i < chunks * 32; i += blockDim.x) out[i] = s_img4[i];
     }
     // payload rows 4..7 (mod 8) by warps 0..3, the other half by warps 4..7 above; two rows in flight per warp
-    if (warp < 4) {
+    if (warp < 4 && a_q) {
       for (int r = warp + 4; r < rows; r += 8)
         copy_row_batched(reinterpret_cast<const uint4*>(hid_q + (size_t)s_tok[r] * q_stride),
                          reinterpret_cast<uint4*>(a_q + (size_t)(row0 + r) * (H >> 1)), vec_per_row, lane);

@@ -285,7 +285,59 @@ k_gemm_nvfp4(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
-    if (lane == 0) {
+    if (MODE == kGemmFc1 && p.a_tok) {
+      // A rows straight from the token matrix: lane l owns rows 4l .. 4l+3 of the tile and fetches them with one
+      // tile::gather4 per stage (four token rows x 128 bytes into 512 bytes of the swizzled A slot). Only the boxes that
+      // hold a valid row are issued (rows past the tile's count keep whatever the slot held: their results are never
+      // stored), and the stage's expected byte count follows the box count.
+      uint32_t s = 0, ph = 1;
+      bool ok = true;
+      int mt_n = 0, e_n = 0, row0_n = 0, rows_n = 0;
+      int4 tok_n = make_int4(0, 0, 0, 0);
+      auto fetch = [&](long long item) {
+        mt_n = (int)(item / n_ntiles);
+        e_n = p.tile_expert[mt_n];
+        row0_n = p.tile_row0[mt_n];
+        rows_n = p.tile_rows[mt_n];
+        tok_n = *reinterpret_cast<const int4*>(p.a_tok + row0_n + 4 * lane);
+      };
+      if (blockIdx.x < total_items) fetch(blockIdx.x);
+      for (long long item = blockIdx.x; ok && item < total_items; item += gridDim.x) {
+        const int nt = (int)(item - (long long)mt_n * n_ntiles);
+        const int e = e_n, row0 = row0_n, rows = rows_n;
+        int4 tok = tok_n;
+        if (item + gridDim.x < total_items) fetch(item + gridDim.x);
+        const int nbox = max(1, min(kBM / 4, (rows + 3) >> 2));
+        // rows of a box past the tile's count repeat the box's first row (entries of padding rows are unspecified)
+        if (4 * lane + 1 >= rows) tok.y = tok.x;
+        if (4 * lane + 2 >= rows) tok.z = tok.x;
+        if (4 * lane + 3 >= rows) tok.w = tok.x;
+        if (4 * lane >= rows) tok = make_int4(0, 0, 0, 0);
+        const int brow0 = e * p.N + nt * BN;
+        const uint8_t* sfa_src = p.sfa + (size_t)(row0 >> 7) * chunks_per_row * kSfChunk;
+        const uint8_t* sfb_src = p.sfb + (size_t)(brow0 >> 7) * chunks_per_row * kSfChunk;
+        const uint32_t stage_bytes = C::kStageBytes - C::kABytes + (uint32_t)nbox * 512u;
+        for (int ks = 0; ks < nk; ++ks) {
+          if (lane == 0 && !mbar_wait(bar_empty + 8 * s, ph)) { report(p.status, 101); ok = false; }
+          ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
+          if (!ok) break;
+          const uint32_t full = bar_full + 8 * s;
+          if (lane == 0) mbar_expect_tx(full, stage_bytes);
+          __syncwarp();
+          if (lane < nbox) tma_gather4(s_a + s * C::kABytes + 512u * lane, &tm_a, full, ks * 128, tok.x, tok.y, tok.z, tok.w);
+          if (lane == 0) {
+            tma_load_2d(s_b + s * C::kBBytes, &tm_b, full, ks * 128, brow0);
+            bulk_load_1d(s_sfa + s * C::kSfaBytes, sfa_src + (size_t)ks * 4 * kSfChunk, 4 * kSfChunk, full);
+#pragma unroll
+            for (int h = 0; h < BN / 128; ++h)
+              bulk_load_1d(s_sfb + s * C::kSfbBytes + h * 4 * kSfChunk,
+                           sfb_src + ((size_t)h * chunks_per_row + (size_t)ks * 4) * kSfChunk, 4 * kSfChunk, full);
+          }
+          if (++s == C::kStages) { s = 0; ph ^= 1; }
+        }
+      }
+      if (lane == 0) pdl_trigger();
+    } else if (lane == 0) {
       uint32_t s = 0, ph = 1;
       bool ok = true;
       // the tile-table entries of an item are fetched one item ahead, so their latency hides behind a whole k-loop

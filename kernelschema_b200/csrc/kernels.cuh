@@ -80,6 +80,8 @@ struct GemmParams {
   int M;                        // rows of A (dense mode only)
   int N;                        // weight rows per expert (2I for FC1, H for FC2)
   int K;                        // reduction length in FP4 elements
+  const int32_t* a_tok;         // FC1 only, non-null: the A map covers the TOKEN rows (box {128, 1}) and row r of a tile is fetched from
+                                // token a_tok[row0 + r] by TMA gather; null: the A map covers pre-permuted rows
   const uint8_t* sfa;           // A scales, 128x4 tiles [rows/128][K/64][512]
   const uint8_t* sfb;           // B scales, 128x4 tiles [E*N/128][K/64][512]
   uint8_t* act_q;               // FC1 out: packed activations [rows, I/2]

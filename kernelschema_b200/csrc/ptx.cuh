@@ -57,6 +57,15 @@ DEV void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int32_t
       ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
       : "memory");
 }
+// TMA tile::gather4: the map's 128-byte box at byte column x of FOUR rows (tensor dim-1 indices r0..r3) lands in four
+// consecutive 128-byte shared slots, the map's swizzle applied per destination row. Map: 2-D, box {128, 1}. Local memory
+// only, no multicast.
+DEV void tma_gather4(uint32_t dst, const CUtensorMap* map, uint32_t bar, int32_t x, int32_t r0, int32_t r1, int32_t r2, int32_t r3) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cta.global.tile::gather4.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(r0), "r"(r1), "r"(r2), "r"(r3)
+      : "memory");
+}
 // 1-D bulk copy global -> shared; both addresses 16-byte aligned, bytes a multiple of 16.
 DEV void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
   asm volatile(

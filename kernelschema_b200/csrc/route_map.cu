@@ -300,37 +300,33 @@ struct GatherView {
   const uint8_t* hid_sf;      // row-major [T, H/16]
   int64_t q_stride, sf_stride;
   int H;
-  uint8_t* a_q;
+  uint8_t* a_q;               // null: only the scale rows are permuted (the GEMM gathers the payload rows by TMA)
   uint8_t* a_sf;
 };
 
 DEV void gather_row(const GatherView& g, int tok, int pos, int lane) {
-  const int vecs = g.H >> 5, words = g.H >> 6;
+  const int vecs = g.a_q ? g.H >> 5 : 0, words = g.H >> 6;     // a_q == null: scales only
   const uint4* src = reinterpret_cast<const uint4*>(g.hid_q + (size_t)tok * g.q_stride);
   uint4* dst = reinterpret_cast<uint4*>(g.a_q + (size_t)pos * (g.H >> 1));
   const uint32_t* sf_src = reinterpret_cast<const uint32_t*>(g.hid_sf + (size_t)tok * g.sf_stride);
   uint32_t* sf_dst = reinterpret_cast<uint32_t*>(g.a_sf + (size_t)(pos >> 7) * words * 512 + (size_t)(pos & 31) * 16 +
                                                  (size_t)((pos >> 5) & 3) * 4);
+  uint32_t sw[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    if (lane + 32 * i < words) sw[i] = __ldg(sf_src + lane + 32 * i);
   for (int v0 = lane; v0 < vecs; v0 += 32 * 8) {
     uint4 t[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i)
       if (v0 + 32 * i < vecs) t[i] = __ldg(src + v0 + 32 * i);
-    uint32_t sw[4];
-    if (v0 == lane) {
-#pragma unroll
-      for (int i = 0; i < 4; ++i)
-        if (lane + 32 * i < words) sw[i] = __ldg(sf_src + lane + 32 * i);
-    }
 #pragma unroll
     for (int i = 0; i < 8; ++i)
       if (v0 + 32 * i < vecs) dst[v0 + 32 * i] = t[i];
-    if (v0 == lane) {
-#pragma unroll
-      for (int i = 0; i < 4; ++i)
-        if (lane + 32 * i < words) sf_dst[(size_t)(lane + 32 * i) * 128] = sw[i];
-    }
   }
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    if (lane + 32 * i < words) sf_dst[(size_t)(lane + 32 * i) * 128] = sw[i];
   for (int w = lane + 128; w < words; w += 32) sf_dst[(size_t)w * 128] = __ldg(sf_src + w);     // H > 8192
 }
 

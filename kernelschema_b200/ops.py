@@ -207,13 +207,15 @@ class MoELayer:
     """One layer instance: owns the library workspace for a geometry (b200moe_create / b200moe_destroy)."""
 
     def __init__(self, hidden: int, intermediate: int, num_experts: int, top_k: int, max_tokens: int,
-                 num_shared_experts: int = 0, tile_n: int = 0, sm_margin: int = 0, graph_cache: bool = False):
+                 num_shared_experts: int = 0, tile_n: int = 0, sm_margin: int = 0, graph_cache: bool = False,
+                 tma_gather: bool = False):
         lib = _lib.load()
         if not torch.cuda.is_available():
             raise RuntimeError("libb200moe needs a CUDA device (sm_100a); there is no CPU path")
         self.cfg = _lib.Config(struct_size=C.sizeof(_lib.Config), hidden=hidden, intermediate=intermediate,
                                num_experts=num_experts, top_k=top_k, num_shared_experts=num_shared_experts,
-                               max_tokens=max_tokens, tile_n=tile_n, sm_margin=sm_margin, graph_cache=int(bool(graph_cache)))
+                               max_tokens=max_tokens, tile_n=tile_n, sm_margin=sm_margin, graph_cache=int(bool(graph_cache)),
+                               tma_gather=int(bool(tma_gather)))
         self._h = C.c_void_p()
         _lib.check(lib.b200moe_create(C.byref(self.cfg), C.byref(self._h)), "b200moe_create")
         self.device = torch.cuda.current_device()

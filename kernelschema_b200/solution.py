@@ -29,10 +29,11 @@ class Model(torch.nn.Module):
     tensor objects skips validation and marshalling and hands the cached argument block to the library, and the
     library replays a CUDA graph from the second call with an identical argument block on (b200moe_config.graph_cache)."""
 
-    def __init__(self, graph_cache: bool = True):
+    def __init__(self, graph_cache: bool = True, tma_gather: bool = False):
         super().__init__()
         self._layers = {}
         self._graph_cache = graph_cache
+        self._tma_gather = tma_gather      # b200moe_config.tma_gather: FC1 fetches the token rows itself, no permuted copy
         self._hot = None            # (key, handle, address of the argument block, [output], device index, keep-alive)
 
     def _layer(self, hidden, intermediate, experts, top_k, shared, tokens, tune_max):
@@ -42,7 +43,8 @@ class Model(torch.nn.Module):
         if layer is None or layer.cfg.max_tokens < tokens:
             if layer is not None:
                 layer.close()
-            layer = MoELayer(hidden, intermediate, experts, top_k, cap, num_shared_experts=shared, graph_cache=self._graph_cache)
+            layer = MoELayer(hidden, intermediate, experts, top_k, cap, num_shared_experts=shared, graph_cache=self._graph_cache,
+                             tma_gather=self._tma_gather)
             self._hot = None
             self._layers[key] = layer
         return layer
