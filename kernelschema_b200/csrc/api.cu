@@ -89,6 +89,8 @@ struct b200moe_layer {
   } cache[4];
   uint64_t tick;
   cudaStream_t capture_stream;   // only ever captured on, never executed on: the caller's stream may be the legacy default
+  cudaStream_t side_stream;      // b200moe_step: the quantiser runs here, beside the router kernels on the caller's stream
+  cudaEvent_t ev_fork, ev_join;
   b200moe_stats stats;
 };
 
@@ -264,6 +266,7 @@ int run_impl(b200moe_layer* h, const b200moe_args* a, cudaStream_t st, cudaEvent
   g.tile_rows = h->rm.tile_rows;
   g.n_tiles_ptr = h->rm.totals;
   g.status = h->status;
+  g.rows_hint = (int64_t)T * h->kk;
   // FC1: [rows, H] x [2I, H]^T -> activation -> NVFP4 [rows, I]
   g.N = 2 * c.intermediate;
   g.K = c.hidden;
@@ -427,6 +430,7 @@ int b200moe_gemm_nvfp4(const void* a_q, const void* a_sf, const void* b_q, const
   g.out_stride = out_stride;
   g.dense_alpha = alpha;
   g.status = status;
+  g.rows_hint = m;
   const int sms = sm_count();
   if (bn == 512) {
     CUtensorMap tsa, tsb;
@@ -545,6 +549,9 @@ int b200moe_destroy(b200moe_handle h) {
   for (auto& c : h->cache)
     if (c.exec) cudaGraphExecDestroy(c.exec);
   if (h->capture_stream) cudaStreamDestroy(h->capture_stream);
+  if (h->side_stream) cudaStreamDestroy(h->side_stream);
+  if (h->ev_fork) cudaEventDestroy(h->ev_fork);
+  if (h->ev_join) cudaEventDestroy(h->ev_join);
   cudaError_t e = cudaFree(h->base);
   delete h;
   return cuda_fail((int)e, "destroy");
@@ -832,15 +839,40 @@ static int run_cached(b200moe_layer* h, const b200moe_args* in, cudaStream_t st)
 static int step_impl(b200moe_layer* h, const b200moe_step_args* a, cudaStream_t st) {
   const b200moe_config& c = h->cfg;
   const int T = a->num_tokens;
-  int rc = launch_quantize_nvfp4(a->x, T, c.hidden, a->x_stride, a->activation_global_scale, h->step_hq, h->step_hs,
-                                 B200MOE_SF_ROW_MAJOR, st);
-  if (rc) return cuda_fail(rc, "step: quantise");
-  if (c.top_k > 0) {
-    rc = router_logits_any(a->x, a->gate_weight, T, c.hidden, c.num_experts, h->step_logits, st);
-    if (rc) return cuda_fail(rc, "step: router logits");
-    rc = launch_route_topk(h->step_logits, a->gate_bias, T, c.num_experts, c.top_k, h->step_ids, h->step_w, st);
-    if (rc) return cuda_fail(rc, "step: top-k");
+  // The quantiser and the router kernels both read the tokens and do not depend on each other: from a few thousand
+  // tokens on (each kernel then outlasts the two event hops) the quantiser runs on a side stream beside the router; the
+  // fork and the join are events, so the pair is captured into the library's graph like any other launch.
+  const bool fork = c.top_k > 0 && T >= 2048;
+  cudaStream_t qs = st;
+  if (fork) {
+    cudaError_t e = cudaSuccess;
+    if (!h->side_stream) e = cudaStreamCreateWithFlags(&h->side_stream, cudaStreamNonBlocking);
+    if (e == cudaSuccess && !h->ev_fork) e = cudaEventCreateWithFlags(&h->ev_fork, cudaEventDisableTiming);
+    if (e == cudaSuccess && !h->ev_join) e = cudaEventCreateWithFlags(&h->ev_join, cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaEventRecord(h->ev_fork, st);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(h->side_stream, h->ev_fork, 0);
+    if (e != cudaSuccess) return cuda_fail((int)e, "step: side stream");
+    qs = h->side_stream;
   }
+  int rc = launch_quantize_nvfp4(a->x, T, c.hidden, a->x_stride, a->activation_global_scale, h->step_hq, h->step_hs,
+                                 B200MOE_SF_ROW_MAJOR, qs);
+  int rc_router = 0;
+  const char* where = "step: quantise";
+  if (c.top_k > 0) {
+    rc_router = router_logits_any(a->x, a->gate_weight, T, c.hidden, c.num_experts, h->step_logits, st);
+    if (rc_router) where = "step: router logits";
+    if (!rc_router) {
+      rc_router = launch_route_topk(h->step_logits, a->gate_bias, T, c.num_experts, c.top_k, h->step_ids, h->step_w, st);
+      if (rc_router) where = "step: top-k";
+    }
+  }
+  if (fork) {   // join even when a launch failed: a capture must not end with an unjoined stream
+    cudaError_t e = cudaEventRecord(h->ev_join, qs);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(st, h->ev_join, 0);
+    if (!rc && e != cudaSuccess) rc = (int)e;
+  }
+  if (rc) return cuda_fail(rc, "step: quantise");
+  if (rc_router) return cuda_fail(rc_router, where);
   b200moe_args r;
   memset(&r, 0, sizeof(r));
   r.struct_size = (int32_t)sizeof(r);

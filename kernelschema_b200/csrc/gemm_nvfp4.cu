@@ -722,12 +722,15 @@ static int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const GemmPa
   return (int)launch_chain(kern, dim3(grid), dim3(gemm_threads<BN, EC>()), GemmCfg<BN>::kSmemBytes, st, ta, tb, p);
 }
 
-// Epilogue columns per warp: 64 when a tile's k-loop is too short to hide the eight-warp epilogue (see epilogue_cols).
-static int epilogue_cols_for(int k) { return k >= 4096 ? 128 : 64; }
+// Epilogue columns per warp. Eight warps x 128 columns win only when the k-loop is long AND the GEMM is tensor-bound
+// (DeepSeek-V3 FC1 at T = 8192: 1-2 %). With a short k-loop the eight-warp epilogue is not hidden, and a batch that merely
+// streams its weights (rows_hint: at most that many rows of A) wants its accumulator back as early as possible:
+// T = 128 over 128 experts at K = 4096 takes 137 us per step with 16 x 64 against 151 us.
+static int epilogue_cols_for(int k, int64_t rows_hint) { return (k >= 4096 && (rows_hint == 0 || rows_hint > 8192)) ? 128 : 64; }
 
 template <int MODE>
 static int launch_mode(int bn, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid, cudaStream_t st) {
-  const int ec = epilogue_cols_for(p.K);
+  const int ec = epilogue_cols_for(p.K, p.rows_hint);
   if (bn == 128) return ec == 64 ? launch_one<MODE, 128, 64>(ta, tb, p, grid, st) : launch_one<MODE, 128, 128>(ta, tb, p, grid, st);
   if (bn == 256) return ec == 64 ? launch_one<MODE, 256, 64>(ta, tb, p, grid, st) : launch_one<MODE, 256, 128>(ta, tb, p, grid, st);
   return 703;

@@ -78,6 +78,7 @@ struct GemmParams {
   const int32_t* n_tiles_ptr;   // device count of m-tiles, or null -> n_tiles_static
   int n_tiles_static;
   int M;                        // rows of A (dense mode only)
+  int64_t rows_hint;            // most rows of A this launch can hold (0 = unknown): picks the epilogue shape, nothing else
   int N;                        // weight rows per expert (2I for FC1, H for FC2)
   int K;                        // reduction length in FP4 elements
   const int32_t* a_tok;         // FC1 only, non-null: the A map covers the TOKEN rows (box {128, 1}) and row r of a tile is fetched from

@@ -186,6 +186,9 @@ constexpr int kLgSmem = kLgStages * (kLgABytes + kLgBBytes) + 1024 + 128;
 __global__ void __launch_bounds__(192, 1)
 k_router_logits_tc(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w, int T, int H, int E,
                    int e_pad, float* __restrict__ logits, int32_t* status) {
+  // e_pad = gate rows of THIS block's tile; blockIdx.y selects which e_pad-row slice of the gate matrix (one slice, or two
+  // when a single slice per token tile would leave more than half of the SMs idle)
+  const int e0 = (int)blockIdx.y * e_pad;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t s_a = base, s_b = s_a + kLgStages * kLgABytes, s_bar = s_b + kLgStages * kLgBBytes;
@@ -218,7 +221,7 @@ k_router_logits_tc(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
           if (!mbar_wait(bar_empty + 8 * s, ((g / kLgStages) & 1) ^ 1)) { if (status) atomicCAS(status, 0, 111); ok = false; break; }
           mbar_expect_tx(bar_full + 8 * s, stage_bytes);
           tma_load_2d(s_a + s * kLgABytes, &tm_x, bar_full + 8 * s, ks * 128, tile * 128);
-          tma_load_2d(s_b + s * kLgBBytes, &tm_w, bar_full + 8 * s, ks * 128, 0);
+          tma_load_2d(s_b + s * kLgBBytes, &tm_w, bar_full + 8 * s, ks * 128, e0);
         }
     }
   } else if (warp == 1) {
@@ -259,14 +262,14 @@ k_router_logits_tc(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
         tmem_ld32(taddr + cb * 32, v);
         tmem_ld_wait();
         if (row < T) {
-          float* dst = logits + (size_t)row * E + cb * 32;
-          if (cb * 32 + 32 <= E && (E & 3) == 0) {
+          float* dst = logits + (size_t)row * E + e0 + cb * 32;
+          if (e0 + cb * 32 + 32 <= E && (E & 3) == 0) {
 #pragma unroll
             for (int j = 0; j < 8; ++j) reinterpret_cast<float4*>(dst)[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
           } else {
 #pragma unroll
             for (int j = 0; j < 32; ++j)
-              if (cb * 32 + j < E) dst[j] = v[j];
+              if (e0 + cb * 32 + j < E) dst[j] = v[j];
           }
         }
       }
@@ -282,7 +285,13 @@ k_router_logits_tc(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
 
 int launch_router_logits_tc(const void* x, const void* w, int64_t T, int H, int E, float* logits, int32_t* status, cudaStream_t st) {
   if (T == 0) return 0;
-  const int e_pad = (E + 31) / 32 * 32;
+  int e_pad = (E + 31) / 32 * 32;
+  const int sms = sm_count();
+  const int n_tiles = (int)((T + 127) / 128);
+  // Every block streams its token tile AND its gate slice once per k-step from L2, at one SM's rate: with at most half of
+  // the SMs busy, two blocks per token tile (half of the experts each) halve the gate bytes per block.
+  const int n_split = (n_tiles * 2 <= sms && e_pad % 64 == 0) ? 2 : 1;
+  e_pad /= n_split;
   CUtensorMap tx, tw;
   int rc = make_operand_map(&tx, x, (uint64_t)T, (uint64_t)H * 2, 128);
   if (rc) return rc;
@@ -290,10 +299,8 @@ int launch_router_logits_tc(const void* x, const void* w, int64_t T, int H, int 
   if (rc) return rc;
   static SmemOptIn opt_in;
   if (int e = opt_in.ensure(k_router_logits_tc, kLgSmem)) return e;
-  const int sms = sm_count();
-  const int n_tiles = (int)((T + 127) / 128);
-  return (int)launch_chain(k_router_logits_tc, dim3(n_tiles < sms ? n_tiles : sms), dim3(192), kLgSmem, st, tx, tw, (int)T, H, E, e_pad,
-                           logits, status);
+  return (int)launch_chain(k_router_logits_tc, dim3(n_tiles < sms ? n_tiles : sms, n_split), dim3(192), kLgSmem, st, tx, tw, (int)T, H, E,
+                           e_pad, logits, status);
 }
 
 int launch_route_topk(const float* logits, const float* bias, int64_t T, int E, int K, int32_t* ids, float* weights,
