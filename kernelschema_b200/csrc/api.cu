@@ -390,7 +390,10 @@ static int router_logits_any(const void* x, const void* w, int64_t T, int H, int
   if (T <= 16)      // decode sizes: stream the gate matrix over the whole device
     return launch_router_logits_small(x, w, T, H, E, logits, st);
   // tensor-core path: whole gate matrix as one B tile (E <= 256), K in 64-element stages, 16-byte aligned rows
-  if (E <= 256 && H % 64 == 0 && E % 8 == 0) return launch_router_logits_tc(x, w, T, H, E, logits, nullptr, st);
+  if (E <= 256 && H % 64 == 0 && E % 8 == 0) {
+    const int rc = launch_router_logits_ksplit(x, w, T, H, E, logits, nullptr, st);      // few token tiles: split the k-steps
+    return rc >= 0 ? rc : launch_router_logits_tc(x, w, T, H, E, logits, nullptr, st);
+  }
   return launch_router_logits(x, w, T, H, E, logits, st);
 }
 

@@ -108,6 +108,9 @@ int launch_route_topk(const float* logits, const float* bias, int64_t T, int E, 
                       cudaStream_t st);
 int launch_router_logits(const void* x, const void* w, int64_t T, int H, int E, float* logits, cudaStream_t st);
 int launch_router_logits_tc(const void* x, const void* w, int64_t T, int H, int E, float* logits, int32_t* status, cudaStream_t st);
+// While (token tiles) x (64-expert slices) fit one wave: clusters of blocks split the k-steps and meet in distributed shared
+// memory. Returns -1 when the shape does not qualify (the caller then uses launch_router_logits_tc).
+int launch_router_logits_ksplit(const void* x, const void* w, int64_t T, int H, int E, float* logits, int32_t* status, cudaStream_t st);
 int launch_router_logits_small(const void* x, const void* w, int64_t T, int H, int E, float* logits, cudaStream_t st);   // T <= 16
 // seg_len > 0: the T token slots are regions of seg_len consecutive slots and only the first seg_valid[slot / seg_len]
 // slots of each region hold a token (the receive buffer of the expert-parallel exchange); the rest count as unrouted.

@@ -303,6 +303,162 @@ int launch_router_logits_tc(const void* x, const void* w, int64_t T, int H, int 
                            e_pad, logits, status);
 }
 
+// ----------------------------------------------------------------------------- tensor-core router logits, few token tiles
+// A few token tiles: one block per tile walks H / 64 dependent k-steps at one SM's load rate (T = 64, H = 7168, E = 256:
+// 35 us for 4.6 MB; 8 us here). A token tile belongs to a CLUSTER of k_split blocks along z, each taking a
+// contiguous range of k-steps and (blockIdx.y) a slice of e_slice experts; the partial tiles meet in distributed shared
+// memory: block r of the cluster adds rows [128 r / k_split, 128 (r + 1) / k_split) of all partials in rank order
+// (reproducible) and stores them. No scratch in global memory, one launch.
+constexpr int kLkStages = 8;
+constexpr int kLkABytes = 128 * 128;
+constexpr int kLkBBytes = 64 * 128;
+constexpr int kLkSmem = kLkStages * (kLkABytes + kLkBBytes) + 1024 + 256;
+
+__global__ void __launch_bounds__(192, 1)
+k_router_logits_ksplit(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w, int T, int H, int E,
+                       int e_slice, float* __restrict__ logits, int32_t* status) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t s_a = base, s_b = s_a + kLkStages * kLkABytes, s_bar = s_b + kLkStages * kLkBBytes;
+  const uint32_t bar_full = s_bar, bar_empty = s_bar + 8 * kLkStages, bar_acc_full = bar_empty + 8 * kLkStages, s_slot = bar_acc_full + 8;
+  const uint32_t s_part = s_a;                    // after the k-loop: this block's partial tile, [e_slice][128] floats
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int k_split = (int)gridDim.z;
+  const uint32_t rank = cluster_ctarank();        // == blockIdx.z: the cluster spans z
+  const int tile = (int)blockIdx.x, e0 = (int)blockIdx.y * e_slice;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kLkStages; ++s) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
+    mbar_init(bar_acc_full, 1);
+    mbar_init_fence();
+  }
+  if (warp == 1) tmem_alloc<64>(s_slot);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  uint32_t tmem;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem) : "r"(s_slot));
+  pdl_trigger();
+  pdl_wait();
+  const int steps = (H >> 6) / k_split, ks0 = (int)rank * steps;
+  const uint32_t stage_bytes = kLkABytes + (uint32_t)e_slice * 128;
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int i = 0; i < steps; ++i) {
+        const uint32_t s = i % kLkStages;
+        if (!mbar_wait(bar_empty + 8 * s, ((i / kLkStages) & 1) ^ 1)) { if (status) atomicCAS(status, 0, 115); break; }
+        mbar_expect_tx(bar_full + 8 * s, stage_bytes);
+        tma_load_2d(s_a + s * kLkABytes, &tm_x, bar_full + 8 * s, (ks0 + i) * 128, tile * 128);
+        tma_load_2d(s_b + s * kLkBBytes, &tm_w, bar_full + 8 * s, (ks0 + i) * 128, e0);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_bf16(128, e_slice);
+      bool ok = true;
+      for (int i = 0; i < steps; ++i) {
+        const uint32_t s = i % kLkStages;
+        if (!mbar_wait(bar_full + 8 * s, (i / kLkStages) & 1)) { if (status) atomicCAS(status, 0, 116); ok = false; break; }
+        tc_fence_after();
+        const uint64_t a_d = make_desc_sw128(s_a + s * kLkABytes), b_d = make_desc_sw128(s_b + s * kLkBBytes);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) mma_bf16(tmem, a_d + 2 * q, b_d + 2 * q, idesc, (i | q) ? 1u : 0u);
+        mma_commit(bar_empty + 8 * s);
+      }
+      if (ok) mma_commit(bar_acc_full);
+    }
+    __syncwarp();
+  } else {
+    // accumulator -> this block's partial tile in shared memory, column-major so that the 32 rows of a warp are contiguous
+    const int quad = warp & 3;
+    int okw = 1;
+    if (lane == 0) okw = mbar_wait(bar_acc_full, 0) ? 1 : 0;
+    okw = __shfl_sync(0xFFFFFFFFu, okw, 0);
+    if (!okw) {
+      if (lane == 0 && status) atomicCAS(status, 0, 117);
+    } else {
+      tc_fence_after();
+      const int row = quad * 32 + lane;
+      const uint32_t taddr = tmem + ((uint32_t)(quad * 32) << 16);
+      for (int cb = 0; cb < e_slice / 32; ++cb) {
+        float v[32];
+        tmem_ld32(taddr + cb * 32, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          asm volatile("st.shared.f32 [%0], %1;" ::"r"(s_part + (uint32_t)(((cb * 32 + j) * 128 + row) * 4)), "f"(v[j]) : "memory");
+      }
+      tc_fence_before();
+    }
+  }
+  cluster_sync_all();                             // every partial tile of the cluster is in place
+  {
+    const int rows_per = 128 / k_split;
+    const int row_base = (int)rank * rows_per;
+    for (int i = threadIdx.x; i < rows_per * e_slice; i += blockDim.x) {
+      const int r = row_base + i % rows_per, col = i / rows_per;     // rows fastest: neighbouring lanes read neighbouring words
+      const uint32_t at = s_part + (uint32_t)((col * 128 + r) * 4);
+      float v[8];                                 // all remote loads first (a distributed-shared-memory round trip each), then
+#pragma unroll                                    // the sum in rank order
+      for (int j = 0; j < 8; ++j) {
+        v[j] = 0.f;
+        if (j < k_split) asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v[j]) : "r"(map_to_cta(at, (uint32_t)j)));
+      }
+      float sum = v[0];
+#pragma unroll
+      for (int j = 1; j < 8; ++j)
+        if (j < k_split) sum += v[j];
+      const int row = tile * 128 + r;
+      if (row < T && e0 + col < E) logits[(size_t)row * E + e0 + col] = sum;
+    }
+  }
+  cluster_sync_all();                             // nobody leaves while a peer still reads its partial tile
+  if (warp == 1) { __syncwarp(); tmem_dealloc<64>(tmem); }
+}
+
+// k_split for the cluster form: the largest of 8, 4, 2, 1 that divides the k-steps and keeps the grid within the SMs; 0 = do
+// not use it (the grid would not fit one wave, or the shape does not fit).
+static int router_ksplit(int64_t T, int H, int E, int* e_slice_out) {
+  const int n_tiles = (int)((T + 127) / 128);
+  const int e_pad = (E + 31) / 32 * 32;
+  if (H % 64 || e_pad > 256) return 0;
+  const int e_slice = e_pad % 64 == 0 ? 64 : 32;
+  const int slices = e_pad / e_slice;
+  const int sms = sm_count();
+  for (int ks = 8; ks >= 1; ks >>= 1)            // ks = 1: no split, but 64-expert slices put four blocks on a token tile
+    if ((H >> 6) % ks == 0 && n_tiles * slices * ks <= sms) { *e_slice_out = e_slice; return ks; }
+  return 0;
+}
+
+int launch_router_logits_ksplit(const void* x, const void* w, int64_t T, int H, int E, float* logits, int32_t* status, cudaStream_t st) {
+  int e_slice = 0;
+  const int k_split = router_ksplit(T, H, E, &e_slice);
+  if (!k_split) return -1;                        // caller falls back to the one-block-per-tile kernel
+  const int e_pad = (E + 31) / 32 * 32;
+  CUtensorMap tx, tw;
+  int rc = make_operand_map(&tx, x, (uint64_t)T, (uint64_t)H * 2, 128);
+  if (rc) return rc;
+  rc = make_operand_map(&tw, w, (uint64_t)E, (uint64_t)H * 2, (uint32_t)e_slice);
+  if (rc) return rc;
+  static SmemOptIn opt_in;
+  if (int e = opt_in.ensure(k_router_logits_ksplit, kLkSmem)) return e;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)((T + 127) / 128), (unsigned)(e_pad / e_slice), (unsigned)k_split);
+  cfg.blockDim = dim3(192);
+  cfg.dynamicSmemBytes = kLkSmem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = (unsigned)k_split;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 2 : 1;
+  return (int)cudaLaunchKernelEx(&cfg, k_router_logits_ksplit, tx, tw, (int)T, H, E, e_slice, logits, status);
+}
+
 int launch_route_topk(const float* logits, const float* bias, int64_t T, int E, int K, int32_t* ids, float* weights,
                       cudaStream_t st) {
   if (T == 0) return 0;
