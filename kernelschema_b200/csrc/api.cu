@@ -387,10 +387,14 @@ int b200moe_route_topk(const float* logits, const float* bias, int64_t T, int32_
 }
 
 static int router_logits_any(const void* x, const void* w, int64_t T, int H, int E, float* logits, cudaStream_t st) {
-  if (T <= 16)      // decode sizes: stream the gate matrix over the whole device
+  // A handful of tokens: the SIMT kernel streams the gate matrix over the whole device (T = 1: 2.4 us at H 2048 / E 128, 6 us
+  // at H 7168 / E 256; its cost grows with T, and from T x H ~ 32K elements on the cluster kernel below is faster: 5.5 / 8.3 us
+  // up to 256 tokens). It also serves shapes the tensor-core kernels do not take.
+  const bool tc_ok = E <= 256 && H % 64 == 0 && E % 8 == 0;
+  if (T <= 16 && (!tc_ok || (T <= 8 && T * H <= 32768)))
     return launch_router_logits_small(x, w, T, H, E, logits, st);
   // tensor-core path: whole gate matrix as one B tile (E <= 256), K in 64-element stages, 16-byte aligned rows
-  if (E <= 256 && H % 64 == 0 && E % 8 == 0) {
+  if (tc_ok) {
     const int rc = launch_router_logits_ksplit(x, w, T, H, E, logits, nullptr, st);      // few token tiles: split the k-steps
     return rc >= 0 ? rc : launch_router_logits_tc(x, w, T, H, E, logits, nullptr, st);
   }

@@ -160,10 +160,10 @@ def test_router_random_with_bias_and_ties(t, e, k):
 
 @pytest.mark.parametrize("t,h,e", [(300, 2048, 130), (300, 7168, 256), (1000, 2048, 128), (129, 1024, 8), (5, 256, 72),
                                    (1, 7168, 256), (8, 2048, 128), (9, 2048, 127), (16, 7168, 256), (17, 2048, 128),
-                                   (64, 7168, 256), (128, 2048, 40), (200, 1088, 64), (1024, 4096, 24), (1025, 2048, 128),
+                                   (8, 7168, 256), (12, 2048, 128), (64, 7168, 256), (128, 2048, 40), (200, 1088, 64), (1024, 4096, 24), (1025, 2048, 128),
                                    (2000, 7168, 256), (8192, 2048, 256)])
 def test_router_logits(t, h, e):
-    """Up to 16 tokens take the decode kernel; above, e=130 takes the SIMT kernel, the others the tcgen05 bf16 kernels:
+    """A handful of tokens (T <= 8 and T x H <= 32768, or shapes the tensor-core kernels do not take) run the SIMT decode kernel; above, e=130 takes the SIMT kernel, the others the tcgen05 bf16 kernels:
     while token tiles x 64-expert slices fit one wave, clusters of 8, 4, 2 or 1 blocks that split the k-steps (1088 = 17
     k-steps cannot be split), above that one or two blocks per token tile."""
     import kernelschema_b200 as ks
