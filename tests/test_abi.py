@@ -53,6 +53,11 @@ def test_bad_config_is_refused_without_a_device(lib):
     assert lib.b200moe_create(C.byref(cfg), C.byref(h)) == 710
     cfg.struct_size = C.sizeof(_lib.Config)
     assert lib.b200moe_workspace_bytes(C.byref(cfg)) > 0
+    cfg.tma_gather = 2
+    assert lib.b200moe_create(C.byref(cfg), C.byref(h)) == 707 and b"tma_gather" in lib.b200moe_last_error()
+    cfg.tma_gather = 0
+    cfg.graph_cache = 5
+    assert lib.b200moe_create(C.byref(cfg), C.byref(h)) == 709
 
 
 def test_argument_checks_precede_launches(lib):
