@@ -12,8 +12,11 @@
 
 namespace b200 {
 
-constexpr int kRouteChunk = 2048;        // routes per block: 8 warps x 8 steps x 32 lanes
-constexpr int kRouteWarps = 8;
+constexpr int kRouteChunk = 2048;        // routes per block: 32 warps x 2 steps x 32 lanes
+constexpr int kRouteWarps = 32;          // these kernels are a few thousand dependent instructions per warp and one block per
+                                         // chunk: with 8 warps a block issued one instruction every ~5 cycles per scheduler
+constexpr int kRouteThreads = kRouteWarps * 32;
+constexpr int kRouteSmemMax = 160 * 1024;  // (32 + 2) x 1024 experts x 4 B + 16 KB of positions
 
 struct RouteView {
   const int32_t* ids;
@@ -98,7 +101,7 @@ DEV void chunk_histogram(const int (&e)[STEPS], int etot, int* hist) {
   __syncthreads();
 }
 
-__global__ void __launch_bounds__(256) k_route_hist(RouteView r, int etot, int32_t* __restrict__ block_hist) {
+__global__ void __launch_bounds__(kRouteThreads) k_route_hist(RouteView r, int etot, int32_t* __restrict__ block_hist) {
   extern __shared__ int hist[];
   pdl_trigger();
   pdl_wait();
@@ -225,7 +228,7 @@ __global__ void __launch_bounds__(1024) k_route_scan(int etot, int nblk, int32_t
   }
 }
 
-__global__ void __launch_bounds__(256) k_route_scatter(RouteView r, const float* __restrict__ scores, int etot,
+__global__ void __launch_bounds__(kRouteThreads) k_route_scatter(RouteView r, const float* __restrict__ scores, int etot,
                                                        const int32_t* __restrict__ block_base, const int32_t* __restrict__ seg_start,
                                                        int32_t* __restrict__ row_of, int32_t* __restrict__ tok_of_row,
                                                        float* __restrict__ weight_of_row) {
@@ -335,7 +338,8 @@ DEV void gather_row(const GatherView& g, int tok, int pos, int lane) {
 // Out: segment starts, tile and pair tables and totals (stored by the `writer` block only), and hist[w][e] turned into
 // the permuted row of warp w's first route of expert e. Ends with a block barrier.
 DEV void scan_experts(int etot, const int* others, const int* before, int* hist, bool writer, const RouteMapBuffers& b) {
-  __shared__ int warp_pad[8], warp_tiles[8], warp_pairs[8], warp_cnt[8];
+  const int nw = (int)blockDim.x >> 5;             // warps of the block = rows of hist
+  __shared__ int warp_pad[kRouteWarps], warp_tiles[kRouteWarps], warp_pairs[kRouteWarps], warp_cnt[kRouteWarps];
   __shared__ int carry[4];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   if (threadIdx.x < 4) carry[threadIdx.x] = 0;
@@ -345,8 +349,7 @@ DEV void scan_experts(int etot, const int* others, const int* before, int* hist,
     int cnt = 0;
     if (e < etot) {
       cnt = others[e];
-#pragma unroll
-      for (int w = 0; w < kRouteWarps; ++w) cnt += hist[w * etot + e];
+      for (int w = 0; w < nw; ++w) cnt += hist[w * etot + e];
     }
     const int ntile = (cnt + 127) >> 7, pad = ntile << 7, npair = (ntile + 1) >> 1;
     int ip = pad, it = ntile, ic = cnt, iq = npair;
@@ -378,8 +381,7 @@ DEV void scan_experts(int etot, const int* others, const int* before, int* hist,
           }
       }
       int run = start + before[e];                   // per-warp bases of this expert, in place of the counts
-#pragma unroll
-      for (int w = 0; w < kRouteWarps; ++w) {
+      for (int w = 0; w < nw; ++w) {
         const int c = hist[w * etot + e];
         hist[w * etot + e] = run;
         run += c;
@@ -388,7 +390,7 @@ DEV void scan_experts(int etot, const int* others, const int* before, int* hist,
     __syncthreads();
     if (threadIdx.x == blockDim.x - 1) {
       int tc = 0;
-      for (int w = 0; w < kRouteWarps; ++w) tc += warp_cnt[w];
+      for (int w = 0; w < nw; ++w) tc += warp_cnt[w];
       carry[0] = bp + ip;
       carry[1] = bt + it;
       carry[2] += tc;
@@ -405,11 +407,11 @@ DEV void scan_experts(int etot, const int* others, const int* before, int* hist,
   }
 }
 
-// A chunk's routes are dealt to the 8 warps in runs of `rpw` (a multiple of 32, just enough for the chunk), so that a
+// A chunk's routes are dealt to the block's warps in runs of `rpw` (a multiple of 32, just enough for the chunk), so that a
 // small chunk occupies every warp with one step instead of one warp with eight; positions stay in ascending route order.
-DEV int routes_per_warp(int chunk_total) { return max(32, (((chunk_total + kRouteWarps - 1) / kRouteWarps) + 31) & ~31); }
+DEV int routes_per_warp(int chunk_total, int nw = kRouteWarps) { return max(32, (((chunk_total + nw - 1) / nw) + 31) & ~31); }
 
-__global__ void __launch_bounds__(256) k_route_fused(RouteView r, const float* __restrict__ scores, int etot, RouteMapBuffers b) {
+__global__ void __launch_bounds__(kRouteThreads) k_route_fused(RouteView r, const float* __restrict__ scores, int etot, RouteMapBuffers b) {
   extern __shared__ int hist[];                    // own chunk [kRouteWarps][etot] | all chunks [etot] | chunks before [etot]
   int* others = hist + kRouteWarps * etot;         // routes of expert e in the other chunks
   int* before = others + etot;                     // ... in the chunks before this block's
@@ -478,20 +480,21 @@ __global__ void __launch_bounds__(256) k_route_fused(RouteView r, const float* _
 // whole map for itself in shared memory (a few thousand integer operations), block 0 stores it, and the blocks share the
 // row copies, one warp per routed row. The step loops are rolled: a one-wave, latency-bound kernel pays for every
 // instruction-cache line it touches, and a decode batch takes one step.
-__global__ void __launch_bounds__(256) k_route_gather(RouteView r, const float* __restrict__ scores, int etot, RouteMapBuffers b,
+__global__ void __launch_bounds__(kRouteThreads) k_route_gather(RouteView r, const float* __restrict__ scores, int etot, RouteMapBuffers b,
                                                       GatherView gv) {
-  extern __shared__ int hist[];                    // [kRouteWarps][etot] | zeros [etot] | zeros [etot] | expert, then row, of every route
-  int* zeros = hist + kRouteWarps * etot;
+  extern __shared__ int hist[];                    // [warps][etot] | zeros [etot] | zeros [etot] | expert, then row, of every route
+  const int nw = (int)blockDim.x >> 5;             // 8 warps for a handful of routes, kRouteWarps otherwise
+  int* zeros = hist + nw * etot;
   int* s_pos = zeros + 2 * etot;
   const int kk = r.K + r.S;
   const int total = (int)(r.T * kk);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const bool writer = blockIdx.x == 0;
-  const int rpw = routes_per_warp(total), nsteps = rpw >> 5;
+  const int rpw = routes_per_warp(total, nw), nsteps = rpw >> 5;
   const int bits = expert_bits(etot);
   pdl_trigger();
   pdl_wait();
-  for (int i = threadIdx.x; i < (kRouteWarps + 2) * etot; i += blockDim.x) hist[i] = 0;
+  for (int i = threadIdx.x; i < (nw + 2) * etot; i += blockDim.x) hist[i] = 0;
 #pragma unroll 4
   for (int step = 0; step < nsteps; ++step) {
     const int f = warp * rpw + step * 32 + lane;
@@ -534,8 +537,8 @@ __global__ void __launch_bounds__(256) k_route_gather(RouteView r, const float* 
     }
   }
   __syncthreads();
-  const int warps = (int)gridDim.x * kRouteWarps;
-  for (int f = (int)blockIdx.x * kRouteWarps + warp; f < total; f += warps) {
+  const int warps = (int)gridDim.x * nw;
+  for (int f = (int)blockIdx.x * nw + warp; f < total; f += warps) {
     const int at = s_pos[f];
     if (at >= 0) gather_row(gv, f / kk, at, lane);
   }
@@ -547,23 +550,30 @@ int launch_route_map(const int32_t* ids, const float* scores, int64_t id_stride,
   const int64_t total = T * (K + S);
   const int nblk = (int)((total + kRouteChunk - 1) / kRouteChunk);
   RouteView r{ids, id_stride > 0 ? id_stride : K, T, K, S, E, expert_offset, seg_valid ? seg_len : 0, seg_valid};
+  {
+    static SmemOptIn fused_opt, hist_opt, scatter_opt;
+    if (int e = fused_opt.ensure(k_route_fused, kRouteSmemMax)) return e;
+    if (int e = hist_opt.ensure(k_route_hist, kRouteSmemMax)) return e;
+    if (int e = scatter_opt.ensure(k_route_scatter, kRouteSmemMax)) return e;
+  }
   if (nblk >= 1 && nblk <= kFusedMaxBlocks)
-    return (int)launch_chain(k_route_fused, dim3(nblk), dim3(256), sizeof(int) * (kRouteWarps + 2) * (size_t)etot, st, r, scores, etot, b);
+    return (int)launch_chain(k_route_fused, dim3(nblk), dim3(kRouteThreads), sizeof(int) * (kRouteWarps + 2) * (size_t)etot, st, r, scores,
+                             etot, b);
   const size_t smem = sizeof(int) * kRouteWarps * (size_t)etot;
   cudaError_t err = cudaSuccess;
-  if (nblk > 0) err = launch_chain(k_route_hist, dim3(nblk), dim3(256), smem, st, r, etot, b.block_hist);
+  if (nblk > 0) err = launch_chain(k_route_hist, dim3(nblk), dim3(kRouteThreads), smem, st, r, etot, b.block_hist);
   if (err == cudaSuccess)
     err = launch_chain(k_route_scan, dim3(1), dim3(1024), 0, st, etot, nblk, b.block_hist, b.counts, b.seg_start, b.tile_expert,
                        b.tile_row0, b.tile_rows, b.totals, b.pair_expert, b.pair_row0, b.pair_rows);
   if (err == cudaSuccess && nblk > 0)
-    err = launch_chain(k_route_scatter, dim3(nblk), dim3(256), smem, st, r, scores, etot, (const int32_t*)b.block_hist,
+    err = launch_chain(k_route_scatter, dim3(nblk), dim3(kRouteThreads), smem, st, r, scores, etot, (const int32_t*)b.block_hist,
                        (const int32_t*)b.seg_start, b.row_of, b.tok_of_row, b.weight_of_row);
   return (int)err;
 }
 
 bool route_gather_fits(int64_t T, int K, int S, int E, int H) {
   const int64_t total = T * (K + S);
-  return total >= 1 && total <= kGatherMaxRoutes && sizeof(int) * ((kRouteWarps + 2) * (size_t)(E + S) + kGatherMaxRoutes) <= 48 * 1024 &&
+  return total >= 1 && total <= kGatherMaxRoutes && sizeof(int) * ((kRouteWarps + 2) * (size_t)(E + S) + kGatherMaxRoutes) <= kRouteSmemMax &&
          H % 256 == 0;
 }
 
@@ -575,10 +585,14 @@ int launch_route_gather(const int32_t* ids, const float* scores, int64_t id_stri
   RouteView r{ids, id_stride > 0 ? id_stride : K, T, K, S, E, expert_offset, seg_valid ? seg_len : 0, seg_valid};
   GatherView gv{(const uint8_t*)hid_q, (const uint8_t*)hid_sf, q_stride > 0 ? q_stride : (int64_t)(H / 2),
                 sf_stride > 0 ? sf_stride : (int64_t)(H / 16), H, (uint8_t*)a_q, (uint8_t*)a_sf};
-  int64_t blocks = (total + kRouteWarps - 1) / kRouteWarps;     // one row per warp while the SMs last
+  // a handful of routes (one step of 8 warps): a small block, whose barriers and zeroing cost less (T = 1: 2 us per step)
+  const int threads = total <= 256 ? 256 : kRouteThreads;
+  int64_t blocks = (total + threads / 32 - 1) / (threads / 32);     // one row per warp while the SMs last
   if (blocks > sm_count()) blocks = sm_count();
-  return (int)launch_chain(k_route_gather, dim3((unsigned)blocks), dim3(256),
-                           sizeof(int) * ((kRouteWarps + 2) * (size_t)etot + kGatherMaxRoutes), st, r, scores, etot, b, gv);
+  static SmemOptIn opt_in;
+  if (int e = opt_in.ensure(k_route_gather, kRouteSmemMax)) return e;
+  return (int)launch_chain(k_route_gather, dim3((unsigned)blocks), dim3(threads),
+                           sizeof(int) * ((threads / 32 + 2) * (size_t)etot + kGatherMaxRoutes), st, r, scores, etot, b, gv);
 }
 
 // ----------------------------------------------------------------------------- allocation-free variant
