@@ -283,10 +283,11 @@ def test_library_graph_cache_and_hot_call():
     cached.close()
 
 
-@pytest.mark.parametrize("t,graph", [(200, False), (200, True), (1, True), (16, True)])
+@pytest.mark.parametrize("t,graph", [(200, False), (200, True), (1, True), (16, True), (2500, False), (2500, True)])
 def test_whole_step_entry_equals_separate_calls(t, graph):
     """b200moe_step (bf16 tokens -> quantiser -> router logits -> top-k -> layer in one library call) against the same
-    kernels called one by one; with the graph cache the second call captures and the later ones replay."""
+    kernels called one by one; with the graph cache the second call captures and the later ones replay. From 2048 tokens
+    on the quantiser runs on the library's side stream beside the router kernels (fork and join by events, captured too)."""
     import kernelschema_b200 as ks
     from gpu_util import to_dev
     h, i, e, k, s = 512, 256, 16, 4, 1
