@@ -61,29 +61,32 @@ DEV void copy_row_batched(const uint4* __restrict__ src, uint4* __restrict__ dst
   }
 }
 
-// Tile form of the permute for row-major token scales: one block per 128-row tile of the permuted buffer. The tile's
-// scale image ([H/64] chunks of 512 bytes, the layout tcgen05.cp consumes) is assembled in shared memory - thread r
-// walks the scale bytes of row r's token with 16-byte loads - and leaves with full 16-byte coalesced stores; written
-// word by word from the rows it would cost one 32-byte sector per 4 bytes. Payload rows are copied by the warps, two rows
-// in flight per warp. Padding rows (past the tile's count) get zero scales and keep whatever payload they had.
-// a_q == null: scales only (the GEMM fetches the payload rows of the tokens itself).
-__global__ void __launch_bounds__(256) k_gather_tiles(const uint8_t* __restrict__ hid_q, const uint8_t* __restrict__ hid_sf,
-                                                      int64_t q_stride, int64_t sf_stride, const int32_t* __restrict__ tok_of_row,
-                                                      const int32_t* __restrict__ tile_rows, const int32_t* __restrict__ totals, int H,
-                                                      uint8_t* __restrict__ a_q, uint8_t* __restrict__ a_sf) {
+// Tile form of the permute for row-major token scales: one block of 16 warps per 128-row tile of the permuted buffer. Warps
+// 0-3 assemble the tile's scale image ([H/64] chunks of 512 bytes, the layout tcgen05.cp consumes) in shared memory -
+// thread r walks the scale bytes of row r's token with 16-byte loads - and store it with full 16-byte coalesced writes
+// (written word by word from the rows it would cost one 32-byte sector per 4 bytes). Payload rows are dealt to the warps
+// from a shared counter, one row (eight 16-byte vectors per lane in flight) at a time: the other twelve warps start at
+// once, the scale warps join when the image is out. Padding rows (past the tile's count) get zero scales and keep whatever
+// payload they had. a_q == null: scales only (the GEMM fetches the payload rows of the tokens itself).
+__global__ void __launch_bounds__(512, 2) k_gather_tiles(const uint8_t* __restrict__ hid_q, const uint8_t* __restrict__ hid_sf,
+                                                         int64_t q_stride, int64_t sf_stride, const int32_t* __restrict__ tok_of_row,
+                                                         const int32_t* __restrict__ tile_rows, const int32_t* __restrict__ totals, int H,
+                                                         uint8_t* __restrict__ a_q, uint8_t* __restrict__ a_sf) {
   extern __shared__ uint4 s_img4[];                 // [H/64][512 B]
   uint32_t* s_img = reinterpret_cast<uint32_t*>(s_img4);
   __shared__ int s_tok[128];
+  __shared__ int s_next;
   pdl_trigger();
   pdl_wait();
   const int n_tiles = totals[0];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int lane = threadIdx.x & 31;
   const int chunks = H >> 6;                        // 512-byte scale chunks per tile = 4-byte scale words per row
   const int vec_per_row = H >> 5;                   // 16-byte vectors of payload per row
   for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
     const int rows = tile_rows[tile];
     const int row0 = tile << 7;
     if (threadIdx.x < 128) s_tok[threadIdx.x] = threadIdx.x < rows ? tok_of_row[row0 + threadIdx.x] : -1;
+    if (threadIdx.x == 0) s_next = 0;
     __syncthreads();
     if (threadIdx.x < 128) {
       const int r = threadIdx.x;
@@ -91,13 +94,13 @@ __global__ void __launch_bounds__(256) k_gather_tiles(const uint8_t* __restrict_
       uint32_t* dst = s_img + (r & 31) * 4 + (r >> 5);          // word (row, chunk j) lives at j * 128 + (r % 32) * 4 + r / 32
       if (tok >= 0) {
         const uint4* src = reinterpret_cast<const uint4*>(hid_sf + (size_t)tok * sf_stride);
-        for (int j0 = 0; j0 < (chunks >> 2); j0 += 8) {          // eight 16-byte loads in flight, then their 32 words
-          uint4 v[8];
+        for (int j0 = 0; j0 < (chunks >> 2); j0 += 4) {          // four 16-byte loads in flight, then their 16 words
+          uint4 v[4];
 #pragma unroll
-          for (int i = 0; i < 8; ++i)
+          for (int i = 0; i < 4; ++i)
             if (j0 + i < (chunks >> 2)) v[i] = __ldg(src + j0 + i);
 #pragma unroll
-          for (int i = 0; i < 8; ++i)
+          for (int i = 0; i < 4; ++i)
             if (j0 + i < (chunks >> 2)) {
               const int j4 = j0 + i;
               dst[(4 * j4 + 0) * 128] = v[i].x;
@@ -109,24 +112,21 @@ __global__ void __launch_bounds__(256) k_gather_tiles(const uint8_t* __restrict_
       } else {
         for (int j = 0; j < chunks; ++j) dst[j * 128] = 0u;
       }
-    } else if (a_q) {
-      // the other four warps start on the payload meanwhile: rows 0, 4, 8, ... of the tile (the rest follows below)
-      for (int r = warp - 4; r < rows; r += 8)
-        copy_row_batched(reinterpret_cast<const uint4*>(hid_q + (size_t)s_tok[r] * q_stride),
-                         reinterpret_cast<uint4*>(a_q + (size_t)(row0 + r) * (H >> 1)), vec_per_row, lane);
-    }
-    __syncthreads();
-    {
+      asm volatile("bar.sync 1, 128;" ::: "memory");             // the four scale warps only: the image is complete
       uint4* out = reinterpret_cast<uint4*>(a_sf + (size_t)tile * chunks * 512);
-      for (int i = threadIdx.x; i < chunks * 32; i += blockDim.x) out[i] = s_img4[i];
+      for (int i = threadIdx.x; i < chunks * 32; i += 128) out[i] = s_img4[i];
     }
-    // payload rows 4..7 (mod 8) by warps 0..3, the other half by warps 4..7 above; two rows in flight per warp
-    if (warp < 4 && a_q) {
-      for (int r = warp + 4; r < rows; r += 8)
+    if (a_q) {
+      for (;;) {
+        int r = 0;
+        if (lane == 0) r = atomicAdd(&s_next, 1);
+        r = __shfl_sync(0xFFFFFFFFu, r, 0);
+        if (r >= rows) break;
         copy_row_batched(reinterpret_cast<const uint4*>(hid_q + (size_t)s_tok[r] * q_stride),
                          reinterpret_cast<uint4*>(a_q + (size_t)(row0 + r) * (H >> 1)), vec_per_row, lane);
+      }
     }
-    __syncthreads();                                  // s_tok and the image are reused by the next tile
+    __syncthreads();                                  // s_tok, the counter and the image are reused by the next tile
   }
 }
 
@@ -140,10 +140,10 @@ int launch_gather_rows(const void* hid_q, const void* hid_sf, int hid_sf_tiled, 
     static SmemOptIn opt_in;
     if (int e = opt_in.ensure(k_gather_tiles, (int)(96 * 1024))) return e;
     int64_t blocks = row_capacity / 128;
-    const int64_t resident = (int64_t)sm_count() * (img > 48 * 1024 ? 3 : 6);
+    const int64_t resident = (int64_t)sm_count() * 2;      // two 512-thread blocks per SM
     if (blocks > resident) blocks = resident;
     if (blocks < 1) blocks = 1;
-    return (int)launch_chain(k_gather_tiles, dim3((unsigned)blocks), dim3(256), img, st, (const uint8_t*)hid_q, (const uint8_t*)hid_sf,
+    return (int)launch_chain(k_gather_tiles, dim3((unsigned)blocks), dim3(512), img, st, (const uint8_t*)hid_q, (const uint8_t*)hid_sf,
                              qs, ss, tok_of_row, tile_rows, totals, H, (uint8_t*)a_q, (uint8_t*)a_sf);
   }
   // Tiled token scales (or odd strides): one warp per permuted row. Short rows (H <= 4096): a resident grid of 8 blocks per
