@@ -4,7 +4,9 @@ checked through size-independent properties and a handful of sampled tokens agai
 * token permutation: rows are independent, so permuting the tokens permutes the output bit for bit;
 * routing-weight scaling by 2 (exact in fp32 and bf16) doubles the output bit for bit;
 * tokens whose routes are all invalid produce exact zeros (plus the shared expert's row when there is one);
-* sampled tokens: the oracle evaluates only the experts those tokens touch.
+* sampled tokens: the oracle evaluates only the experts those tokens touch;
+* decode batches: the first 1, 32, 64 and 256 tokens run alone take other kernels (one-launch route map + permute,
+  narrower tiles and epilogues, batched combine) and must reproduce their rows of the full batch bit for bit.
 Weights are generated and quantised on the device with the benchmark's own generator (the quantiser's bytes are
 verified separately, bit for bit)."""
 import os
@@ -99,6 +101,10 @@ def test_full_size_properties_and_samples(name, n_sample):
     tokens = sorted(rng.choice(t, size=n_sample, replace=False).tolist())
     ref = _oracle_for_tokens(wl, L, ids, w, hq, hs, tokens)
     assert_layer_parity(base[torch.as_tensor(tokens, device=ids.device)].float().cpu().numpy(), ref, f"{name} sampled tokens")
+    # decode batches of the same tokens: every output element is the same sum in the same order, whatever the tile shapes
+    for n in (1, 32, 64, 256):
+        small = run(ids[:n].contiguous(), w[:n].contiguous(), hq[:n].contiguous(), hs.view(torch.uint8)[:n].contiguous())
+        assert torch.equal(small, base[:n]), f"{name}: decode batch of {n} tokens differs from its rows of the full batch"
     layer.close()
 
 
