@@ -196,10 +196,10 @@ def make_step(wl, L, world, device, tokens=None):
             return out, ids_view[:x.shape[0]]
 
         step.front = front
-        # quantiser, router logits, top-k + the layer: route map and permute are one kernel up to 4096 routes, the route map
+        # quantiser, router logits, top-k + the layer: route map and permute are one kernel up to 8192 routes, the route map
         # alone is one kernel up to 16384 routes and three above; then FC1, FC2 and the combine
         routes = t * (k + s)
-        return step, layer, 3 + (4 if routes <= 4096 else 5 if routes <= 16384 else 7)
+        return step, layer, 3 + (4 if routes <= 8192 else 5 if routes <= 16384 else 7)
     from kernelschema_b200.ep import ExpertParallelMoE
     ep = ExpertParallelMoE(h, i, e, k, t, num_shared_experts=s)
 

@@ -116,7 +116,7 @@ int launch_router_logits_small(const void* x, const void* w, int64_t T, int H, i
 // slots of each region hold a token (the receive buffer of the expert-parallel exchange); the rest count as unrouted.
 int launch_route_map(const int32_t* ids, const float* scores, int64_t id_stride, int64_t T, int K, int S, int E, int expert_offset,
                      RouteMapBuffers b, cudaStream_t st, int seg_len = 0, const int32_t* seg_valid = nullptr);
-// Route map and permute in ONE launch for batches of at most 4096 routes with row-major token scales (decode sizes):
+// Route map and permute in ONE launch for batches of at most 8192 routes with row-major token scales (decode sizes):
 // `route_gather_fits` says whether a call qualifies.
 bool route_gather_fits(int64_t T, int K, int S, int E, int H);
 int launch_route_gather(const int32_t* ids, const float* scores, int64_t id_stride, int64_t T, int K, int S, int E, int expert_offset,

@@ -293,7 +293,7 @@ __global__ void __launch_bounds__(kRouteThreads) k_route_scatter(RouteView r, co
 // the segment). The counts of foreign chunks are accumulated with shared-memory atomics; a count does not depend on the
 // order of the additions, so every output stays reproducible. Block 0 also writes the per-expert tables.
 constexpr int kFusedMaxBlocks = 8;
-constexpr int kGatherMaxRoutes = 4096;           // the fused form that also permutes the rows: 16 routes per lane of ONE chunk
+constexpr int kGatherMaxRoutes = 8192;           // the fused form that also permutes the rows: 8 routes per lane of ONE chunk
 
 // The permute of one routed row from inside the route-map kernel (small batches): payload with 16-byte vectors, the row's
 // scale words straight into the 128x4-tiled image. Scales of padding rows are left as they are: the GEMMs neither store

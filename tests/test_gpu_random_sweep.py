@@ -1,6 +1,6 @@
 """Seeded sweep over small layer geometries against the oracle: expert counts from 1 to 300, 1 to 12 slots per token
 (routed + shared: the combine pass batches eight slots at a time), batches from 1 to 700 tokens (the one-launch route map +
-permute up to 4096 routes, the one-block route map up to 16384, the three-kernel build above), masked routes, Zipf and
+permute up to 8192 routes, the one-block route map up to 16384, the three-kernel build above), masked routes, Zipf and
 uniform routing, both activation types. Integer tables bit for bit, outputs by the reference's acceptance rule."""
 import numpy as np
 import pytest

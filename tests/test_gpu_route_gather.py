@@ -1,4 +1,4 @@
-"""The one-launch route map + permute of small batches (at most 4096 routes, row-major token scales) against the oracle,
+"""The one-launch route map + permute of small batches (at most 8192 routes, row-major token scales) against the oracle,
 on both sides of its size limit, with masked routes and a shared expert, and with rows longer than 8192 elements."""
 import numpy as np
 import pytest
@@ -55,10 +55,10 @@ def _check_map_and_rows(p, model):
 
 
 @pytest.mark.parametrize("tma_gather", [False, True])
-@pytest.mark.parametrize("tokens", [1, 3, 37, 511, 512, 513])
+@pytest.mark.parametrize("tokens", [1, 3, 37, 512, 1023, 1024, 1025])
 def test_small_batch_map_rows_and_output(tokens, tma_gather):
-    """7 routed slots + 1 shared expert = 8 routes per token: 512 tokens are exactly 4096 routes (the last size of the
-    one-launch form), 513 take the separate route-map and permute kernels; both must give the same tables. With the
+    """7 routed slots + 1 shared expert = 8 routes per token: 1024 tokens are exactly 8192 routes (the last size of the
+    one-launch form), 1025 take the separate route-map and permute kernels; both must give the same tables. With the
     permuted copy of the payload rows and without it (FC1 fetching the token rows by TMA gather)."""
     import kernelschema_b200 as ks
     from gpu_util import run_model
