@@ -337,8 +337,9 @@ DEV void gather_row(const GatherView& g, int tok, int pos, int lane) {
 // this block owns, others[e] = routes of e owned by other blocks, before[e] = those of them that precede this block's.
 // Out: segment starts, tile and pair tables and totals (stored by the `writer` block only), and hist[w][e] turned into
 // the permuted row of warp w's first route of expert e. Ends with a block barrier.
+template <int NW>                                  // NW = warps of the block = rows of hist
 DEV void scan_experts(int etot, const int* others, const int* before, int* hist, bool writer, const RouteMapBuffers& b) {
-  const int nw = (int)blockDim.x >> 5;             // warps of the block = rows of hist
+  constexpr int nw = NW;
   __shared__ int warp_pad[kRouteWarps], warp_tiles[kRouteWarps], warp_pairs[kRouteWarps], warp_cnt[kRouteWarps];
   __shared__ int carry[4];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -349,6 +350,7 @@ DEV void scan_experts(int etot, const int* others, const int* before, int* hist,
     int cnt = 0;
     if (e < etot) {
       cnt = others[e];
+#pragma unroll
       for (int w = 0; w < nw; ++w) cnt += hist[w * etot + e];
     }
     const int ntile = (cnt + 127) >> 7, pad = ntile << 7, npair = (ntile + 1) >> 1;
@@ -381,6 +383,7 @@ DEV void scan_experts(int etot, const int* others, const int* before, int* hist,
           }
       }
       int run = start + before[e];                   // per-warp bases of this expert, in place of the counts
+#pragma unroll
       for (int w = 0; w < nw; ++w) {
         const int c = hist[w * etot + e];
         hist[w * etot + e] = run;
@@ -450,7 +453,7 @@ __global__ void __launch_bounds__(kRouteThreads) k_route_fused(RouteView r, cons
       }
   }
   chunk_histogram(ex, etot, hist);                 // own chunk, per warp; its barriers also publish others/before
-  scan_experts(etot, others, before, hist, writer, b);
+  scan_experts<kRouteWarps>(etot, others, before, hist, writer, b);
   int pos[kRouteSteps];
 #pragma unroll
   for (int step = 0; step < kRouteSteps; ++step) {
@@ -480,10 +483,11 @@ __global__ void __launch_bounds__(kRouteThreads) k_route_fused(RouteView r, cons
 // whole map for itself in shared memory (a few thousand integer operations), block 0 stores it, and the blocks share the
 // row copies, one warp per routed row. The step loops are rolled: a one-wave, latency-bound kernel pays for every
 // instruction-cache line it touches, and a decode batch takes one step.
-__global__ void __launch_bounds__(kRouteThreads) k_route_gather(RouteView r, const float* __restrict__ scores, int etot, RouteMapBuffers b,
-                                                      GatherView gv) {
+template <int NW>                                  // warps per block: 8 for a handful of routes, kRouteWarps otherwise
+__global__ void __launch_bounds__(NW * 32) k_route_gather(RouteView r, const float* __restrict__ scores, int etot, RouteMapBuffers b,
+                                                     GatherView gv) {
   extern __shared__ int hist[];                    // [warps][etot] | zeros [etot] | zeros [etot] | expert, then row, of every route
-  const int nw = (int)blockDim.x >> 5;             // 8 warps for a handful of routes, kRouteWarps otherwise
+  constexpr int nw = NW;
   int* zeros = hist + nw * etot;
   int* s_pos = zeros + 2 * etot;
   const int kk = r.K + r.S;
@@ -511,7 +515,7 @@ __global__ void __launch_bounds__(kRouteThreads) k_route_gather(RouteView r, con
     __syncwarp();
   }
   __syncthreads();
-  scan_experts(etot, zeros, zeros + etot, hist, writer, b);
+  scan_experts<NW>(etot, zeros, zeros + etot, hist, writer, b);
 #pragma unroll 1
   for (int step = 0; step < nsteps; ++step) {
     const int f = warp * rpw + step * 32 + lane;
@@ -589,10 +593,13 @@ int launch_route_gather(const int32_t* ids, const float* scores, int64_t id_stri
   const int threads = total <= 256 ? 256 : kRouteThreads;
   int64_t blocks = (total + threads / 32 - 1) / (threads / 32);     // one row per warp while the SMs last
   if (blocks > sm_count()) blocks = sm_count();
+  if (threads == 256)       // at most 256 routes: their positions need 1 KB, the whole block stays far below 48 KB
+    return (int)launch_chain(k_route_gather<8>, dim3((unsigned)blocks), dim3(256), sizeof(int) * ((8 + 2) * (size_t)etot + 256), st, r,
+                             scores, etot, b, gv);
   static SmemOptIn opt_in;
-  if (int e = opt_in.ensure(k_route_gather, kRouteSmemMax)) return e;
-  return (int)launch_chain(k_route_gather, dim3((unsigned)blocks), dim3(threads),
-                           sizeof(int) * ((threads / 32 + 2) * (size_t)etot + kGatherMaxRoutes), st, r, scores, etot, b, gv);
+  if (int e = opt_in.ensure(k_route_gather<kRouteWarps>, kRouteSmemMax)) return e;
+  return (int)launch_chain(k_route_gather<kRouteWarps>, dim3((unsigned)blocks), dim3(kRouteThreads),
+                           sizeof(int) * ((kRouteWarps + 2) * (size_t)etot + kGatherMaxRoutes), st, r, scores, etot, b, gv);
 }
 
 // ----------------------------------------------------------------------------- allocation-free variant
