@@ -710,6 +710,12 @@ def run_gpu(args, wl):
                     fl2 = layer_flops(wl, float(v2.item()), tt * world)
                     sub[name] = dict(tokens_per_gpu=tt, ms_per_step=ms2, tflops=fl2 / (ms2 * 1e-3) / 1e12,
                                      tokens_per_s=tt * world / (ms2 * 1e-3), device_status=own2.status())
+                    if zipf is not None:      # where rank 0's step goes when every rank holds the same load
+                        own2.profile = True
+                        fn()
+                        torch.cuda.synchronize()
+                        sub[name]["stage_ms"] = own2.stage_ms()
+                        own2.profile = False
                 except Exception as exc:
                     sub[name] = dict(error=repr(exc)[:300])
     if rank != 0:
