@@ -48,13 +48,18 @@ __global__ void __launch_bounds__(256) k_ep_dispatch(const uint8_t* __restrict__
                                                      int shared_base, int32_t* __restrict__ row_of, float* __restrict__ weight_of_row,
                                                      unsigned int* __restrict__ done_counter) {
   const int world = peers.world;
-  const int rows = totals[1];
   const int lane = threadIdx.x & 31;
   const int warps = (gridDim.x * blockDim.x) >> 5;
   const int q_vecs = H >> 5, sf_words = H >> 6;
-  for (int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < rows; r += warps) {
+  // Message rows are grouped by destination. Every rank starts with the segment of the rank after itself and wraps around:
+  // walked from row 0 by all ranks at once, all of them would write into rank 0 first, then into rank 1, ... and a
+  // destination's inbound link would carry the traffic of the whole machine while the other links idle.
+  const int n_msg = seg_start[world];              // rows of the rank segments; the plan's shared-expert slot follows them
+  const int first = seg_start[(peers.rank + 1) % world];
+  for (int i = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; i < n_msg; i += warps) {
+    int r = i + first;
+    if (r >= n_msg) r -= n_msg;
     const int dest = tile_expert[r >> 7];
-    if (dest >= world) break;  // rows of the plan's shared-expert slot follow the last rank's segment: not messages
     uint8_t* dst = peers.recv[dest] + (size_t)(r - seg_start[dest]) * row_bytes;
     int32_t* id_dst = reinterpret_cast<int32_t*>(dst + (H >> 1) + (H >> 4));
     float* w_dst = reinterpret_cast<float*>(id_dst + K);
@@ -64,8 +69,7 @@ __global__ void __launch_bounds__(256) k_ep_dispatch(const uint8_t* __restrict__
       continue;
     }
     const int tok = tok_of_row[r];
-    const uint4* src = reinterpret_cast<const uint4*>(hid_q + (size_t)tok * (H >> 1));
-    for (int v = lane; v < q_vecs; v += 32) reinterpret_cast<uint4*>(dst)[v] = __ldg(src + v);
+    copy_row_batched(reinterpret_cast<const uint4*>(hid_q + (size_t)tok * (H >> 1)), reinterpret_cast<uint4*>(dst), q_vecs, lane);
     const uint32_t* sf_src = reinterpret_cast<const uint32_t*>(hid_sf + (size_t)tok * (H >> 4));
     for (int w = lane; w < sf_words; w += 32) reinterpret_cast<uint32_t*>(dst + (H >> 1))[w] = __ldg(sf_src + w);
     if (lane < K) {
@@ -127,7 +131,11 @@ __global__ void __launch_bounds__(128) k_finalize_ep(const __nv_bfloat16* __rest
   const int vecs = H >> 3;
   pdl_trigger();
   pdl_wait();
-  for (int64_t t = blockIdx.x; t < T; t += gridDim.x) {
+  // sources are visited starting with the rank after this one (see k_ep_dispatch: all ranks returning rows to the same source
+  // at the same time would share that source's inbound link)
+  const int64_t first = (int64_t)((peers.rank + 1) % peers.world) * seg_len;
+  for (int64_t tt = blockIdx.x; tt < T; tt += gridDim.x) {
+    const int64_t t = tt + first < T ? tt + first : tt + first - T;
     const int s = (int)(t / seg_len);
     const int i = (int)(t - (int64_t)s * seg_len);
     if (i >= ctrl[kEpCount + s]) continue;

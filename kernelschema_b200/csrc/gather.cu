@@ -48,19 +48,6 @@ __global__ void __launch_bounds__(256) k_gather_rows(const uint8_t* __restrict__
   }
 }
 
-// One payload row by one warp, eight 16-byte vectors per lane in flight (all loads of a batch before its stores).
-DEV void copy_row_batched(const uint4* __restrict__ src, uint4* __restrict__ dst, int vecs, int lane) {
-  for (int v0 = lane; v0 < vecs; v0 += 32 * 8) {
-    uint4 t[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i)
-      if (v0 + 32 * i < vecs) t[i] = __ldg(src + v0 + 32 * i);
-#pragma unroll
-    for (int i = 0; i < 8; ++i)
-      if (v0 + 32 * i < vecs) dst[v0 + 32 * i] = t[i];
-  }
-}
-
 // Tile form of the permute for row-major token scales: one block of 16 warps per 128-row tile of the permuted buffer. Warps
 // 0-3 assemble the tile's scale image ([H/64] chunks of 512 bytes, the layout tcgen05.cp consumes) in shared memory -
 // thread r walks the scale bytes of row r's token with 16-byte loads - and store it with full 16-byte coalesced writes

@@ -291,4 +291,17 @@ DEV uint4 pack_bf16x8(const float (&acc)[8]) {
   return o;
 }
 
+// One payload row by one warp, eight 16-byte vectors per lane in flight (all loads of a batch before its stores).
+DEV void copy_row_batched(const uint4* __restrict__ src, uint4* __restrict__ dst, int vecs, int lane) {
+  for (int v0 = lane; v0 < vecs; v0 += 32 * 8) {
+    uint4 t[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      if (v0 + 32 * i < vecs) t[i] = __ldg(src + v0 + 32 * i);
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      if (v0 + 32 * i < vecs) dst[v0 + 32 * i] = t[i];
+  }
+}
+
 }  // namespace b200
