@@ -16,7 +16,7 @@ constexpr int kRouteChunk = 2048;        // routes per block: 32 warps x 2 steps
 constexpr int kRouteWarps = 32;          // these kernels are a few thousand dependent instructions per warp and one block per
                                          // chunk: with 8 warps a block issued one instruction every ~5 cycles per scheduler
 constexpr int kRouteThreads = kRouteWarps * 32;
-constexpr int kRouteSmemMax = 160 * 1024;  // (32 + 2) x 1024 experts x 4 B + 16 KB of positions
+constexpr int kRouteSmemMax = 176 * 1024;  // (32 + 2) x 1024 experts x 4 B + 32 KB of positions (kGatherMaxRoutes x 4 B)
 
 struct RouteView {
   const int32_t* ids;

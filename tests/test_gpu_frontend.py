@@ -175,7 +175,8 @@ def test_router_logits(t, h, e):
 
 
 @pytest.mark.parametrize("t,k,e,shared,offset", [(1, 8, 128, 0, 0), (300, 4, 8, 0, 0), (4096, 8, 256, 1, 0),
-                                                 (1000, 8, 32, 0, 64), (50, 2, 4, 2, 0), (2049, 1, 3, 0, 0), (600, 8, 512, 0, 0), (1500, 8, 128, 1, 0)])
+                                                 (1000, 8, 32, 0, 64), (50, 2, 4, 2, 0), (2049, 1, 3, 0, 0), (600, 8, 512, 0, 0), (1500, 8, 128, 1, 0),
+                                                 (300, 8, 1000, 1, 0), (5000, 8, 1000, 0, 0)])
 def test_route_map_matches_oracle(t, k, e, shared, offset):
     import kernelschema_b200 as ks
     rng = np.random.default_rng(t * 7 + e)
